@@ -1,0 +1,116 @@
+/*
+ * C-ABI of the B200 block-sparse matmul engine (libbsmm_b200.so).
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless stated
+ * otherwise, every size is in elements, the library allocates nothing and keeps no
+ * state between calls, and each call only enqueues work on `stream` (a
+ * cudaStream_t passed as void*; NULL = the legacy default stream).  Return value:
+ * BSMM_OK or one of the BSMM_ERR_* codes; bsmm_status_string() names them.
+ *
+ * The weight format is the reference's (pytorch_block_sparse/block_sparse.py:10-76,
+ * :125-153): `data` fp32 [nnz*32, 32], slot s holding its 32x32 block transposed
+ * (data[s*32+c][r] = W[R*32+r][C*32+c]); CSR `ptr`/`idx` = row_start_ends_a/cols_a,
+ * CSC = col_start_ends_b/rows_b, where idx is int32 [nnz,2] = (other-axis block
+ * index, slot); `blocks` int32 [2*nnz] = (block-col, block-row) per slot.
+ */
+#ifndef BSMM_B200_H_
+#define BSMM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSMM_ABI_VERSION 1
+
+/* status codes */
+#define BSMM_OK 0
+#define BSMM_ERR_INVALID_ARGUMENT 1 /* null pointer, negative size, size not a multiple of 32, misaligned pointer */
+#define BSMM_ERR_UNSUPPORTED 2      /* flag combination this build has no kernel for */
+#define BSMM_ERR_CUDA 3             /* a CUDA call failed; bsmm_last_cuda_error() returns the cudaError_t */
+#define BSMM_ERR_TOO_LARGE 4        /* size exceeds a documented limit */
+
+/* arithmetic of a contraction (bits 0..3 of `flags`) */
+#define BSMM_PREC_FP32_SIMT 0u /* exact fp32 FMA on CUDA cores (the reference's arithmetic) */
+#define BSMM_PREC_TF32X3 1u    /* tcgen05 kind::tf32, 3-pass hi/lo split, fp32-class accuracy  */
+#define BSMM_PREC_BF16 2u      /* tcgen05 kind::f16 on bf16 operands, fp32 accumulate        */
+#define BSMM_PREC_MASK 0xFu
+
+/* bsmm_dsd flags */
+#define BSMM_DSD_DGRAD 0x10u        /* 0: out = a * W^T (CSR given); 1: out = a * W (CSC given) */
+#define BSMM_DSD_OUT_COLMAJOR 0x20u /* 0: out is [m, n] row-major; 1: out is [n, m] (the reference's buffer) */
+
+/* bsmm_sddmm flags */
+#define BSMM_SDDMM_A_COLMAJOR 0x10u /* dY given as [rows, tokens] contiguous instead of [tokens, rows] */
+#define BSMM_SDDMM_B_COLMAJOR 0x20u /* X  given as [cols, tokens] contiguous instead of [tokens, cols] */
+
+typedef void* bsmm_stream_t;
+
+int bsmm_abi_version(void);
+const char* bsmm_status_string(int status);
+/* cudaError_t of the most recent BSMM_ERR_CUDA on the calling thread (0 if none). */
+int bsmm_last_cuda_error(void);
+/*
+ * Device-side health word of the current device: 0, or non-zero once a tensor-core kernel gave up
+ * on one of its bounded waits (its output is then invalid).  Synchronizes the device; `clear`
+ * resets the word.  `status` is a HOST pointer.  The reference has no counterpart: its split-K
+ * semaphore spins without a limit (cutlass/gemm/k_split_control.h:147-156).
+ */
+int bsmm_device_status(unsigned int* status, int clear);
+
+/*
+ * Kernel-ready weight images + the per-slot sum of squares used by block_norm
+ * (reference block_sparse.py:155-157; replaces the per-call transposed weight copy at
+ * block_sparse.py:538-544).  `packed` must hold bsmm_packed_bytes(nnz, precision) bytes,
+ * 256-byte aligned; `block_sumsq` (fp32 [nnz], may be NULL) receives sum(data[s]^2).
+ * precision FP32_SIMT needs no images: packed may be NULL and only the statistic is produced.
+ */
+int64_t bsmm_packed_bytes(int64_t nnz, uint32_t precision);
+int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* packed, float* block_sumsq,
+                      bsmm_stream_t stream);
+
+/*
+ * Per-pattern launch plan of the tensor-core dsd kernel: for every group of
+ * BSMM_PLAN_GROUP consecutive output block-rows, the group's index entries re-ordered by
+ * (inner block index, row-in-group).  `plan` must hold bsmm_plan_bytes(nnz) bytes.
+ * Depends only on ptr/idx; rebuild after block_replace / load_state_dict.
+ */
+#define BSMM_PLAN_GROUP 8
+int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz);
+int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, void* plan,
+                    bsmm_stream_t stream);
+
+/*
+ * Dense x block-sparse -> dense.  Replaces blocksparse_matmul_cutlass
+ * (reference native/block_sparse_native.cpp:6-16, native/block_sparse_cutlass_kernel.cu:113-150):
+ *   fwd   (flags without BSMM_DSD_DGRAD): out[m, n] = a[m, k] * W^T (+ bias[n]),  W is [n, k], ptr/idx = CSR
+ *   dgrad (BSMM_DSD_DGRAD)              : out[m, n] = a[m, k] * W,               W is [k, n], ptr/idx = CSC
+ * a: [m, k] row-major (fp32, or bf16 with BSMM_PREC_BF16); out: same element type; m is free,
+ * n and k are multiples of 32.  Every output element is written (empty block-rows give zeros),
+ * so `out` needs no pre-zeroing.  `data` is always required; `packed`/`plan` are required by the
+ * tensor-core precisions and ignored by FP32_SIMT.  bias may be NULL.
+ */
+int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+             const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
+             uint32_t flags, bsmm_stream_t stream);
+
+/*
+ * Dense^T x dense -> block-sparse (SDDMM).  Replaces blocksparse_matmul_back_cutlass
+ * (reference native/block_sparse_native.cpp:18-29, native/block_sparse_cutlass_kernel_back.cu:118-160):
+ *   sparse_c[s*32 + c][r] = sum_t a[t, R*32+r] * b[t, C*32+c],  (C, R) = blocks[2s], blocks[2s+1]
+ * a = dY [tokens, rows], b = X [tokens, cols] (row-major unless the *_COLMAJOR flag is set),
+ * rows/cols multiples of 32, tokens free.  sparse_c fp32 [nnz*32, 32] is overwritten (beta = 0).
+ * `block_sumsq` (fp32 [nnz], may be NULL) receives sum(sparse_c[s]^2).
+ * `workspace` (may be NULL) must hold bsmm_sddmm_workspace_bytes(...) bytes when that is non-zero.
+ */
+int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t flags);
+int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens, float* sparse_c,
+               const int32_t* blocks, int64_t nnz, float* block_sumsq, void* workspace, uint32_t flags,
+               bsmm_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BSMM_B200_H_ */

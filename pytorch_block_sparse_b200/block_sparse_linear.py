@@ -1,0 +1,157 @@
+"""Drop-in ``nn.Linear`` with a block-sparse weight and its autograd function.
+
+Mirrors ``pytorch_block_sparse/block_sparse_linear.py`` of the reference: same constructor
+arguments, same initialisation rules, same three contractions per layer --
+
+* forward ``y = x @ W.T + b``      (reference ``block_sparse_linear.py:40``, ``:229-233``)
+* dgrad   ``dx = dy @ W``           (``:80``)
+* wgrad   ``dW = dy.T @ x`` at W's non-zero blocks, in ``data`` layout (``:123``)
+
+-- each served by a CUDA kernel behind the C-ABI.  Differences, all invisible in values:
+the bias is added in the forward kernel's epilogue instead of a separate elementwise pass,
+dgrad no longer copies the weights transposed per call, and the reference's
+``assert not (grad == 0).all()`` device->host sync after wgrad is not kept.
+"""
+import math
+from typing import Tuple
+
+import torch
+import torch.autograd
+import torch.nn as nn
+
+from .block_sparse import BlockSparseMatrix, BlockSparseMatrixBase, BlockSparseMatrixEmulator
+
+
+class BlockSparseLinearFunction(torch.autograd.Function):
+    """``apply(input, weight_data, weight[, bias])``.
+
+    ``weight_data`` is ``weight.get_differentiable_data()`` passed separately so that the
+    Parameter receives the gradient (reference ``block_sparse_linear.py:15-53``, ``:154``).
+    The optional 4th argument fuses the bias add into the forward kernel.
+    """
+
+    @staticmethod
+    def forward(ctx, input, weight_data, weight, *maybe_bias):
+        assert isinstance(weight, BlockSparseMatrixBase)
+        bias = maybe_bias[0] if maybe_bias else None
+        ctx.save_for_backward(input, weight_data)
+        ctx.weight = weight
+        ctx.n_extra = len(maybe_bias)
+        ctx.has_bias = bias is not None
+        return weight.reverse_matmul(input, transpose=True, bias=bias)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, weight_data = ctx.saved_tensors
+        weight = ctx.weight
+        grad_input = grad_weight = grad_bias = None
+        if ctx.needs_input_grad[0]:
+            grad_input = weight.reverse_matmul(grad_output, transpose=False)
+            assert grad_input.shape == input.shape
+        if ctx.needs_input_grad[1]:
+            grad_weight = weight.matmul_with_output_sparse_support(grad_output, input)
+        if ctx.has_bias and ctx.needs_input_grad[3]:
+            grad_bias = grad_output.reshape(-1, grad_output.shape[-1]).sum(0)
+        return (grad_input, grad_weight, None, grad_bias)[: 3 + ctx.n_extra]
+
+
+class BlockSparseLinear(nn.Module):
+    """Block-sparse replacement of ``torch.nn.Linear`` (reference ``block_sparse_linear.py:157-233``).
+
+    ``density`` fixes the block count as ``int(density * in * out / (bh * bw))``.  Built from
+    ``torch_nn_linear`` it takes that layer's sizes and bias, fills ``data`` through
+    ``from_dense`` and rescales by ``1/sqrt(density)``.  Block shapes other than 32x32 use the
+    dense-masked emulator class, as in the reference.  Parameters live on ``"cuda"``.
+    """
+
+    OPTIMIZED_BLOCK_SIZE = 32
+
+    def __init__(
+        self,
+        in_features: int,
+        out_features: int,
+        bias: bool = True,
+        density: float = 0.5,
+        torch_nn_linear=None,
+        verbose: bool = False,
+        block_shape: Tuple[int, int] = (32, 32),
+    ):
+        super().__init__()
+        self.fn = BlockSparseLinearFunction.apply
+        self.verbose = verbose
+        self.block_shape = block_shape
+        self._optimized = block_shape[0] == self.OPTIMIZED_BLOCK_SIZE and block_shape[1] == self.OPTIMIZED_BLOCK_SIZE
+
+        if torch_nn_linear is not None:
+            in_features = torch_nn_linear.in_features
+            out_features = torch_nn_linear.out_features
+            bias = torch_nn_linear.bias is not None
+
+        if in_features % block_shape[1] != 0:
+            raise Exception(f"BlockSparseLinear invalid in_features={in_features}, should be multiple of {block_shape[1]}")
+        if out_features % block_shape[0] != 0:
+            raise Exception(f"BlockSparseLinear invalid in_features={in_features}, should be multiple of {block_shape[0]}")
+        if density < 0 or density > 1:
+            raise Exception(f"BlockSparseLinear invalid density={density}")
+
+        self.block_count = int(density * (in_features * out_features / (block_shape[0] * block_shape[1])))
+        self.in_features = in_features
+        self.out_features = out_features
+
+        matrix_cls = BlockSparseMatrix if self._optimized else BlockSparseMatrixEmulator
+        if torch_nn_linear is not None:
+            with torch.no_grad():
+                weight = matrix_cls.from_dense(torch_nn_linear.weight.to("cuda"), block_shape, self.block_count)
+            weight.multiply_(1.0 / math.sqrt(density))
+        else:
+            weight = matrix_cls.randn(
+                (out_features, in_features), self.block_count, blocks=None, block_shape=block_shape, device="cuda"
+            )
+        self.weight = weight
+
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(out_features, device="cuda"))
+            if torch_nn_linear is not None:
+                with torch.no_grad():
+                    self.bias.copy_(torch_nn_linear.bias)
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x):
+        if self._optimized:
+            return self.fn(x, self.weight.get_differentiable_data(), self.weight, self.bias)
+        x = self.fn(x, self.weight.get_differentiable_data(), self.weight)
+        if self.bias is not None:
+            x = x + self.bias
+        return x
+
+    def extra_repr(self):
+        return "in_features={}, out_features={}, bias={}, block_count={}".format(
+            self.in_features, self.out_features, self.bias is not None, self.block_count
+        )
+
+
+class PseudoBlockSparseLinear(torch.nn.Module):
+    """Pure-torch twin of a :class:`BlockSparseLinear` for debugging (reference ``block_sparse_linear.py:236-262``)."""
+
+    def __init__(self, block_sparse_linear):
+        super().__init__()
+        matrix = block_sparse_linear.weight.cuda()
+        self.weight = torch.nn.Parameter(matrix.to_dense())
+        mask = matrix.to_dense(data_replace=torch.ones_like(matrix.data)) == 1
+        if block_sparse_linear.bias is not None:
+            self.bias = torch.nn.Parameter(block_sparse_linear.bias)
+        else:
+            self.register_parameter("bias", None)
+        self.register_buffer("mask", mask)
+        self.in_features = block_sparse_linear.in_features
+        self.out_features = block_sparse_linear.out_features
+        self.density = mask.sum().item() / (mask.shape[0] * mask.shape[1])
+
+    def forward(self, input):
+        return torch.nn.functional.linear(input, self.weight * self.mask, self.bias)
+
+    def extra_repr(self):
+        return "in_features={}, out_features={}, bias={}, fill_ratio={}".format(
+            self.in_features, self.out_features, self.bias is not None, self.density
+        )

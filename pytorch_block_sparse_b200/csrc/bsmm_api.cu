@@ -1,0 +1,144 @@
+// extern "C" entry points of libbsmm_b200.so: argument validation and kernel selection.
+#include "bsmm_common.cuh"
+#include "bsmm_umma.cuh"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int cuda_status(cudaError_t err) {
+    if (err == cudaSuccess) return BSMM_OK;
+    g_last_cuda_error = static_cast<int>(err);
+    return BSMM_ERR_CUDA;
+}
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+int bsmm_abi_version(void) { return BSMM_ABI_VERSION; }
+
+const char* bsmm_status_string(int status) {
+    switch (status) {
+        case BSMM_OK: return "ok";
+        case BSMM_ERR_INVALID_ARGUMENT: return "invalid argument (null/misaligned pointer, negative size, or size not a multiple of 32)";
+        case BSMM_ERR_UNSUPPORTED: return "unsupported flag combination";
+        case BSMM_ERR_CUDA: return "CUDA error (see bsmm_last_cuda_error)";
+        case BSMM_ERR_TOO_LARGE: return "size exceeds a documented limit";
+        default: return "unknown status";
+    }
+}
+
+int bsmm_last_cuda_error(void) { return g_last_cuda_error; }
+
+int bsmm_device_status(unsigned int* status, int clear) {
+    if (status == nullptr) return BSMM_ERR_INVALID_ARGUMENT;
+    return cuda_status(bsmm::read_device_status(status, clear != 0));
+}
+
+int64_t bsmm_packed_bytes(int64_t nnz, uint32_t precision) {
+    if (nnz < 0) return -1;
+    return 2 * nnz * bsmm::packed_slot_bytes(precision & BSMM_PREC_MASK);
+}
+
+int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* packed, float* block_sumsq,
+                      bsmm_stream_t stream) {
+    precision &= BSMM_PREC_MASK;
+    if (nnz < 0 || (nnz > 0 && data == nullptr) || !aligned(data, 16)) return BSMM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (precision == BSMM_PREC_FP32_SIMT) {
+        if (block_sumsq == nullptr) return BSMM_OK;
+        return cuda_status(bsmm::launch_block_sumsq(data, nnz, block_sumsq, s));
+    }
+    if (precision != BSMM_PREC_TF32X3 && precision != BSMM_PREC_BF16) return BSMM_ERR_UNSUPPORTED;
+    if (nnz > 0 && (packed == nullptr || !aligned(packed, 256))) return BSMM_ERR_INVALID_ARGUMENT;
+    return cuda_status(bsmm::launch_pack(data, nnz, precision, packed, block_sumsq, s));
+}
+
+int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz) {
+    if (n_out_blocks < 0 || nnz < 0) return -1;
+    return bsmm::plan_bytes(n_out_blocks, nnz);
+}
+
+int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, void* plan,
+                    bsmm_stream_t stream) {
+    if (n_out_blocks < 0 || nnz < 0 || ptr == nullptr || plan == nullptr || (nnz > 0 && idx == nullptr))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (!aligned(plan, 16) || !aligned(idx, 8)) return BSMM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0x7fffffff || n_out_blocks > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
+    return cuda_status(bsmm::launch_build_plan(ptr, idx, n_out_blocks, nnz, plan, static_cast<cudaStream_t>(stream)));
+}
+
+int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+             const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
+             uint32_t flags, bsmm_stream_t stream) {
+    const uint32_t precision = flags & BSMM_PREC_MASK;
+    const bool dgrad = (flags & BSMM_DSD_DGRAD) != 0;
+    const bool colmajor = (flags & BSMM_DSD_OUT_COLMAJOR) != 0;
+    if (m < 0 || n < 0 || k < 0 || nnz < 0 || (n % 32) != 0 || (k % 32) != 0) return BSMM_ERR_INVALID_ARGUMENT;
+    if (m == 0 || n == 0) return BSMM_OK;
+    if (ptr == nullptr || out == nullptr || (nnz > 0 && (idx == nullptr || data == nullptr || a == nullptr)))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (!aligned(a, 16) || !aligned(out, 16) || !aligned(data, 16) || !aligned(idx, 8))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (dgrad && bias != nullptr) return BSMM_ERR_UNSUPPORTED;
+    if (nnz > 0x7fffffff || n / 32 > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (precision == BSMM_PREC_FP32_SIMT) {
+        if (colmajor && (m + 127) / 128 > 65535) return BSMM_ERR_TOO_LARGE;
+        return cuda_status(bsmm::launch_dsd_simt(static_cast<const float*>(a), m, k, ptr, idx, data, n,
+                                                 static_cast<float*>(out), bias, dgrad, colmajor, s));
+    }
+    if (precision == BSMM_PREC_TF32X3 || precision == BSMM_PREC_BF16) {
+        if (packed == nullptr || plan == nullptr || !aligned(packed, 256) || !aligned(plan, 16))
+            return BSMM_ERR_INVALID_ARGUMENT;
+        return cuda_status(bsmm::launch_dsd_umma(a, m, k, nnz, packed, plan, n, out, bias, precision, dgrad,
+                                                 colmajor, s));
+    }
+    return BSMM_ERR_UNSUPPORTED;
+}
+
+int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t flags) {
+    if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0) return -1;
+    const uint32_t precision = flags & BSMM_PREC_MASK;
+    if (precision == BSMM_PREC_FP32_SIMT) return 0;
+    return bsmm::sddmm_umma_workspace_bytes(rows, cols, tokens, nnz, precision);
+}
+
+int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens, float* sparse_c,
+               const int32_t* blocks, int64_t nnz, float* block_sumsq, void* workspace, uint32_t flags,
+               bsmm_stream_t stream) {
+    const uint32_t precision = flags & BSMM_PREC_MASK;
+    const bool a_col = (flags & BSMM_SDDMM_A_COLMAJOR) != 0;
+    const bool b_col = (flags & BSMM_SDDMM_B_COLMAJOR) != 0;
+    if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0 || (rows % 32) != 0 || (cols % 32) != 0)
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (nnz == 0) return BSMM_OK;
+    if (sparse_c == nullptr || blocks == nullptr || (tokens > 0 && (a == nullptr || b == nullptr)))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (!aligned(a, 16) || !aligned(b, 16) || !aligned(sparse_c, 16) || !aligned(blocks, 8))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (precision == BSMM_PREC_FP32_SIMT) {
+        return cuda_status(bsmm::launch_sddmm_simt(static_cast<const float*>(a), a_col, static_cast<const float*>(b),
+                                                   b_col, rows, cols, tokens, sparse_c, blocks, nnz, block_sumsq, s));
+    }
+    if (precision == BSMM_PREC_TF32X3 || precision == BSMM_PREC_BF16) {
+        if (a_col || b_col) return BSMM_ERR_UNSUPPORTED;
+        const cudaError_t err = bsmm::launch_sddmm_umma(a, b, rows, cols, tokens, sparse_c, blocks, nnz, block_sumsq,
+                                                        workspace, precision, s);
+        // shapes the tensor-core kernel does not take run on the CUDA-core kernel (same fp32-class result)
+        if (err == cudaErrorNotSupported && precision == BSMM_PREC_TF32X3)
+            return cuda_status(bsmm::launch_sddmm_simt(static_cast<const float*>(a), false,
+                                                       static_cast<const float*>(b), false, rows, cols, tokens,
+                                                       sparse_c, blocks, nnz, block_sumsq, s));
+        return cuda_status(err);
+    }
+    return BSMM_ERR_UNSUPPORTED;
+}
+
+}  // extern "C"

@@ -1,0 +1,70 @@
+// Launch-plan builder for the tensor-core dsd kernel.
+//
+// The kernel owns a tile of 128 tokens x BSMM_PLAN_GROUP output block-rows and walks the
+// contraction axis one 32-wide activation slab at a time, so it wants the group's blocks merged
+// across its rows and ordered by slab.  The CSR/CSC arrays of the reference
+// (block_sparse.py:85-153) list each row's blocks in ascending inner index; the merged position of
+// an entry is therefore a sum of lower bounds over the rows of its group -- no sort needed.
+#include "bsmm_umma.cuh"
+
+namespace bsmm {
+namespace {
+
+constexpr int G = BSMM_PLAN_GROUP;
+
+__global__ void __launch_bounds__(128)
+build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx, int n_out_blocks,
+                  int32_t* __restrict__ group_off, PlanEntry* __restrict__ entries) {
+    __shared__ int rp[G + 1];
+    const int g = blockIdx.x;
+    const int r0 = g * G;
+    const int nrows = min(G, n_out_blocks - r0);
+    if (threadIdx.x <= G) rp[threadIdx.x] = ptr[r0 + min((int)threadIdx.x, nrows)];
+    __syncthreads();
+    const int base = rp[0], end = rp[nrows];
+    if (threadIdx.x == 0) {
+        group_off[g] = base;
+        if (g == gridDim.x - 1) group_off[g + 1] = end;
+    }
+    for (int e = base + threadIdx.x; e < end; e += blockDim.x) {
+        const int2 ent = idx[e];
+        int r = 0;
+        while (r + 1 < nrows && rp[r + 1] <= e) ++r;
+        int rank = 0;
+        bool before = false, after = false;
+        for (int q = 0; q < nrows; ++q) {
+            int lo = rp[q], hi = rp[q + 1];
+            const int row_end = hi;
+            while (lo < hi) {  // first entry of row q whose inner index is >= ent.x
+                const int mid = (lo + hi) >> 1;
+                if (idx[mid].x < ent.x) lo = mid + 1; else hi = mid;
+            }
+            rank += lo - rp[q];
+            const bool present = lo < row_end && idx[lo].x == ent.x;
+            if (present && q < r) { ++rank; before = true; }
+            if (present && q > r) after = true;
+        }
+        PlanEntry pe;
+        pe.inner = ent.x;
+        pe.slot = ent.y;
+        pe.row = r;
+        pe.flags = (before ? 0 : kPlanFirst) | (after ? 0 : kPlanLast);
+        entries[base + rank] = pe;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, void* plan,
+                              cudaStream_t stream) {
+    (void)nnz;
+    const int64_t groups = plan_groups(n_out_blocks);
+    if (groups == 0) return cudaSuccess;
+    int32_t* group_off = static_cast<int32_t*>(plan);
+    PlanEntry* entries = reinterpret_cast<PlanEntry*>(static_cast<uint8_t*>(plan) + plan_entries_offset(n_out_blocks));
+    build_plan_kernel<<<(unsigned)groups, 128, 0, stream>>>(ptr, reinterpret_cast<const int2*>(idx), (int)n_out_blocks,
+                                                            group_off, entries);
+    return cudaGetLastError();
+}
+
+}  // namespace bsmm

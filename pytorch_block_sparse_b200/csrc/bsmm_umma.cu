@@ -1,0 +1,356 @@
+// Tensor-core dense x block-sparse -> dense kernel for sm_100a (forward and dgrad of one
+// block-sparse Linear; replaces the reference's cutlass::gemm::kernel<block_task>,
+// cutlass/gemm/dispatch.h:185-218 and block_task.h:647-715).
+//
+// Tile: 128 tokens x G = BSMM_PLAN_GROUP output block-rows (G*32 columns) per CTA, accumulated in
+// tensor memory (G*32 fp32 columns).  The contraction axis is walked one 32-wide activation slab
+// at a time, visiting only slabs for which the group has at least one block (the plan lists them).
+//
+//   warp 0   producer : TMA tensor load of the [128 x 32] fp32 activation slab (128-B swizzle) and
+//                       one 8 KiB linear bulk copy per block of its packed hi/lo weight images
+//   warps 2-5 transform: slab smem -> registers, split into tf32 hi/lo, tcgen05.st into tensor
+//                       memory (lane = token, column = k), which makes it the MMA's A operand
+//   warp 1   MMA      : per block 4 k-steps x 3 passes (hi*hi, hi*lo, lo*hi) of
+//                       tcgen05.mma kind::tf32 M=128 N=32 K=8, A from tensor memory, B from smem
+//   warps 2-5 epilogue: tcgen05.ld accumulators -> (+bias) -> global stores
+//
+// A from tensor memory keeps shared-memory operand traffic at 1 KiB per MMA (the weight image);
+// with both operands in shared memory an N=32 MMA would be limited by the 4 KiB A read.
+// Every mbarrier wait is bounded; on expiry the CTA raises the device status word and drains.
+#include <cuda.h>
+
+#include "bsmm_ptx.cuh"
+#include "bsmm_umma.cuh"
+
+namespace bsmm {
+
+__device__ unsigned int g_device_status = 0;  // sticky: non-zero once any CTA gave up on a wait
+
+namespace {
+
+using namespace ptx;
+
+constexpr int G = BSMM_PLAN_GROUP;
+constexpr int kTileTokens = 128;
+constexpr int kXStages = 4;   // activation slabs in shared memory
+constexpr int kWStages = 8;   // weight image sets in shared memory
+constexpr int kAStages = 4;   // split activation slabs in tensor memory
+constexpr uint32_t kXStageBytes = kTileTokens * 32 * 4;  // 16 KiB
+constexpr uint32_t kWStageBytes = 2 * kImage32Bytes;     // 8 KiB: hi image, lo image
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccCols = G * 32;                    // 256
+constexpr uint32_t kAStageCols = 64;                     // hi: 32 columns, lo: 32 columns
+
+constexpr uint32_t kOffX = 0;
+constexpr uint32_t kOffW = kOffX + kXStages * kXStageBytes;
+constexpr uint32_t kOffBar = kOffW + kWStages * kWStageBytes;
+constexpr int kNumBars = 2 * kXStages + 2 * kWStages + 2 * kAStages + 1;
+constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
+constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;  // + slack for 1 KiB alignment of the base
+
+constexpr int kThreads = 192;
+
+struct DsdParams {
+    const uint8_t* packed;     // image sets of this orientation, slot-major
+    const int32_t* group_off;  // [groups + 1]
+    const PlanEntry* entries;
+    const float* bias;         // may be null
+    float* out;
+    int64_t m, n;
+    int32_t n_out_blocks, groups;
+    int32_t out_colmajor;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+dsd_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t bar0 = smem_base + kOffBar;
+    auto x_full = [&](int s) { return bar0 + 8u * s; };
+    auto x_empty = [&](int s) { return bar0 + 8u * (kXStages + s); };
+    auto w_full = [&](int s) { return bar0 + 8u * (2 * kXStages + s); };
+    auto w_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + kWStages + s); };
+    auto a_full = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + s); };
+    auto a_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + kAStages + s); };
+    const uint32_t acc_full = bar0 + 8u * (kNumBars - 1);
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + kOffMisc);
+    // misc[0]: tensor-memory base address, misc[1]: abort flag
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int g = blockIdx.x % p.groups;
+    const int64_t tok0 = (int64_t)(blockIdx.x / p.groups) * kTileTokens;
+    const int e0 = p.group_off[g], e1 = p.group_off[g + 1];
+    const int nrows = min(G, p.n_out_blocks - g * G);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kXStages; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); }
+        for (int s = 0; s < kWStages; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1); }
+        for (int s = 0; s < kAStages; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), 1); }
+        mbar_init(acc_full, 1);
+        misc[1] = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_base + kOffMisc, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = misc[0];
+    volatile uint32_t* abort_flag = &misc[1];
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            int xs = 0, ws = 0;
+            uint32_t xph = 0, wph = 0;
+            for (int e = e0; e < e1; ++e) {
+                const PlanEntry ent = p.entries[e];
+                if (ent.flags & kPlanFirst) {
+                    if (!mbar_wait(x_empty(xs), xph ^ 1u, abort_flag)) break;
+                    mbar_arrive_expect_tx(x_full(xs), kXStageBytes);
+                    tma_load_2d(smem_base + kOffX + xs * kXStageBytes, &tmap_a, ent.inner * 32, (int32_t)tok0,
+                                x_full(xs));
+                    if (++xs == kXStages) { xs = 0; xph ^= 1u; }
+                }
+                if (!mbar_wait(w_empty(ws), wph ^ 1u, abort_flag)) break;
+                mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
+                bulk_load(smem_base + kOffW + ws * kWStageBytes, p.packed + (int64_t)ent.slot * kWStageBytes,
+                          kWStageBytes, w_full(ws));
+                if (++ws == kWStages) { ws = 0; wph ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(2u, 128u, 32u, false, false);
+            int ws = 0, as = 0;
+            uint32_t wph = 0, aph = 0;
+            uint32_t touched = 0;
+            uint32_t a_hi = 0;
+            bool ok = true;
+            for (int e = e0; e < e1 && ok; ++e) {
+                const PlanEntry ent = p.entries[e];
+                if (ent.flags & kPlanFirst) {
+                    if (!mbar_wait(a_full(as), aph, abort_flag)) { ok = false; break; }
+                    a_hi = tmem + kAccCols + as * kAStageCols;
+                }
+                if (!mbar_wait(w_full(ws), wph, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t w_addr = smem_base + kOffW + ws * kWStageBytes;
+                const uint64_t b_hi = smem_desc_noswizzle(w_addr, 512, 128);
+                const uint64_t b_lo = smem_desc_noswizzle(w_addr + kImage32Bytes, 512, 128);
+                const uint32_t d = tmem + ent.row * 32;
+                uint32_t accumulate = (touched >> ent.row) & 1u;
+                touched |= 1u << ent.row;
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const uint64_t koff = (uint64_t)((s * 1024) >> 4);  // two 512-B k-chunks per step
+                    mma_ts_tf32(d, a_hi + 32 + s * 8, b_hi + koff, idesc, accumulate);  // lo * hi
+                    mma_ts_tf32(d, a_hi + s * 8, b_lo + koff, idesc, 1u);               // hi * lo
+                    mma_ts_tf32(d, a_hi + s * 8, b_hi + koff, idesc, 1u);               // hi * hi
+                    accumulate = 1u;
+                }
+                mma_commit(w_empty(ws));
+                if (++ws == kWStages) { ws = 0; wph ^= 1u; }
+                if (ent.flags & kPlanLast) {
+                    mma_commit(a_empty(as));
+                    if (++as == kAStages) { as = 0; aph ^= 1u; }
+                }
+            }
+            mma_commit(acc_full);
+        }
+    } else {
+        // ------------------------------------------------------------------ transform, then epilogue
+        const int quarter = warp & 3;              // tensor-memory lane quarter this warp may access
+        const int row = quarter * 32 + lane;       // token inside the tile = tensor-memory lane
+        const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        int xs = 0, as = 0;
+        uint32_t xph = 0, aph = 0;
+        uint32_t touched = 0;
+        bool ok = true;
+        for (int e = e0; e < e1; ++e) {
+            const PlanEntry ent = p.entries[e];
+            touched |= 1u << ent.row;
+            if (!(ent.flags & kPlanFirst) || !ok) continue;
+            ok = __all_sync(0xffffffffu, mbar_wait(x_full(xs), xph, abort_flag));
+            if (!ok) continue;
+            uint32_t hi[32], lo[32];
+            {
+                const uint8_t* xrow = smem_gen + kOffX + xs * kXStageBytes + row * 128;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    // 128-B swizzle: the 16-B chunk index is XORed with (row mod 8)
+                    const float4 v = *reinterpret_cast<const float4*>(xrow + ((j ^ (row & 7)) << 4));
+                    const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint32_t h = tf32_rna_bits(f[q]);
+                        hi[j * 4 + q] = h;
+                        lo[j * 4 + q] = tf32_rna_bits(f[q] - __uint_as_float(h));
+                    }
+                }
+            }
+            mbar_arrive(x_empty(xs));
+            if (++xs == kXStages) { xs = 0; xph ^= 1u; }
+            ok = __all_sync(0xffffffffu, mbar_wait(a_empty(as), aph ^ 1u, abort_flag));
+            if (!ok) continue;
+            tc_fence_after();
+            const uint32_t a_hi = tmem_lane + kAccCols + as * kAStageCols;
+            tmem_st32(a_hi, hi);
+            tmem_st32(a_hi + 32, lo);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(a_full(as));
+            if (++as == kAStages) { as = 0; aph ^= 1u; }
+        }
+
+        // epilogue
+        ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full, 0u, abort_flag));
+        tc_fence_after();
+        if (ok) {
+            const int64_t tok = tok0 + row;
+            for (int r = 0; r < nrows; ++r) {
+                uint32_t acc[32];
+                if ((touched >> r) & 1u) {
+                    tmem_ld32(tmem_lane + r * 32, acc);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[j] = 0u;
+                }
+                const int64_t col0 = ((int64_t)g * G + r) * 32;
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j4);
+                        acc[j4 * 4 + 0] = __float_as_uint(__uint_as_float(acc[j4 * 4 + 0]) + b.x);
+                        acc[j4 * 4 + 1] = __float_as_uint(__uint_as_float(acc[j4 * 4 + 1]) + b.y);
+                        acc[j4 * 4 + 2] = __float_as_uint(__uint_as_float(acc[j4 * 4 + 2]) + b.z);
+                        acc[j4 * 4 + 3] = __float_as_uint(__uint_as_float(acc[j4 * 4 + 3]) + b.w);
+                    }
+                }
+                if (tok < p.m) {
+                    if (!p.out_colmajor) {
+                        float4* dst = reinterpret_cast<float4*>(p.out + tok * p.n + col0);
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4)
+                            dst[j4] = make_float4(__uint_as_float(acc[j4 * 4 + 0]), __uint_as_float(acc[j4 * 4 + 1]),
+                                                  __uint_as_float(acc[j4 * 4 + 2]), __uint_as_float(acc[j4 * 4 + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) p.out[(col0 + j) * p.m + tok] = __uint_as_float(acc[j]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicOr(&g_device_status, 1u);
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// cuTensorMapEncodeTiled, resolved at run time so the library needs no link-time libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+}  // namespace
+
+cudaError_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
+                         uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
+                         CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {inner * elem_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,
+                            int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
+                            bool out_colmajor, cudaStream_t stream) {
+    if (precision != BSMM_PREC_TF32X3) return cudaErrorNotSupported;
+    if (m == 0 || n == 0) return cudaSuccess;
+    const int64_t n_out_blocks = n / 32;
+    const int64_t groups = plan_groups(n_out_blocks);
+    const int64_t tiles = (m + kTileTokens - 1) / kTileTokens;
+    if (groups * tiles > 0x7fffffffll || m > 0x7fffffffll) return cudaErrorInvalidValue;
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t err = cudaFuncSetAttribute(dsd_umma_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)kSmemBytes);
+        if (err != cudaSuccess) return err;
+        attr_set = true;
+    }
+
+    CUtensorMap tmap_a;
+    // k == 0 cannot be described by a tensor map; the plan is empty then and the map is never used
+    cudaError_t err = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)(k > 0 ? k : 32),
+                                   (uint64_t)m, 32, kTileTokens, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (err != cudaSuccess) return err;
+
+    DsdParams p;
+    const int64_t slot_bytes = packed_slot_bytes(BSMM_PREC_TF32X3);
+    p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * slot_bytes : 0);
+    p.group_off = static_cast<const int32_t*>(plan);
+    p.entries = reinterpret_cast<const PlanEntry*>(static_cast<const uint8_t*>(plan) + plan_entries_offset(n_out_blocks));
+    p.bias = bias;
+    p.out = static_cast<float*>(out);
+    p.m = m;
+    p.n = n;
+    p.n_out_blocks = (int32_t)n_out_blocks;
+    p.groups = (int32_t)groups;
+    p.out_colmajor = out_colmajor ? 1 : 0;
+    dsd_umma_tf32x3_kernel<<<(unsigned)(groups * tiles), kThreads, kSmemBytes, stream>>>(tmap_a, p);
+    return cudaGetLastError();
+}
+
+cudaError_t read_device_status(unsigned int* status, bool clear) {
+    cudaError_t err = cudaMemcpyFromSymbol(status, g_device_status, sizeof(unsigned int));
+    if (err != cudaSuccess) return err;
+    if (clear && *status != 0) {
+        const unsigned int zero = 0;
+        err = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(unsigned int));
+    }
+    return err;
+}
+
+int64_t sddmm_umma_workspace_bytes(int64_t, int64_t, int64_t, int64_t, uint32_t) { return 0; }
+
+cudaError_t launch_sddmm_umma(const void*, const void*, int64_t, int64_t, int64_t, float*, const int32_t*, int64_t,
+                              float*, void*, uint32_t, cudaStream_t) {
+    return cudaErrorNotSupported;
+}
+
+}  // namespace bsmm

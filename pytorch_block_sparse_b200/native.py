@@ -1,0 +1,233 @@
+"""ctypes binding of libbsmm_b200.so (declared in ``include/bsmm_b200.h``) plus the thin
+torch-facing helpers the matrix class uses.  torch only supplies device memory and the
+current stream here; every byte of arithmetic happens in the library's CUDA kernels.
+
+There is no CPU path: a missing library or a non-CUDA tensor raises.
+"""
+import ctypes
+import os
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libbsmm_b200.so")
+
+# mirrors include/bsmm_b200.h
+ABI_VERSION = 1
+OK = 0
+PREC_FP32_SIMT, PREC_TF32X3, PREC_BF16 = 0, 1, 2
+DSD_DGRAD, DSD_OUT_COLMAJOR = 0x10, 0x20
+SDDMM_A_COLMAJOR, SDDMM_B_COLMAJOR = 0x10, 0x20
+PLAN_GROUP = 8
+
+PRECISIONS = {"fp32": PREC_FP32_SIMT, "simt": PREC_FP32_SIMT, "tf32x3": PREC_TF32X3, "bf16": PREC_BF16}
+EXPORTS = (
+    "bsmm_abi_version",
+    "bsmm_status_string",
+    "bsmm_last_cuda_error",
+    "bsmm_device_status",
+    "bsmm_packed_bytes",
+    "bsmm_pack_weights",
+    "bsmm_plan_bytes",
+    "bsmm_build_plan",
+    "bsmm_dsd",
+    "bsmm_sddmm_workspace_bytes",
+    "bsmm_sddmm",
+)
+
+_lib = None
+_default_precision = os.environ.get("BSMM_PRECISION", "tf32x3")
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def load():
+    """dlopen the library once and declare the argument types of every export."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise NativeError(
+            "%s is missing: build it with `python -m pytorch_block_sparse_b200.build` "
+            "(this package has no CPU or PyTorch fallback)" % LIB_PATH
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    c = ctypes
+    vp, i64, u32, i32 = c.c_void_p, c.c_int64, c.c_uint32, c.c_int
+    lib.bsmm_abi_version.restype = i32
+    lib.bsmm_abi_version.argtypes = []
+    lib.bsmm_status_string.restype = c.c_char_p
+    lib.bsmm_status_string.argtypes = [i32]
+    lib.bsmm_last_cuda_error.restype = i32
+    lib.bsmm_last_cuda_error.argtypes = []
+    lib.bsmm_device_status.restype = i32
+    lib.bsmm_device_status.argtypes = [c.POINTER(c.c_uint), i32]
+    lib.bsmm_packed_bytes.restype = i64
+    lib.bsmm_packed_bytes.argtypes = [i64, u32]
+    lib.bsmm_pack_weights.restype = i32
+    lib.bsmm_pack_weights.argtypes = [vp, i64, u32, vp, vp, vp]
+    lib.bsmm_plan_bytes.restype = i64
+    lib.bsmm_plan_bytes.argtypes = [i64, i64]
+    lib.bsmm_build_plan.restype = i32
+    lib.bsmm_build_plan.argtypes = [vp, vp, i64, i64, vp, vp]
+    lib.bsmm_dsd.restype = i32
+    lib.bsmm_dsd.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, vp, u32, vp]
+    lib.bsmm_sddmm_workspace_bytes.restype = i64
+    lib.bsmm_sddmm_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
+    lib.bsmm_sddmm.restype = i32
+    lib.bsmm_sddmm.argtypes = [vp, vp, i64, i64, i64, vp, vp, i64, vp, vp, u32, vp]
+    if lib.bsmm_abi_version() != ABI_VERSION:
+        raise NativeError("libbsmm_b200.so has ABI %d, this package expects %d" % (lib.bsmm_abi_version(), ABI_VERSION))
+    _lib = lib
+    return lib
+
+
+def check(status, what):
+    if status != OK:
+        lib = load()
+        msg = lib.bsmm_status_string(status).decode()
+        extra = ""
+        if status == 3:
+            extra = " [cudaError_t=%d]" % lib.bsmm_last_cuda_error()
+        raise NativeError("%s failed: %s%s" % (what, msg, extra))
+
+
+def device_status(clear=True):
+    """Device health word (synchronizes): non-zero after a kernel abandoned a bounded wait."""
+    lib = load()
+    word = ctypes.c_uint(0)
+    check(lib.bsmm_device_status(ctypes.byref(word), 1 if clear else 0), "bsmm_device_status")
+    return word.value
+
+
+def set_default_precision(name):
+    """'tf32x3' (default; fp32-class accuracy on tensor cores), 'fp32' (CUDA-core FMA) or 'bf16'."""
+    global _default_precision
+    if name not in PRECISIONS:
+        raise ValueError("unknown precision %r, expected one of %s" % (name, sorted(PRECISIONS)))
+    _default_precision = name
+
+
+def resolve_precision(precision):
+    name = _default_precision if precision is None else precision
+    if name not in PRECISIONS:
+        raise ValueError("unknown precision %r, expected one of %s" % (name, sorted(PRECISIONS)))
+    return PRECISIONS[name]
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _need_cuda(t, name):
+    if not t.is_cuda:
+        raise NativeError("%s must be a CUDA tensor (got %s); there is no CPU path" % (name, t.device))
+
+
+class PackedWeights:
+    """Kernel-ready images of one ``data`` tensor + the fused per-slot sum of squares."""
+
+    def __init__(self, data, precision, images, block_sumsq):
+        self.data = data
+        self.precision = precision
+        self.images = images
+        self.block_sumsq = block_sumsq
+
+
+def pack_weights(data, precision):
+    """Run ``bsmm_pack_weights`` on ``data`` (fp32 ``[nnz*32, 32]``)."""
+    _need_cuda(data, "data")
+    lib = load()
+    nnz = data.shape[0] // 32
+    raw = data.detach()
+    sumsq = torch.empty(nnz, dtype=torch.float32, device=data.device)
+    nbytes = lib.bsmm_packed_bytes(nnz, precision)
+    images = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=data.device) if nbytes > 0 else None
+    with torch.cuda.device(data.device):
+        check(
+            lib.bsmm_pack_weights(_ptr(raw), nnz, precision, _ptr(images), _ptr(sumsq), _stream(data.device)),
+            "bsmm_pack_weights",
+        )
+    return PackedWeights(raw, precision, images, sumsq)
+
+
+class DsdPlan:
+    """Launch plan of the tensor-core dsd kernel for one (offsets, indices) pair."""
+
+    def __init__(self, ptr, idx):
+        _need_cuda(ptr, "ptr")
+        lib = load()
+        self.ptr = ptr
+        self.idx = idx
+        self.n_out_blocks = ptr.shape[0] - 1
+        self.nnz = idx.shape[0]
+        nbytes = lib.bsmm_plan_bytes(self.n_out_blocks, self.nnz)
+        self.buffer = torch.empty(nbytes, dtype=torch.uint8, device=ptr.device)
+        with torch.cuda.device(ptr.device):
+            check(
+                lib.bsmm_build_plan(
+                    _ptr(ptr), _ptr(idx), self.n_out_blocks, self.nnz, _ptr(self.buffer), _stream(ptr.device)
+                ),
+                "bsmm_build_plan",
+            )
+
+
+def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colmajor=False):
+    """``a @ W.T (+bias)`` (``transpose=True``) or ``a @ W`` through ``bsmm_dsd``.  ``a``: contiguous ``[m, k]``."""
+    _need_cuda(a, "dense_a")
+    lib = load()
+    m, k = a.shape
+    prec = packed.precision
+    want = torch.bfloat16 if prec == PREC_BF16 else torch.float32
+    if a.dtype != want:
+        a = a.to(want)
+    if out is None:
+        out = torch.empty((n_out, m) if out_colmajor else (m, n_out), dtype=want, device=a.device)
+    flags = prec | (0 if transpose else DSD_DGRAD) | (DSD_OUT_COLMAJOR if out_colmajor else 0)
+    if bias is not None and bias.dtype != torch.float32:
+        bias = bias.float()
+    with torch.cuda.device(a.device):
+        check(
+            lib.bsmm_dsd(
+                _ptr(a), m, k, _ptr(plan.ptr), _ptr(plan.idx), plan.nnz, _ptr(packed.data), _ptr(packed.images),
+                _ptr(plan.buffer), n_out, _ptr(out), _ptr(bias.detach() if bias is not None else None), flags,
+                _stream(a.device),
+            ),
+            "bsmm_dsd",
+        )
+    return out
+
+
+def sddmm(a, a_rowmajor, b, b_rowmajor, blocks, out, precision=None, block_sumsq=None):
+    """``out[s] = (a.T @ b)[block s]`` in ``data`` layout through ``bsmm_sddmm``.
+
+    ``a``: dY ``[tokens, rows]``, ``b``: X ``[tokens, cols]``; ``*_rowmajor`` False means the tensor's
+    transpose is the contiguous one."""
+    _need_cuda(a, "dense_a")
+    lib = load()
+    prec = resolve_precision(precision) if not isinstance(precision, int) else precision
+    tokens, rows = a.shape
+    cols = b.shape[1]
+    nnz = blocks.shape[0] // 2
+    flags = prec | (0 if a_rowmajor else SDDMM_A_COLMAJOR) | (0 if b_rowmajor else SDDMM_B_COLMAJOR)
+    if (not a_rowmajor or not b_rowmajor or a.dtype != torch.float32) and prec != PREC_FP32_SIMT:
+        # the tensor-core SDDMM takes token-major fp32 operands only
+        flags = (flags & ~0xF) | PREC_FP32_SIMT
+        a, b = a.float(), b.float()
+    ws_bytes = lib.bsmm_sddmm_workspace_bytes(rows, cols, tokens, nnz, flags)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes > 0 else None
+    with torch.cuda.device(a.device):
+        check(
+            lib.bsmm_sddmm(
+                _ptr(a), _ptr(b), rows, cols, tokens, _ptr(out), _ptr(blocks), nnz, _ptr(block_sumsq), _ptr(ws),
+                flags, _stream(a.device),
+            ),
+            "bsmm_sddmm",
+        )
+    return out
