@@ -43,6 +43,13 @@ class BlockSparseMatrixBase(torch.nn.Module):
         self._pack_cache = {}
         self.rebuild(block_mask, callback=False)
 
+    # derived, device-specific caches never travel with a pickle or a replica's state
+    def __getstate__(self):
+        state = dict(super().__getstate__() if hasattr(super(), "__getstate__") else self.__dict__)
+        state["_plan_cache"] = {}
+        state["_pack_cache"] = {}
+        return state
+
     # ------------------------------------------------------------------ hooks
     def updated_data(self):
         pass

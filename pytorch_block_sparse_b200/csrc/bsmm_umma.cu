@@ -59,6 +59,7 @@ struct DsdParams {
     int64_t m, n;
     int32_t n_out_blocks, groups;
     int32_t out_colmajor;
+    uint32_t x_bytes;          // bytes one activation-slab load delivers: min(128, m) rows of 128 B
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -113,7 +114,7 @@ dsd_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdPara
                 const PlanEntry ent = p.entries[e];
                 if (ent.flags & kPlanFirst) {
                     if (!mbar_wait(x_empty(xs), xph ^ 1u, abort_flag)) break;
-                    mbar_arrive_expect_tx(x_full(xs), kXStageBytes);
+                    mbar_arrive_expect_tx(x_full(xs), p.x_bytes);
                     tma_load_2d(smem_base + kOffX + xs * kXStageBytes, &tmap_a, ent.inner * 32, (int32_t)tok0,
                                 x_full(xs));
                     if (++xs == kXStages) { xs = 0; xph ^= 1u; }
@@ -306,18 +307,18 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     const int64_t tiles = (m + kTileTokens - 1) / kTileTokens;
     if (groups * tiles > 0x7fffffffll || m > 0x7fffffffll) return cudaErrorInvalidValue;
 
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t err = cudaFuncSetAttribute(dsd_umma_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)kSmemBytes);
-        if (err != cudaSuccess) return err;
-        attr_set = true;
-    }
+    // per call: the attribute is per device and the caller may switch devices
+    cudaError_t err = cudaFuncSetAttribute(dsd_umma_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)kSmemBytes);
+    if (err != cudaSuccess) return err;
 
+    if (k == 0) return cudaErrorInvalidValue;  // nothing to contract over; a tensor map cannot describe it
+    // The box never exceeds the tensor: with fewer than 128 tokens the slab load fills only the first
+    // m rows; the remaining tensor-memory lanes hold stale values whose outputs are never stored.
+    const uint32_t box_rows = (uint32_t)(m < kTileTokens ? m : kTileTokens);
     CUtensorMap tmap_a;
-    // k == 0 cannot be described by a tensor map; the plan is empty then and the map is never used
-    cudaError_t err = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)(k > 0 ? k : 32),
-                                   (uint64_t)m, 32, kTileTokens, CU_TENSOR_MAP_SWIZZLE_128B);
+    err = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)k, (uint64_t)m, 32, box_rows,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess) return err;
 
     DsdParams p;
@@ -332,6 +333,7 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     p.n_out_blocks = (int32_t)n_out_blocks;
     p.groups = (int32_t)groups;
     p.out_colmajor = out_colmajor ? 1 : 0;
+    p.x_bytes = box_rows * 128u;
     dsd_umma_tf32x3_kernel<<<(unsigned)(groups * tiles), kThreads, kSmemBytes, stream>>>(tmap_a, p);
     return cudaGetLastError();
 }

@@ -1,0 +1,168 @@
+"""GPU tests of the layer-level API: autograd through BlockSparseLinear against a dense masked
+twin (reference tests/test_linear_nn.py), checkpoint round trips (tests/test_save.py), model
+patching (tests/test_integration.py:37-64) and the sparsity optimizer (tests/test_sparse_optimizer.py)."""
+import io
+
+import numpy as np
+import pytest
+import torch
+
+from pytorch_block_sparse_b200 import (
+    BlockSparseLinear,
+    BlockSparseMatrix,
+    BlockSparseModelPatcher,
+    PseudoBlockSparseLinear,
+    SparseOptimizer,
+    native,
+)
+
+from .gpu_util import assert_device_healthy
+
+pytestmark = pytest.mark.gpu
+
+
+class DenseTwin(torch.nn.Module):
+    """nn.Linear whose weight is masked to the sparse layer's pattern every forward."""
+
+    def __init__(self, sparse):
+        super().__init__()
+        w = sparse.weight
+        self.weight = torch.nn.Parameter(w.to_dense().detach().clone())
+        self.register_buffer("mask", w.to_dense(data_replace=torch.ones_like(w.data)).detach())
+        self.bias = None if sparse.bias is None else torch.nn.Parameter(sparse.bias.detach().clone())
+
+    def forward(self, x):
+        return torch.nn.functional.linear(x, self.weight * self.mask, self.bias)
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32x3"])
+@pytest.mark.parametrize("bias", [True, False])
+def test_training_steps_match_dense_masked_twin(precision, bias):
+    # reference tests/test_linear_nn.py:58-134: output, dX and dW agree step after step under Adam
+    native.set_default_precision(precision)
+    try:
+        np.random.seed(0)
+        torch.manual_seed(0)
+        torch.backends.cuda.matmul.allow_tf32 = False
+        lin = BlockSparseLinear(256, 128, bias=bias, density=0.4)
+        with torch.no_grad():
+            lin.weight.data.mul_(0.05)
+            if bias:
+                lin.bias.normal_(0, 0.02)
+        twin = DenseTwin(lin).cuda()
+        opt_a = torch.optim.Adam(lin.parameters(), lr=1e-3)
+        opt_b = torch.optim.Adam(twin.parameters(), lr=1e-3)
+        for step in range(10):
+            x = torch.randn(8, 50, 256, device="cuda", requires_grad=True)
+            x2 = x.detach().clone().requires_grad_(True)
+            y, y2 = lin(x), twin(x2)
+            assert torch.allclose(y, y2, atol=1e-5, rtol=1e-4), (step, (y - y2).abs().max())
+            g = torch.randn_like(y)
+            opt_a.zero_grad()
+            opt_b.zero_grad()
+            y.backward(g)
+            y2.backward(g)
+            assert torch.allclose(x.grad, x2.grad, atol=1e-5, rtol=1e-4), step
+            dw = lin.weight.to_dense(data_replace=lin.weight.data.grad)
+            dw2 = twin.weight.grad * twin.mask
+            assert torch.allclose(dw, dw2, atol=2e-4, rtol=1e-4), (step, (dw - dw2).abs().max())
+            if bias:
+                assert torch.allclose(lin.bias.grad, twin.bias.grad, atol=1e-4, rtol=1e-4)
+            opt_a.step()
+            opt_b.step()
+        assert_device_healthy()
+    finally:
+        native.set_default_precision("tf32x3")
+
+
+def test_from_torch_linear_and_pseudo_layer():
+    np.random.seed(1)
+    torch.manual_seed(1)
+    dense = torch.nn.Linear(128, 64).cuda()
+    full = BlockSparseLinear(0, 0, False, torch_nn_linear=dense, density=1.0)
+    x = torch.randn(33, 128, device="cuda")
+    assert torch.allclose(full(x), dense(x), atol=1e-5)
+    half = BlockSparseLinear(0, 0, False, torch_nn_linear=dense, density=0.5)
+    assert half.block_count == 4 and half.weight.data.shape == (4 * 32, 32)
+    # density < 1 keeps the first nnz*1024 dense values, rescaled (reference block_sparse.py:345-350)
+    want = dense.weight.detach().flatten()[: 4 * 1024].reshape(128, 32) / np.sqrt(0.5)
+    assert torch.allclose(half.weight.data, want)
+    pseudo = PseudoBlockSparseLinear(half)
+    assert torch.allclose(pseudo(x), half(x), atol=1e-5)
+
+
+def test_save_and_load():
+    # reference tests/test_save.py:11-51
+    np.random.seed(2)
+    lin = BlockSparseLinear(64, 128, True, density=0.5)
+    x = torch.randn(10, 64, device="cuda")
+    y = lin(x)
+    keys = list(lin.state_dict().keys())
+    assert keys == ["bias", "weight.data", "weight.cols_a", "weight.row_start_ends_a", "weight.rows_b",
+                    "weight.col_start_ends_b", "weight.blocks"]
+    buf = io.BytesIO()
+    torch.save(lin.state_dict(), buf)
+    buf.seek(0)
+    np.random.seed(3)
+    other = BlockSparseLinear(64, 128, True, density=0.5)
+    assert not torch.allclose(other(x), y)
+    other.load_state_dict(torch.load(buf))
+    assert torch.equal(other(x), y)  # plans and packed weights were rebuilt from the loaded buffers
+    buf = io.BytesIO()
+    torch.save(lin, buf)
+    buf.seek(0)
+    assert torch.equal(torch.load(buf, weights_only=False)(x), y)
+
+
+def test_patcher_parameter_counts():
+    model = torch.nn.Sequential(torch.nn.Linear(128, 256), torch.nn.ReLU(), torch.nn.Linear(256, 64)).cuda()
+    before = sum(p.numel() for p in model.parameters())
+    mp = BlockSparseModelPatcher()
+    mp.add_pattern("0", {"density": 0.5})
+    mp.add_pattern("2", {"density": 0.25})
+    mp.patch_model(model)
+    after = sum(p.numel() for p in model.parameters())
+    assert isinstance(model[0], BlockSparseLinear) and isinstance(model[2], BlockSparseLinear)
+    assert before - after == 128 * 256 // 2 + 256 * 64 * 3 // 4
+    y = model(torch.randn(5, 128, device="cuda"))
+    y.sum().backward()
+    assert model[0].weight.data.grad.shape == model[0].weight.data.shape
+
+
+def test_sparse_optimizer_with_adam_on_gpu():
+    # reference tests/test_sparse_optimizer.py:57-90
+    np.random.seed(4)
+    torch.manual_seed(4)
+    lin = BlockSparseLinear(256, 256, True, density=0.5)
+    adam = torch.optim.Adam(lin.parameters(), lr=1e-3)
+    so = SparseOptimizer(SparseOptimizer.sparse_objects(lin), lr=0.25)
+    so.attach_optimizer(adam)
+    x = torch.randn(64, 256, device="cuda")
+    lin(x).square().mean().backward()
+    adam.step()
+    before = lin.weight.block_mask_build(None).clone()
+    so.step()
+    after = lin.weight.block_mask_build(None)
+    assert int((before != after).sum()) == 2 * int(0.25 * lin.block_count)
+    y = lin(x)  # the new pattern is picked up by fresh plans
+    dense = lin.weight.to_dense()
+    assert torch.allclose(y, x @ dense.t() + lin.bias, atol=1e-4)
+    assert_device_healthy()
+
+
+def test_data_parallel_forward():
+    # reference tests/test_data_parallel.py:11-17
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    lin = BlockSparseLinear(64, 128, False)
+    model = torch.nn.DataParallel(lin)
+    out = model(torch.randn(16, 64, device="cuda"))
+    assert out.shape == (16, 128)
+
+
+def test_nonsquare_block_shape_uses_emulator():
+    lin = BlockSparseLinear(64, 32, True, density=0.5, block_shape=(4, 8))
+    x = torch.randn(6, 64, device="cuda", requires_grad=True)
+    y = lin(x)
+    y.sum().backward()
+    assert torch.allclose(y, x @ lin.weight.to_dense().t() + lin.bias, atol=1e-5)
