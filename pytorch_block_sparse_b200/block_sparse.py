@@ -518,4 +518,6 @@ class BlockSparseMatrixEmulator(BlockSparseMatrixBase):
         return out if bias is None else out + bias
 
     def matmul_with_output_sparse_support(self, dense_a, dense_b, overwrite_data=False, precision=None):
-        return dense_a.t().mm(dense_b) * self._mask
+        a = dense_a.reshape(-1, dense_a.shape[-1])
+        b = dense_b.reshape(-1, dense_b.shape[-1])
+        return a.t().mm(b) * self._mask
