@@ -41,6 +41,7 @@ extern "C" {
 /* bsmm_dsd flags */
 #define BSMM_DSD_DGRAD 0x10u        /* 0: out = a * W^T (CSR given); 1: out = a * W (CSC given) */
 #define BSMM_DSD_OUT_COLMAJOR 0x20u /* 0: out is [m, n] row-major; 1: out is [n, m] (the reference's buffer) */
+#define BSMM_DSD_GROUP(g) (((uint32_t)(g)&0xFFu) << 8) /* group size the plan was built with (tensor-core precisions) */
 
 /* bsmm_sddmm flags */
 #define BSMM_SDDMM_A_COLMAJOR 0x10u /* dY given as [rows, tokens] contiguous instead of [tokens, rows] */
@@ -72,14 +73,17 @@ int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* 
                       bsmm_stream_t stream);
 
 /*
- * Per-pattern launch plan of the tensor-core dsd kernel: for every group of
- * BSMM_PLAN_GROUP consecutive output block-rows, the group's index entries re-ordered by
- * (inner block index, row-in-group).  `plan` must hold bsmm_plan_bytes(nnz) bytes.
- * Depends only on ptr/idx; rebuild after block_replace / load_state_dict.
+ * Per-pattern launch plan of the tensor-core dsd kernel: for every group of `group`
+ * consecutive output block-rows (group = 4, 6 or 8: the kernel's tile is 128 tokens x group*32
+ * columns), the group's index entries re-ordered by (inner block index, row-in-group), with the
+ * points at which the kernel promotes its tensor-memory partial sums.  `plan` must hold
+ * bsmm_plan_bytes(n_out_blocks, nnz, group) bytes, 16-byte aligned.  Depends only on ptr/idx
+ * (each row's entries in ascending inner index, as the reference builds them); rebuild after
+ * block_replace / load_state_dict.  bsmm_plan_group suggests a group size for a problem shape.
  */
-#define BSMM_PLAN_GROUP 8
-int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz);
-int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, void* plan,
+int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz);
+int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz, int group);
+int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, int group, void* plan,
                     bsmm_stream_t stream);
 
 /*

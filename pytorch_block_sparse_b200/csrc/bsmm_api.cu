@@ -58,18 +58,32 @@ int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* 
     return cuda_status(bsmm::launch_pack(data, nnz, precision, packed, block_sumsq, s));
 }
 
-int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz) {
-    if (n_out_blocks < 0 || nnz < 0) return -1;
-    return bsmm::plan_bytes(n_out_blocks, nnz);
+int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz) {
+    (void)nnz;
+    if (m <= 0 || n_out_blocks <= 0) return 8;
+    // The widest tile re-uses each activation slab most; narrower tiles are only worth it when the
+    // wide one would leave most of the 148 SMs without a CTA.
+    const int64_t tiles = (m + 127) / 128;
+    for (int g : {8, 6, 4}) {
+        if (tiles * ((n_out_blocks + g - 1) / g) >= 148) return g;
+    }
+    return 4;
 }
 
-int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, void* plan,
+int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz, int group) {
+    if (n_out_blocks < 0 || nnz < 0 || !bsmm::plan_group_valid(group)) return -1;
+    return bsmm::plan_bytes(n_out_blocks, nnz, group);
+}
+
+int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, int group, void* plan,
                     bsmm_stream_t stream) {
     if (n_out_blocks < 0 || nnz < 0 || ptr == nullptr || plan == nullptr || (nnz > 0 && idx == nullptr))
         return BSMM_ERR_INVALID_ARGUMENT;
+    if (!bsmm::plan_group_valid(group)) return BSMM_ERR_INVALID_ARGUMENT;
     if (!aligned(plan, 16) || !aligned(idx, 8)) return BSMM_ERR_INVALID_ARGUMENT;
     if (nnz > 0x7fffffff || n_out_blocks > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
-    return cuda_status(bsmm::launch_build_plan(ptr, idx, n_out_blocks, nnz, plan, static_cast<cudaStream_t>(stream)));
+    return cuda_status(
+        bsmm::launch_build_plan(ptr, idx, n_out_blocks, nnz, group, plan, static_cast<cudaStream_t>(stream)));
 }
 
 int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
@@ -93,9 +107,14 @@ int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int3
                                                  static_cast<float*>(out), bias, dgrad, colmajor, s));
     }
     if (precision == BSMM_PREC_TF32X3 || precision == BSMM_PREC_BF16) {
-        if (packed == nullptr || plan == nullptr || !aligned(packed, 256) || !aligned(plan, 16))
+        if (k == 0 || nnz == 0)  // nothing to contract: the CUDA-core kernel writes the zeros (+bias)
+            return cuda_status(bsmm::launch_dsd_simt(static_cast<const float*>(a), m, k, ptr, idx, data, n,
+                                                     static_cast<float*>(out), bias, dgrad, colmajor, s));
+        const int group = (int)((flags >> 8) & 0xFFu);
+        if (packed == nullptr || plan == nullptr || !aligned(packed, 256) || !aligned(plan, 16) ||
+            !bsmm::plan_group_valid(group))
             return BSMM_ERR_INVALID_ARGUMENT;
-        return cuda_status(bsmm::launch_dsd_umma(a, m, k, nnz, packed, plan, n, out, bias, precision, dgrad,
+        return cuda_status(bsmm::launch_dsd_umma(a, m, k, nnz, packed, plan, group, n, out, bias, precision, dgrad,
                                                  colmajor, s));
     }
     return BSMM_ERR_UNSUPPORTED;

@@ -1,6 +1,6 @@
 // Launch-plan builder for the tensor-core dsd kernel.
 //
-// The kernel owns a tile of 128 tokens x BSMM_PLAN_GROUP output block-rows and walks the
+// The kernel owns a tile of 128 tokens x `group` (4, 6 or 8) output block-rows and walks the
 // contraction axis one 32-wide activation slab at a time, so it wants the group's blocks merged
 // across its rows and ordered by slab.  The CSR/CSC arrays of the reference
 // (block_sparse.py:85-153) list each row's blocks in ascending inner index; the merged position of
@@ -10,12 +10,12 @@
 namespace bsmm {
 namespace {
 
-constexpr int G = BSMM_PLAN_GROUP;
+constexpr int kMaxGroup = 8;
 
 __global__ void __launch_bounds__(128)
-build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx, int n_out_blocks,
+build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx, int n_out_blocks, int G,
                   int32_t* __restrict__ group_off, PlanEntry* __restrict__ entries) {
-    __shared__ int rp[G + 1];
+    __shared__ int rp[kMaxGroup + 1];
     const int g = blockIdx.x;
     const int r0 = g * G;
     const int nrows = min(G, n_out_blocks - r0);
@@ -48,22 +48,27 @@ build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx,
         pe.inner = ent.x;
         pe.slot = ent.y;
         pe.row = r;
-        pe.flags = (before ? 0 : kPlanFirst) | (after ? 0 : kPlanLast);
+        // promote the row's partial sum after every kDrainEvery-th block of the row and after its last one
+        const int ord = e - rp[r];
+        const bool drain = ((ord + 1) % kDrainEvery) == 0 || e + 1 == rp[r + 1];
+        pe.flags = (before ? 0 : kPlanFirst) | (after ? 0 : kPlanLast) | (drain ? kPlanDrain : 0);
         entries[base + rank] = pe;
     }
 }
 
 }  // namespace
 
-cudaError_t launch_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, void* plan,
-                              cudaStream_t stream) {
+cudaError_t launch_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, int group,
+                              void* plan, cudaStream_t stream) {
     (void)nnz;
-    const int64_t groups = plan_groups(n_out_blocks);
+    if (!plan_group_valid(group)) return cudaErrorInvalidValue;
+    const int64_t groups = plan_groups(n_out_blocks, group);
     if (groups == 0) return cudaSuccess;
     int32_t* group_off = static_cast<int32_t*>(plan);
-    PlanEntry* entries = reinterpret_cast<PlanEntry*>(static_cast<uint8_t*>(plan) + plan_entries_offset(n_out_blocks));
+    PlanEntry* entries =
+        reinterpret_cast<PlanEntry*>(static_cast<uint8_t*>(plan) + plan_entries_offset(n_out_blocks, group));
     build_plan_kernel<<<(unsigned)groups, 128, 0, stream>>>(ptr, reinterpret_cast<const int2*>(idx), (int)n_out_blocks,
-                                                            group_off, entries);
+                                                            group, group_off, entries);
     return cudaGetLastError();
 }
 

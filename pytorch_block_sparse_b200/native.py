@@ -18,7 +18,6 @@ OK = 0
 PREC_FP32_SIMT, PREC_TF32X3, PREC_BF16 = 0, 1, 2
 DSD_DGRAD, DSD_OUT_COLMAJOR = 0x10, 0x20
 SDDMM_A_COLMAJOR, SDDMM_B_COLMAJOR = 0x10, 0x20
-PLAN_GROUP = 8
 
 PRECISIONS = {"fp32": PREC_FP32_SIMT, "simt": PREC_FP32_SIMT, "tf32x3": PREC_TF32X3, "bf16": PREC_BF16}
 EXPORTS = (
@@ -28,6 +27,7 @@ EXPORTS = (
     "bsmm_device_status",
     "bsmm_packed_bytes",
     "bsmm_pack_weights",
+    "bsmm_plan_group",
     "bsmm_plan_bytes",
     "bsmm_build_plan",
     "bsmm_dsd",
@@ -68,10 +68,12 @@ def load():
     lib.bsmm_packed_bytes.argtypes = [i64, u32]
     lib.bsmm_pack_weights.restype = i32
     lib.bsmm_pack_weights.argtypes = [vp, i64, u32, vp, vp, vp]
+    lib.bsmm_plan_group.restype = i32
+    lib.bsmm_plan_group.argtypes = [i64, i64, i64]
     lib.bsmm_plan_bytes.restype = i64
-    lib.bsmm_plan_bytes.argtypes = [i64, i64]
+    lib.bsmm_plan_bytes.argtypes = [i64, i64, i32]
     lib.bsmm_build_plan.restype = i32
-    lib.bsmm_build_plan.argtypes = [vp, vp, i64, i64, vp, vp]
+    lib.bsmm_build_plan.argtypes = [vp, vp, i64, i64, i32, vp, vp]
     lib.bsmm_dsd.restype = i32
     lib.bsmm_dsd.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, vp, u32, vp]
     lib.bsmm_sddmm_workspace_bytes.restype = i64
@@ -158,24 +160,42 @@ def pack_weights(data, precision):
 
 
 class DsdPlan:
-    """Launch plan of the tensor-core dsd kernel for one (offsets, indices) pair."""
+    """Launch plans of the tensor-core dsd kernel for one (offsets, indices) pair, one per group size
+    (the kernel's tile is 128 tokens x group*32 columns; the group is chosen from the token count)."""
 
     def __init__(self, ptr, idx):
         _need_cuda(ptr, "ptr")
-        lib = load()
+        load()
         self.ptr = ptr
         self.idx = idx
         self.n_out_blocks = ptr.shape[0] - 1
         self.nnz = idx.shape[0]
-        nbytes = lib.bsmm_plan_bytes(self.n_out_blocks, self.nnz)
-        self.buffer = torch.empty(nbytes, dtype=torch.uint8, device=ptr.device)
-        with torch.cuda.device(ptr.device):
-            check(
-                lib.bsmm_build_plan(
-                    _ptr(ptr), _ptr(idx), self.n_out_blocks, self.nnz, _ptr(self.buffer), _stream(ptr.device)
-                ),
-                "bsmm_build_plan",
-            )
+        self._buffers = {}
+
+    def group_for(self, m):
+        forced = os.environ.get("BSMM_PLAN_GROUP")
+        if forced:
+            return int(forced)
+        return load().bsmm_plan_group(m, self.n_out_blocks, self.nnz)
+
+    def buffer(self, group):
+        buf = self._buffers.get(group)
+        if buf is None:
+            lib = load()
+            nbytes = lib.bsmm_plan_bytes(self.n_out_blocks, self.nnz, group)
+            if nbytes < 0:
+                raise NativeError("invalid plan group %r" % (group,))
+            buf = torch.empty(nbytes, dtype=torch.uint8, device=self.ptr.device)
+            with torch.cuda.device(self.ptr.device):
+                check(
+                    lib.bsmm_build_plan(
+                        _ptr(self.ptr), _ptr(self.idx), self.n_out_blocks, self.nnz, group, _ptr(buf),
+                        _stream(self.ptr.device),
+                    ),
+                    "bsmm_build_plan",
+                )
+            self._buffers[group] = buf
+        return buf
 
 
 def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colmajor=False):
@@ -190,13 +210,18 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
     if out is None:
         out = torch.empty((n_out, m) if out_colmajor else (m, n_out), dtype=want, device=a.device)
     flags = prec | (0 if transpose else DSD_DGRAD) | (DSD_OUT_COLMAJOR if out_colmajor else 0)
+    plan_buf = None
+    if prec != PREC_FP32_SIMT:
+        group = plan.group_for(m)
+        plan_buf = plan.buffer(group)
+        flags |= group << 8
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
     with torch.cuda.device(a.device):
         check(
             lib.bsmm_dsd(
                 _ptr(a), m, k, _ptr(plan.ptr), _ptr(plan.idx), plan.nnz, _ptr(packed.data), _ptr(packed.images),
-                _ptr(plan.buffer), n_out, _ptr(out), _ptr(bias.detach() if bias is not None else None), flags,
+                _ptr(plan_buf), n_out, _ptr(out), _ptr(bias.detach() if bias is not None else None), flags,
                 _stream(a.device),
             ),
             "bsmm_dsd",

@@ -40,7 +40,11 @@ def test_size_queries():
     assert lib.bsmm_packed_bytes(10, native.PREC_BF16) == 2 * 10 * 2048
     assert lib.bsmm_packed_bytes(10, native.PREC_FP32_SIMT) == 0
     assert lib.bsmm_packed_bytes(-1, native.PREC_TF32X3) == -1
-    assert lib.bsmm_plan_bytes(16, 100) == 16 + 100 * 16
+    assert lib.bsmm_plan_bytes(16, 100, 8) == 16 + 100 * 16
+    assert lib.bsmm_plan_bytes(16, 100, 4) == 32 + 100 * 16
+    assert lib.bsmm_plan_bytes(16, 100, 5) == -1
+    assert lib.bsmm_plan_group(16384, 128, 4096) == 8
+    assert lib.bsmm_plan_group(128, 24, 288) == 4
     assert lib.bsmm_sddmm_workspace_bytes(64, 64, 100, 2, native.PREC_FP32_SIMT) == 0
 
 
@@ -52,8 +56,9 @@ def test_argument_validation_without_device():
     assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, null, null, 33, fake, null, 0, null) == 1
     # null output
     assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, null, null, 32, null, null, 0, null) == 1
-    # tensor-core precision without packed images / plan
-    assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, null, null, 32, fake, null, native.PREC_TF32X3, null) == 1
+    # tensor-core precision without packed images / plan, or without the plan's group size in the flags
+    assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, null, null, 32, fake, null, native.PREC_TF32X3 | (8 << 8), null) == 1
+    assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, fake, fake, 32, fake, null, native.PREC_TF32X3, null) == 1
     # bias with dgrad
     assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, null, null, 32, fake, fake, native.DSD_DGRAD, null) == 2
     # empty problem is a no-op
@@ -62,4 +67,5 @@ def test_argument_validation_without_device():
     assert lib.bsmm_sddmm(ctypes.c_void_p(0x1004), fake, 32, 32, 8, fake, fake, 1, null, null, 0, null) == 1
     assert lib.bsmm_sddmm(fake, fake, 48, 32, 8, fake, fake, 1, null, null, 0, null) == 1
     assert lib.bsmm_pack_weights(null, 3, native.PREC_TF32X3, fake, null, null) == 1
-    assert lib.bsmm_build_plan(null, fake, 4, 4, fake, null) == 1
+    assert lib.bsmm_build_plan(null, fake, 4, 4, 8, fake, null) == 1
+    assert lib.bsmm_build_plan(fake, fake, 4, 4, 7, fake, null) == 1

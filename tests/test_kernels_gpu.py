@@ -219,27 +219,60 @@ def test_pack_statistic_matches_block_norm():
         assert np.allclose(got, want, rtol=1e-5)
 
 
-def test_plan_is_the_group_merge_of_the_csr():
-    m = make_matrix((512, 384), n_blocks=60, seed=8)
+@pytest.mark.parametrize("group", [4, 6, 8])
+def test_plan_is_the_group_merge_of_the_csr(group):
+    m = make_matrix((512, 384), n_blocks=110, seed=8)
     plan = m._plan(True)
+    raw = plan.buffer(group)
     torch.cuda.synchronize()
-    raw = plan.buffer.cpu().numpy()
-    groups = (16 + 7) // 8
+    raw = raw.cpu().numpy()
+    groups = (16 + group - 1) // group
     off = raw[: (groups + 1) * 4].view(np.int32)
     ent_off = ((groups + 1) * 4 + 15) // 16 * 16
     ent = raw[ent_off: ent_off + plan.nnz * 16].view(np.int32).reshape(-1, 4)
     ptr = m.row_start_ends_a.cpu().numpy()
     idx = m.cols_a.cpu().numpy()
     for g in range(groups):
-        rows = range(g * 8, min(16, g * 8 + 8))
-        want = sorted((int(idx[e, 0]), r - g * 8, int(idx[e, 1])) for r in rows for e in range(ptr[r], ptr[r + 1]))
-        assert off[g] == ptr[g * 8]
+        rows = range(g * group, min(16, g * group + group))
+        want = sorted((int(idx[e, 0]), r - g * group, int(idx[e, 1])) for r in rows for e in range(ptr[r], ptr[r + 1]))
+        assert off[g] == ptr[g * group]
         got = ent[off[g]: off[g + 1]]
         assert [(int(c), int(r), int(s)) for c, s, r, _ in got] == want
+        seen = {}
         for i, (c, s, r, flags) in enumerate(got):
             first = i == 0 or got[i - 1][0] != c
             last = i == len(got) - 1 or got[i + 1][0] != c
-            assert flags == (1 if first else 0) | (2 if last else 0)
+            seen[r] = seen.get(r, 0) + 1
+            row_len = ptr[g * group + r + 1] - ptr[g * group + r]
+            drain = seen[r] % 8 == 0 or seen[r] == row_len  # promotion every 8 blocks of a row and at its end
+            assert flags == (1 if first else 0) | (2 if last else 0) | (4 if drain else 0)
+
+
+@pytest.mark.parametrize("group", ["4", "6", "8"])
+def test_dsd_every_tile_width(group, monkeypatch):
+    monkeypatch.setenv("BSMM_PLAN_GROUP", group)
+    m = make_matrix((416, 352), n_blocks=70, seed=21)  # 13 x 11 blocks: ragged last group for every width
+    x = randn((333, 352), seed=22)
+    dy = randn((333, 416), seed=23)
+    bias = randn((416,), seed=24)
+    check(run_dsd(m, x, True, "tf32x3", bias), oracle_dsd(m, x, True, bias), "tf32x3", "fwd")
+    check(run_dsd(m, dy, False, "tf32x3"), oracle_dsd(m, dy, False), "tf32x3", "dgrad")
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_dsd_long_rows_stay_within_the_error_bound(precision):
+    """96 blocks per output row (K = 4096 at density 0.75): the tensor-core accumulator alone would drift
+    past 1e-5 here; the periodic promotion to an fp32 master tile keeps the error at the CUDA-core level."""
+    m = make_matrix((256, 4096), n_blocks=int(0.75 * 8 * 128), seed=31)
+    x = randn((256, 4096), seed=32)
+    err = check(run_dsd(m, x, True, precision), oracle_dsd(m, x, True), precision, "fwd")
+    assert err < 4e-6, err
+    m2 = make_matrix((4096, 256), n_blocks=int(0.75 * 8 * 128), seed=33)
+    dy = randn((256, 4096), seed=34)
+    err = check(run_dsd(m2, dy, False, precision), oracle_dsd(m2, dy, False), precision, "dgrad")
+    assert err < 4e-6, err
+    assert_device_healthy()
 
 
 def test_missing_cuda_tensor_is_rejected():
