@@ -1,0 +1,484 @@
+// Tensor-core dense^T x dense -> block-sparse kernel (the wgrad of one block-sparse Linear) for
+// sm_100a; replaces the reference's cutlass::gemm::kernel<block_task_back>
+// (cutlass/gemm/dispatch_back.h:186-218, block_task_back.h:643-707).
+//
+//   out[slot][c][r] = sum over tokens t of X[t, C*32 + c] * dY[t, R*32 + r]
+//
+// A CTA owns one "item": up to 32 blocks of ONE block-row R (a CSR row segment) and one range of
+// tokens.  Four blocks of the row form a chunk and fill the 128 rows of one MMA:
+//   D[128 = 4 blocks x 32 c, 32 = r] += A[128 x K] * B[32 x K]^T,   K = tokens, 8 per instruction,
+// A = the four blocks' X slabs, transposed on the way into tensor memory (lane = feature c, column =
+// token), B = the dY slab of row R, shared by every chunk of the item.  D is already the block's
+// storage layout (row c holds 32 consecutive r), so the epilogue writes plain 128-byte rows.
+//
+//   warp 0    producer : TMA tensor loads of [32 tokens x 32 features] fp32 boxes: one dY slab per
+//                        step, four X slabs per chunk
+//   warps 2-5 transform: per step the dY slab -> tf32 hi/lo operand images in shared memory (K-major,
+//                        un-swizzled); per chunk the X slabs, read column-wise, split hi/lo, tcgen05.st
+//   warp 1    MMA      : per chunk and step 4 k-steps x 3 passes of tcgen05.mma kind::tf32 M=128 N=32 K=8
+//   warps 6-9 drain    : every 256 tokens tcgen05.ld each chunk's partial sum and add it (fp32, round to
+//                        nearest) to the chunk's master tile in shared memory; final store to global
+//
+// The promotion bounds the tensor core's systematic accumulate error (about 2e-8 relative per MMA).
+// Token ranges (grid.y > 1) write partial results to the workspace; a second kernel sums them in a
+// fixed order (deterministic, no atomics) and produces the per-slot sum of squares.
+#include "bsmm_ptx.cuh"
+#include "bsmm_umma.cuh"
+
+namespace bsmm {
+namespace {
+
+using namespace ptx;
+
+constexpr int kChunks = 8;                 // chunks (of 4 blocks) per item
+constexpr int kItemBlocks = 4 * kChunks;   // 32
+constexpr int kStepTokens = 32;
+constexpr int kDrainSteps = 8;             // promote every 256 tokens: 96 MMAs per partial sum
+constexpr uint32_t kSlabBytes = 32 * 32 * 4;            // 4 KiB: [32 tokens][32 features]
+constexpr uint32_t kXStageBytes = 4 * kSlabBytes;       // one chunk's X slabs
+constexpr uint32_t kBImgBytes = 2 * kImage32Bytes;      // hi + lo images of the dY slab
+constexpr uint32_t kMasterBytes = 128 * 32 * 4;         // 16 KiB per chunk
+constexpr int kXStages = 4, kDyStages = 2, kBStages = 2, kAStages = 4;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccCols = kChunks * 32;             // 256
+constexpr uint32_t kAStageCols = 64;
+constexpr int kThreads = 320;
+
+constexpr uint32_t kOffMaster = 0;
+constexpr uint32_t kOffX = kOffMaster + kChunks * kMasterBytes;
+constexpr uint32_t kOffDy = kOffX + kXStages * kXStageBytes;
+constexpr uint32_t kOffBImg = kOffDy + kDyStages * kSlabBytes;
+constexpr uint32_t kOffBar = kOffBImg + kBStages * kBImgBytes;
+constexpr int kNumBars = 2 * kXStages + 2 * kDyStages + 2 * kBStages + 2 * kAStages + 2 * kChunks;
+constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
+constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
+static_assert(kAccCols + kAStages * kAStageCols <= kTmemCols, "tensor memory over-subscribed");
+
+// Item table: [0] = item count; item i at int32 offsets 4 + 4*i: {block-row, first CSR entry, blocks, 0}
+struct SddmmParams {
+    const int32_t* items;
+    const int2* idx;       // CSR entries: (block-col, slot)
+    float* out;            // sparse_c, or the workspace when the token axis is split
+    float* block_sumsq;    // may be null; only written when the token axis is not split
+    unsigned int* status;
+    int64_t tokens;
+    int64_t tokens_per_split;  // multiple of kStepTokens * kDrainSteps
+    int64_t split_stride;      // floats between two splits' partial results
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
+                         const SddmmParams p) {
+    const int n_items = p.items[0];
+    if ((int)blockIdx.x >= n_items) return;
+    const int4 item = reinterpret_cast<const int4*>(p.items + 4)[blockIdx.x];
+    const int brow = item.x, ent0 = item.y, nblk = item.z;
+    const int nchunks = (nblk + 3) >> 2;
+    const int64_t t_begin = (int64_t)blockIdx.y * p.tokens_per_split;
+    const int64_t t_end = min(p.tokens, t_begin + p.tokens_per_split);
+    const int nsteps = (int)((t_end - t_begin + kStepTokens - 1) / kStepTokens);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar0 = smem_base + kOffBar;
+    auto x_full = [&](int s) { return bar0 + 8u * s; };
+    auto x_empty = [&](int s) { return bar0 + 8u * (kXStages + s); };
+    auto dy_full = [&](int s) { return bar0 + 8u * (2 * kXStages + s); };
+    auto dy_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + kDyStages + s); };
+    auto b_full = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + s); };
+    auto b_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + kBStages + s); };
+    auto a_full = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + 2 * kBStages + s); };
+    auto a_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + 2 * kBStages + kAStages + s); };
+    auto p_ready = [&](int c) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + 2 * kBStages + 2 * kAStages + c); };
+    auto p_taken = [&](int c) {
+        return bar0 + 8u * (2 * kXStages + 2 * kDyStages + 2 * kBStages + 2 * kAStages + kChunks + c);
+    };
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + kOffMisc);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kXStages; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); }
+        for (int s = 0; s < kDyStages; ++s) { mbar_init(dy_full(s), 1); mbar_init(dy_empty(s), 128); }
+        for (int s = 0; s < kBStages; ++s) { mbar_init(b_full(s), 128); mbar_init(b_empty(s), 1); }
+        for (int s = 0; s < kAStages; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), 1); }
+        for (int c = 0; c < kChunks; ++c) { mbar_init(p_ready(c), 1); mbar_init(p_taken(c), 128); }
+        misc[1] = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_base + kOffMisc, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = misc[0];
+    volatile uint32_t* abort_flag = &misc[1];
+
+    // a step is a promotion point when it closes a 256-token segment or the token range
+    auto drain_step = [&](int step) { return ((step + 1) % kDrainSteps) == 0 || step + 1 == nsteps; };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            int xs = 0, ds = 0;
+            uint32_t xph = 0, dph = 0;
+            bool ok = true;
+            for (int step = 0; step < nsteps && ok; ++step) {
+                const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
+                if (!mbar_wait(dy_empty(ds), dph ^ 1u, abort_flag)) break;
+                mbar_arrive_expect_tx(dy_full(ds), kSlabBytes);
+                tma_load_2d(smem_base + kOffDy + ds * kSlabBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
+                if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
+                for (int ch = 0; ch < nchunks; ++ch) {
+                    const int nb = min(4, nblk - ch * 4);
+                    if (!mbar_wait(x_empty(xs), xph ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
+                    for (int j = 0; j < nb; ++j) {
+                        const int bcol = p.idx[ent0 + ch * 4 + j].x;
+                        tma_load_2d(smem_base + kOffX + xs * kXStageBytes + j * kSlabBytes, &tmap_x, bcol * 32, tok,
+                                    x_full(xs));
+                    }
+                    if (++xs == kXStages) { xs = 0; xph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(2u, 128u, 32u, false, false);
+            int bs = 0, as = 0;
+            uint32_t bph = 0, aph = 0;
+            uint32_t pending = 0, taken_ph = 0;
+            bool ok = true;
+            for (int step = 0; step < nsteps && ok; ++step) {
+                if (!mbar_wait(b_full(bs), bph, abort_flag)) break;
+                const uint32_t b_addr = smem_base + kOffBImg + bs * kBImgBytes;
+                const uint64_t b_hi = smem_desc_noswizzle(b_addr, 512, 128);
+                const uint64_t b_lo = smem_desc_noswizzle(b_addr + kImage32Bytes, 512, 128);
+                const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites P
+                const bool drain = drain_step(step);
+                for (int ch = 0; ch < nchunks; ++ch) {
+                    if (!mbar_wait(a_full(as), aph, abort_flag)) { ok = false; break; }
+                    if (fresh && ((pending >> ch) & 1u)) {
+                        if (!mbar_wait(p_taken(ch), (taken_ph >> ch) & 1u, abort_flag)) { ok = false; break; }
+                        taken_ph ^= 1u << ch;
+                        pending &= ~(1u << ch);
+                    }
+                    tc_fence_after();
+                    const uint32_t a_hi = tmem + kAccCols + as * kAStageCols;
+                    const uint32_t d = tmem + ch * 32;
+                    uint32_t accumulate = fresh ? 0u : 1u;
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        const uint64_t koff = (uint64_t)((s * 1024) >> 4);
+                        mma_ts_tf32(d, a_hi + 32 + s * 8, b_hi + koff, idesc, accumulate);  // lo * hi
+                        mma_ts_tf32(d, a_hi + s * 8, b_lo + koff, idesc, 1u);               // hi * lo
+                        mma_ts_tf32(d, a_hi + s * 8, b_hi + koff, idesc, 1u);               // hi * hi
+                        accumulate = 1u;
+                    }
+                    mma_commit(a_empty(as));
+                    if (++as == kAStages) { as = 0; aph ^= 1u; }
+                    if (drain) {
+                        mma_commit(p_ready(ch));
+                        pending |= 1u << ch;
+                    }
+                }
+                mma_commit(b_empty(bs));
+                if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------------ transform
+        const int quarter = warp & 3;  // block position inside the chunk = tensor-memory lane quarter
+        const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        const int tt = (warp - 2) * 32 + lane;  // 0..127 over the four transform warps
+        int xs = 0, ds = 0, bs = 0, as = 0;
+        uint32_t xph = 0, dph = 0, bph = 0, aph = 0;
+        bool ok = true;
+        for (int step = 0; step < nsteps && ok; ++step) {
+            // dY slab [32 tokens][32 r] -> B operand images B[n = r][k = token], hi and lo
+            ok = __all_sync(0xffffffffu, mbar_wait(dy_full(ds), dph, abort_flag));
+            if (!ok) break;
+            ok = __all_sync(0xffffffffu, mbar_wait(b_empty(bs), bph ^ 1u, abort_flag));
+            if (!ok) break;
+            {
+                const int kk = tt >> 2;          // token of the step
+                const int r0 = (tt & 3) * 8;     // eight features
+                const float* src = reinterpret_cast<const float*>(smem_gen + kOffDy + ds * kSlabBytes) + kk * 32 + r0;
+                const float4 v0 = *reinterpret_cast<const float4*>(src);
+                const float4 v1 = *reinterpret_cast<const float4*>(src + 4);
+                const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                uint8_t* img = smem_gen + kOffBImg + bs * kBImgBytes;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t off = image32_offset((uint32_t)(r0 + i), (uint32_t)kk);
+                    const uint32_t h = tf32_rna_bits(f[i]);
+                    *reinterpret_cast<uint32_t*>(img + off) = h;
+                    *reinterpret_cast<uint32_t*>(img + kImage32Bytes + off) = tf32_rna_bits(f[i] - __uint_as_float(h));
+                }
+            }
+            fence_proxy_async_smem();  // generic-proxy writes, read by the MMA through the async proxy
+            mbar_arrive(b_full(bs));
+            mbar_arrive(dy_empty(ds));
+            if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+            if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
+
+            for (int ch = 0; ch < nchunks; ++ch) {
+                const int nb = min(4, nblk - ch * 4);
+                ok = __all_sync(0xffffffffu, mbar_wait(x_full(xs), xph, abort_flag));
+                if (!ok) break;
+                uint32_t hi[32], lo[32];
+                if (quarter < nb) {
+                    // column `lane` of this quarter's slab: one feature, 32 tokens
+                    const float* col = reinterpret_cast<const float*>(smem_gen + kOffX + xs * kXStageBytes +
+                                                                      quarter * kSlabBytes) + lane;
+#pragma unroll
+                    for (int kk = 0; kk < 32; ++kk) {
+                        const float f = col[kk * 32];
+                        const uint32_t h = tf32_rna_bits(f);
+                        hi[kk] = h;
+                        lo[kk] = tf32_rna_bits(f - __uint_as_float(h));
+                    }
+                } else {
+#pragma unroll
+                    for (int kk = 0; kk < 32; ++kk) { hi[kk] = 0u; lo[kk] = 0u; }
+                }
+                mbar_arrive(x_empty(xs));
+                if (++xs == kXStages) { xs = 0; xph ^= 1u; }
+                ok = __all_sync(0xffffffffu, mbar_wait(a_empty(as), aph ^ 1u, abort_flag));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_hi = tmem_lane + kAccCols + as * kAStageCols;
+                tmem_st32(a_hi, hi);
+                tmem_st32(a_hi + 32, lo);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(a_full(as));
+                if (++as == kAStages) { as = 0; aph ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ drain + epilogue
+        const int quarter = warp & 3;
+        const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        // this thread's row (feature c = lane of block `quarter`) of chunk ch's master tile
+        float* master = reinterpret_cast<float*>(smem_gen + kOffMaster) + (quarter * 32 + lane) * 32;
+        const int swz = lane & 7;  // rotate 16-B chunks by the row so that a warp's accesses spread over banks
+        for (int ch = 0; ch < nchunks; ++ch)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<float4*>(master + ch * (kMasterBytes / 4) + ((j ^ swz) << 2)) =
+                    make_float4(0.f, 0.f, 0.f, 0.f);
+
+        uint32_t ready_ph = 0;
+        bool ok = true;
+        for (int step = 0; step < nsteps && ok; ++step) {
+            if (!drain_step(step)) continue;
+            for (int ch = 0; ch < nchunks; ++ch) {
+                ok = __all_sync(0xffffffffu, mbar_wait(p_ready(ch), (ready_ph >> ch) & 1u, abort_flag));
+                if (!ok) break;
+                ready_ph ^= 1u << ch;
+                tc_fence_after();
+                uint32_t acc[32];
+                tmem_ld32(tmem_lane + ch * 32, acc);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(p_taken(ch));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float4* mp = reinterpret_cast<float4*>(master + ch * (kMasterBytes / 4) + ((j ^ swz) << 2));
+                    float4 v = *mp;
+                    v.x += __uint_as_float(acc[j * 4 + 0]);
+                    v.y += __uint_as_float(acc[j * 4 + 1]);
+                    v.z += __uint_as_float(acc[j * 4 + 2]);
+                    v.w += __uint_as_float(acc[j * 4 + 3]);
+                    *mp = v;
+                }
+            }
+        }
+
+        if (ok && *abort_flag == 0) {
+            float* out = p.out + (int64_t)blockIdx.y * p.split_stride;
+            for (int ch = 0; ch < nchunks; ++ch) {
+                const int nb = min(4, nblk - ch * 4);
+                if (quarter >= nb) continue;  // warp-uniform
+                const int slot = p.idx[ent0 + ch * 4 + quarter].y;
+                float4* dst = reinterpret_cast<float4*>(out + ((int64_t)slot * 32 + lane) * 32);
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 v = *reinterpret_cast<const float4*>(master + ch * (kMasterBytes / 4) + ((j ^ swz) << 2));
+                    dst[j] = v;
+                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                }
+                if (p.block_sumsq != nullptr) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    if (lane == 0) p.block_sumsq[slot] = ss;
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0) atomicOr(p.status, 1u);
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// item table from the CSR offsets: every row is cut into segments of at most kItemBlocks blocks
+__global__ void __launch_bounds__(256)
+sddmm_items_kernel(const int32_t* __restrict__ ptr, int n_rows, int32_t* __restrict__ items) {
+    __shared__ int running;
+    __shared__ int scan[256];
+    if (threadIdx.x == 0) running = 0;
+    __syncthreads();
+    for (int base = 0; base < n_rows; base += 256) {
+        const int r = base + threadIdx.x;
+        const int cnt = r < n_rows ? ptr[r + 1] - ptr[r] : 0;
+        const int mine = (cnt + kItemBlocks - 1) / kItemBlocks;
+        scan[threadIdx.x] = mine;
+        __syncthreads();
+        for (int o = 1; o < 256; o <<= 1) {  // inclusive Hillis-Steele scan
+            const int v = threadIdx.x >= o ? scan[threadIdx.x - o] : 0;
+            __syncthreads();
+            scan[threadIdx.x] += v;
+            __syncthreads();
+        }
+        const int first = running + scan[threadIdx.x] - mine;
+        for (int i = 0; i < mine; ++i) {
+            int4 it;
+            it.x = r;
+            it.y = ptr[r] + i * kItemBlocks;
+            it.z = min(kItemBlocks, cnt - i * kItemBlocks);
+            it.w = 0;
+            reinterpret_cast<int4*>(items + 4)[first + i] = it;
+        }
+        __syncthreads();
+        if (threadIdx.x == 255) running += scan[255];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) items[0] = running;
+}
+
+// out[i] = sum over splits of ws[s][i], in split order; optional per-slot sum of squares
+__global__ void __launch_bounds__(256)
+sddmm_reduce_kernel(const float* __restrict__ ws, int splits, int64_t split_stride, float* __restrict__ out,
+                    float* __restrict__ block_sumsq) {
+    __shared__ float red[8];
+    const int64_t slot = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(ws + slot * kBlockElems) + threadIdx.x;
+    float4 acc = *src;
+    for (int s = 1; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + s * split_stride);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(out + slot * kBlockElems)[threadIdx.x] = acc;
+    if (block_sumsq != nullptr) {
+        float ss = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) t += red[w];
+            block_sumsq[slot] = t;
+        }
+    }
+}
+
+int64_t max_items(int64_t n_rows, int64_t nnz) { return nnz / kItemBlocks + n_rows; }
+
+// token ranges: enough CTAs for a few waves over 148 SMs, each range a multiple of the 256-token segment
+void choose_splits(int64_t n_rows, int64_t nnz, int64_t tokens, int64_t* splits, int64_t* tokens_per_split) {
+    const int64_t seg = (int64_t)kStepTokens * kDrainSteps;
+    int64_t est_items = (nnz + kItemBlocks - 1) / kItemBlocks;
+    if (est_items < n_rows && nnz >= n_rows) est_items = n_rows;
+    if (est_items < 1) est_items = 1;
+    int64_t want = (4 * 148 + est_items - 1) / est_items;
+    const int64_t max_splits = (tokens + 4 * seg - 1) / (4 * seg);  // at least 1024 tokens per range
+    if (want > max_splits) want = max_splits;
+    if (want < 1) want = 1;
+    int64_t per = (tokens + want - 1) / want;
+    per = (per + seg - 1) / seg * seg;
+    *tokens_per_split = per;
+    *splits = (tokens + per - 1) / per;
+    if (*splits < 1) *splits = 1;
+}
+
+}  // namespace
+
+int64_t sddmm_plan_bytes(int64_t n_rows, int64_t nnz) { return 16 + 16 * max_items(n_rows, nnz); }
+
+cudaError_t launch_build_sddmm_plan(const int32_t* ptr, int64_t n_rows, int64_t nnz, void* plan, cudaStream_t stream) {
+    (void)nnz;
+    sddmm_items_kernel<<<1, 256, 0, stream>>>(ptr, (int)n_rows, static_cast<int32_t*>(plan));
+    return cudaGetLastError();
+}
+
+int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t precision) {
+    (void)cols;
+    if (precision != BSMM_PREC_TF32X3 || tokens < kStepTokens || nnz == 0) return 0;
+    int64_t splits, per;
+    choose_splits(rows / 32, nnz, tokens, &splits, &per);
+    return splits > 1 ? splits * nnz * (int64_t)kBlockElems * 4 : 0;
+}
+
+cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens,
+                              float* sparse_c, const int32_t* idx, const void* plan, int64_t nnz,
+                              float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream) {
+    if (precision != BSMM_PREC_TF32X3 || plan == nullptr || idx == nullptr) return cudaErrorNotSupported;
+    if (tokens < kStepTokens) return cudaErrorNotSupported;  // a box may not exceed its tensor
+    if (tokens > 0x7fffffffll) return cudaErrorInvalidValue;
+    const int64_t n_rows = rows / 32;
+    int64_t splits, per;
+    choose_splits(n_rows, nnz, tokens, &splits, &per);
+    if (splits > 1 && workspace == nullptr) return cudaErrorInvalidValue;
+    if (splits > 65535) return cudaErrorInvalidValue;
+
+    cudaError_t err = cudaFuncSetAttribute(sddmm_umma_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)kSmemBytes);
+    if (err != cudaSuccess) return err;
+    CUtensorMap tmap_x, tmap_dy;
+    err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)cols, (uint64_t)tokens, 32,
+                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (err != cudaSuccess) return err;
+    err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)rows, (uint64_t)tokens, 32,
+                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (err != cudaSuccess) return err;
+
+    SddmmParams p;
+    p.items = static_cast<const int32_t*>(plan);
+    p.idx = reinterpret_cast<const int2*>(idx);
+    p.out = splits > 1 ? static_cast<float*>(workspace) : sparse_c;
+    p.block_sumsq = splits > 1 ? nullptr : block_sumsq;
+    err = device_status_address(&p.status);
+    if (err != cudaSuccess) return err;
+    p.tokens = tokens;
+    p.tokens_per_split = per;
+    p.split_stride = nnz * (int64_t)kBlockElems;
+    dim3 grid((unsigned)max_items(n_rows, nnz), (unsigned)splits);
+    sddmm_umma_tf32x3_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    if (splits > 1) {
+        sddmm_reduce_kernel<<<(unsigned)nnz, 256, 0, stream>>>(static_cast<const float*>(workspace), (int)splits,
+                                                               p.split_stride, sparse_c, block_sumsq);
+        err = cudaGetLastError();
+    }
+    return err;
+}
+
+}  // namespace bsmm
