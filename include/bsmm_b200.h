@@ -36,6 +36,7 @@ extern "C" {
 #define BSMM_PREC_FP32_SIMT 0u /* exact fp32 FMA on CUDA cores (the reference's arithmetic) */
 #define BSMM_PREC_TF32X3 1u    /* tcgen05 kind::tf32, 3-pass hi/lo split, fp32-class accuracy  */
 #define BSMM_PREC_BF16 2u      /* tcgen05 kind::f16 on bf16 operands, fp32 accumulate        */
+#define BSMM_PREC_TF32 3u      /* tcgen05 kind::tf32, single pass (cuBLAS allow_tf32 accuracy class) */
 #define BSMM_PREC_MASK 0xFu
 
 /* bsmm_dsd flags */
@@ -74,7 +75,7 @@ int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* 
 
 /*
  * Per-pattern launch plan of the tensor-core dsd kernel: for every group of `group`
- * consecutive output block-rows (group = 4, 6 or 8: the kernel's tile is 128 tokens x group*32
+ * consecutive output block-rows (group = 4 or 6: the kernel's tile is 128 tokens x group*32
  * columns), the group's index entries re-ordered by (inner block index, row-in-group), with the
  * points at which the kernel promotes its tensor-memory partial sums.  `plan` must hold
  * bsmm_plan_bytes(n_out_blocks, nnz, group) bytes, 16-byte aligned.  Depends only on ptr/idx
@@ -93,8 +94,9 @@ int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks
  *   dgrad (BSMM_DSD_DGRAD)              : out[m, n] = a[m, k] * W,               W is [k, n], ptr/idx = CSC
  * a: [m, k] row-major (fp32, or bf16 with BSMM_PREC_BF16); out: same element type; m is free,
  * n and k are multiples of 32.  Every output element is written (empty block-rows give zeros),
- * so `out` needs no pre-zeroing.  `data` is always required; `packed`/`plan` are required by the
- * tensor-core precisions and ignored by FP32_SIMT.  bias may be NULL.
+ * so `out` needs no pre-zeroing.  `data` is always required; `packed`/`plan` (and the plan's group size
+ * in the flags, BSMM_DSD_GROUP) are required by the tensor-core precisions and ignored by FP32_SIMT.
+ * bias may be NULL.
  */
 int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
              const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
@@ -107,12 +109,22 @@ int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int3
  * a = dY [tokens, rows], b = X [tokens, cols] (row-major unless the *_COLMAJOR flag is set),
  * rows/cols multiples of 32, tokens free.  sparse_c fp32 [nnz*32, 32] is overwritten (beta = 0).
  * `block_sumsq` (fp32 [nnz], may be NULL) receives sum(sparse_c[s]^2).
- * `workspace` (may be NULL) must hold bsmm_sddmm_workspace_bytes(...) bytes when that is non-zero.
+ *
+ * The tensor-core kernel (BSMM_PREC_TF32X3, row-major fp32 operands, at least 32 tokens) walks the
+ * matrix by block-rows and therefore also wants the CSR index array `csr_idx` (cols_a) and the
+ * item table bsmm_build_sddmm_plan makes from the CSR offsets (row_start_ends_a); `plan` must hold
+ * bsmm_sddmm_plan_bytes(n_block_rows, nnz) bytes, 16-byte aligned, and depends only on the pattern.
+ * When the token axis is split over several CTAs the partial results go through `workspace`
+ * (bsmm_sddmm_workspace_bytes(...) bytes, 16-byte aligned) and are summed in a fixed order.
+ * With csr_idx or plan NULL, or for shapes that kernel does not take, the CUDA-core kernel runs
+ * (same fp32-class result).
  */
+int64_t bsmm_sddmm_plan_bytes(int64_t n_block_rows, int64_t nnz);
+int bsmm_build_sddmm_plan(const int32_t* ptr, int64_t n_block_rows, int64_t nnz, void* plan, bsmm_stream_t stream);
 int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t flags);
 int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens, float* sparse_c,
-               const int32_t* blocks, int64_t nnz, float* block_sumsq, void* workspace, uint32_t flags,
-               bsmm_stream_t stream);
+               const int32_t* blocks, int64_t nnz, const int32_t* csr_idx, const void* plan, float* block_sumsq,
+               void* workspace, uint32_t flags, bsmm_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -405,6 +405,17 @@ class BlockSparseMatrixBase(torch.nn.Module):
             self._plan_cache[key] = plan
         return plan
 
+    def _sddmm_plan(self):
+        """Cached per-pattern item table of the tensor-core wgrad kernel (built from the CSR)."""
+        ptr, idx = self.row_start_ends_a, self.cols_a
+        key = ("sddmm", ptr.data_ptr(), ptr._version, idx.data_ptr(), idx._version)
+        plan = self._plan_cache.get(key)
+        if plan is None:
+            plan = native.SddmmPlan(ptr, idx)
+            self._plan_cache = {k: v for k, v in self._plan_cache.items() if k[0] != "sddmm"}
+            self._plan_cache[key] = plan
+        return plan
+
     def packed_weights(self, precision=None):
         """Kernel-ready images of ``data`` (tf32 hi/lo or bf16, both orientations) and the fused
         per-slot sum of squares; rebuilt only when ``data`` changed since the last call."""
@@ -462,7 +473,9 @@ class BlockSparseMatrixBase(torch.nn.Module):
         a, a_rowmajor = self._orient(dense_a)
         b, b_rowmajor = self._orient(dense_b)
         with torch.no_grad():
-            native.sddmm(a, a_rowmajor, b, b_rowmajor, self.blocks, out.detach(), precision=precision)
+            native.sddmm(
+                a, a_rowmajor, b, b_rowmajor, self.blocks, out.detach(), precision=precision, plan=self._sddmm_plan()
+            )
         if overwrite_data:
             self._pack_cache = {}  # the kernel wrote `data` behind autograd's version counter
         return out

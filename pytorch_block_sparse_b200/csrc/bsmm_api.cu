@@ -53,21 +53,18 @@ int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* 
         if (block_sumsq == nullptr) return BSMM_OK;
         return cuda_status(bsmm::launch_block_sumsq(data, nnz, block_sumsq, s));
     }
-    if (precision != BSMM_PREC_TF32X3 && precision != BSMM_PREC_BF16) return BSMM_ERR_UNSUPPORTED;
+    if (!bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return BSMM_ERR_UNSUPPORTED;
     if (nnz > 0 && (packed == nullptr || !aligned(packed, 256))) return BSMM_ERR_INVALID_ARGUMENT;
     return cuda_status(bsmm::launch_pack(data, nnz, precision, packed, block_sumsq, s));
 }
 
 int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz) {
     (void)nnz;
-    if (m <= 0 || n_out_blocks <= 0) return 8;
+    if (m <= 0 || n_out_blocks <= 0) return 6;
     // The widest tile re-uses each activation slab most; narrower tiles are only worth it when the
     // wide one would leave most of the 148 SMs without a CTA.
     const int64_t tiles = (m + 127) / 128;
-    for (int g : {8, 6, 4}) {
-        if (tiles * ((n_out_blocks + g - 1) / g) >= 148) return g;
-    }
-    return 4;
+    return tiles * ((n_out_blocks + 5) / 6) >= 148 ? 6 : 4;
 }
 
 int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz, int group) {
@@ -106,7 +103,7 @@ int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int3
         return cuda_status(bsmm::launch_dsd_simt(static_cast<const float*>(a), m, k, ptr, idx, data, n,
                                                  static_cast<float*>(out), bias, dgrad, colmajor, s));
     }
-    if (precision == BSMM_PREC_TF32X3 || precision == BSMM_PREC_BF16) {
+    if (bsmm::is_tf32_precision(precision) || precision == BSMM_PREC_BF16) {
         if (k == 0 || nnz == 0)  // nothing to contract: the CUDA-core kernel writes the zeros (+bias)
             return cuda_status(bsmm::launch_dsd_simt(static_cast<const float*>(a), m, k, ptr, idx, data, n,
                                                      static_cast<float*>(out), bias, dgrad, colmajor, s));
@@ -120,16 +117,29 @@ int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int3
     return BSMM_ERR_UNSUPPORTED;
 }
 
+int64_t bsmm_sddmm_plan_bytes(int64_t n_block_rows, int64_t nnz) {
+    if (n_block_rows < 0 || nnz < 0) return -1;
+    return bsmm::sddmm_plan_bytes(n_block_rows, nnz);
+}
+
+int bsmm_build_sddmm_plan(const int32_t* ptr, int64_t n_block_rows, int64_t nnz, void* plan, bsmm_stream_t stream) {
+    if (n_block_rows < 0 || nnz < 0 || ptr == nullptr || plan == nullptr || !aligned(plan, 16))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (nnz > 0x7fffffff || n_block_rows > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
+    return cuda_status(bsmm::launch_build_sddmm_plan(ptr, n_block_rows, nnz, plan, static_cast<cudaStream_t>(stream)));
+}
+
 int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t flags) {
     if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0) return -1;
     const uint32_t precision = flags & BSMM_PREC_MASK;
-    if (precision == BSMM_PREC_FP32_SIMT) return 0;
+    if (precision != BSMM_PREC_TF32X3) return 0;
+    if ((flags & (BSMM_SDDMM_A_COLMAJOR | BSMM_SDDMM_B_COLMAJOR)) != 0) return 0;
     return bsmm::sddmm_umma_workspace_bytes(rows, cols, tokens, nnz, precision);
 }
 
 int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens, float* sparse_c,
-               const int32_t* blocks, int64_t nnz, float* block_sumsq, void* workspace, uint32_t flags,
-               bsmm_stream_t stream) {
+               const int32_t* blocks, int64_t nnz, const int32_t* csr_idx, const void* plan, float* block_sumsq,
+               void* workspace, uint32_t flags, bsmm_stream_t stream) {
     const uint32_t precision = flags & BSMM_PREC_MASK;
     const bool a_col = (flags & BSMM_SDDMM_A_COLMAJOR) != 0;
     const bool b_col = (flags & BSMM_SDDMM_B_COLMAJOR) != 0;
@@ -138,26 +148,20 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
     if (nnz == 0) return BSMM_OK;
     if (sparse_c == nullptr || blocks == nullptr || (tokens > 0 && (a == nullptr || b == nullptr)))
         return BSMM_ERR_INVALID_ARGUMENT;
-    if (!aligned(a, 16) || !aligned(b, 16) || !aligned(sparse_c, 16) || !aligned(blocks, 8))
+    if (!aligned(a, 16) || !aligned(b, 16) || !aligned(sparse_c, 16) || !aligned(blocks, 8) || !aligned(csr_idx, 8) ||
+        !aligned(plan, 16) || !aligned(workspace, 16))
         return BSMM_ERR_INVALID_ARGUMENT;
     if (nnz > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
+    if (precision != BSMM_PREC_FP32_SIMT && precision != BSMM_PREC_TF32X3) return BSMM_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (precision == BSMM_PREC_FP32_SIMT) {
-        return cuda_status(bsmm::launch_sddmm_simt(static_cast<const float*>(a), a_col, static_cast<const float*>(b),
-                                                   b_col, rows, cols, tokens, sparse_c, blocks, nnz, block_sumsq, s));
-    }
-    if (precision == BSMM_PREC_TF32X3 || precision == BSMM_PREC_BF16) {
-        if (a_col || b_col) return BSMM_ERR_UNSUPPORTED;
-        const cudaError_t err = bsmm::launch_sddmm_umma(a, b, rows, cols, tokens, sparse_c, blocks, nnz, block_sumsq,
-                                                        workspace, precision, s);
+    if (precision == BSMM_PREC_TF32X3 && !a_col && !b_col) {
+        const cudaError_t err = bsmm::launch_sddmm_umma(a, b, rows, cols, tokens, sparse_c, csr_idx, plan, nnz,
+                                                        block_sumsq, workspace, precision, s);
+        if (err != cudaErrorNotSupported) return cuda_status(err);
         // shapes the tensor-core kernel does not take run on the CUDA-core kernel (same fp32-class result)
-        if (err == cudaErrorNotSupported && precision == BSMM_PREC_TF32X3)
-            return cuda_status(bsmm::launch_sddmm_simt(static_cast<const float*>(a), false,
-                                                       static_cast<const float*>(b), false, rows, cols, tokens,
-                                                       sparse_c, blocks, nnz, block_sumsq, s));
-        return cuda_status(err);
     }
-    return BSMM_ERR_UNSUPPORTED;
+    return cuda_status(bsmm::launch_sddmm_simt(static_cast<const float*>(a), a_col, static_cast<const float*>(b),
+                                               b_col, rows, cols, tokens, sparse_c, blocks, nnz, block_sumsq, s));
 }
 
 }  // extern "C"

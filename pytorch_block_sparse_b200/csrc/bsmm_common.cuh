@@ -10,23 +10,34 @@ namespace bsmm {
 constexpr int kBlock = 32;             // block edge (the reference's OPTIMIZED_BLOCK_SIZE)
 constexpr int kBlockElems = 32 * 32;   // 1024 values, 4 KiB fp32 per slot
 
-// Byte offset of element (mn, k) inside one K-major, un-swizzled UMMA operand image of
-// 32 (mn) x 32 (k) 32-bit values: 8x(16 B) core matrices, the four mn-groups of one
-// k-chunk contiguous (SBO = 128 B), k-chunks 512 B apart (LBO = 512 B).
-__host__ __device__ constexpr uint32_t image32_offset(uint32_t mn, uint32_t k) {
-    return (k >> 2) * 512u + (mn >> 3) * 128u + (mn & 7u) * 16u + (k & 3u) * 4u;
+// tf32 operand image of one 32 (mn) x 32 (k) block, hi and lo parts interleaved per k-chunk:
+// K-major, un-swizzled UMMA canonical layout of 8 x (16 B) core matrices,
+//   k-chunk (4 values of k) stride = leading byte offset = 1024 B: [hi: 4 mn-groups][lo: 4 mn-groups],
+//   mn-group (8 rows) stride = stride byte offset = 128 B.
+// Read with N = 64 from the image start, the MMA sees the operand [hi rows 0..31 ; lo rows 0..31];
+// read with N = 32 it sees the hi part alone.
+__host__ __device__ constexpr uint32_t image32_offset(uint32_t mn, uint32_t k, uint32_t lo_part) {
+    return (k >> 2) * 1024u + lo_part * 512u + (mn >> 3) * 128u + (mn & 7u) * 16u + (k & 3u) * 4u;
 }
-constexpr uint32_t kImage32Bytes = 4096;
-// Same for 16-bit values: core matrix rows hold 8 k-values; k-chunks 512 B apart.
+constexpr uint32_t kImage32Bytes = 8192;       // hi + lo
+constexpr uint32_t kImage32Lbo = 1024;
+constexpr uint32_t kImage32Sbo = 128;
+constexpr uint32_t kImage32StepBytes = 2048;   // one MMA k-step = 8 values of k = two k-chunks
+
+// bf16 operand image of one 32 x 32 block: core-matrix rows hold 8 values of k; k-chunks 512 B apart.
 __host__ __device__ constexpr uint32_t image16_offset(uint32_t mn, uint32_t k) {
     return (k >> 3) * 512u + (mn >> 3) * 128u + (mn & 7u) * 16u + (k & 7u) * 2u;
 }
 constexpr uint32_t kImage16Bytes = 2048;
 
-// Packed-weight buffer layout: [fwd images: nnz][dgrad images: nnz]; one image set per slot is
-//   TF32X3: hi image then lo image (8 KiB);  BF16: one image (2 KiB).
+// tensor-core arithmetic that reads the tf32 images
+__host__ __device__ constexpr bool is_tf32_precision(uint32_t precision) {
+    return precision == BSMM_PREC_TF32X3 || precision == BSMM_PREC_TF32;
+}
+
+// Packed-weight buffer layout: [fwd images: nnz][dgrad images: nnz]
 __host__ __device__ constexpr int64_t packed_slot_bytes(uint32_t precision) {
-    return precision == BSMM_PREC_TF32X3 ? 2 * (int64_t)kImage32Bytes
+    return is_tf32_precision(precision)  ? (int64_t)kImage32Bytes
          : precision == BSMM_PREC_BF16   ? (int64_t)kImage16Bytes
                                          : 0;
 }

@@ -2,13 +2,13 @@
 // into the shared-memory images the tcgen05 kernels fetch with one bulk copy per block, and
 // produces the per-slot sum of squares behind block_norm in the same pass.
 //
-// Per slot and orientation the image is the B operand [mn][k] of a 128 x 32 x 32 UMMA step in the
+// Per slot and orientation the image is the B operand [mn][k] of a 128 x N x 32 UMMA step in the
 // K-major, un-swizzled canonical layout (image32_offset / image16_offset):
 //   fwd   (out = x * W^T): mn = r (output feature), k = c  -> value T[k][mn]
 //   dgrad (out = dy * W ): mn = c (input feature),  k = r  -> value T[mn][k]
-// TF32X3 stores two images per orientation: hi = rna_tf32(w) and lo = rna_tf32(w - hi), so the
-// tensor core sees operands that are already exact tf32 values (no dependence on how the MMA
-// unit would truncate fp32 bit patterns).
+// The tf32 image interleaves hi = rna_tf32(w) and lo = rna_tf32(w - hi) per k-chunk, so that one
+// N = 64 MMA reads [hi ; lo] and an N = 32 MMA reads hi alone.  Both parts are exact tf32 values:
+// nothing depends on how the MMA unit would truncate fp32 bit patterns.
 #include <cuda_bf16.h>
 
 #include "bsmm_common.cuh"
@@ -22,7 +22,7 @@ __device__ __forceinline__ float tf32_rna(float x) {
     return __uint_as_float(r);
 }
 
-template <uint32_t kPrecision>
+template <bool kTf32>
 __global__ void __launch_bounds__(256)
 pack_kernel(const float* __restrict__ data, int64_t nnz, uint8_t* __restrict__ packed,
             float* __restrict__ block_sumsq) {
@@ -51,29 +51,26 @@ pack_kernel(const float* __restrict__ data, int64_t nnz, uint8_t* __restrict__ p
         block_sumsq[slot] = t;
     }
 
-    if (kPrecision == BSMM_PREC_TF32X3) {
-        const int64_t slot_bytes = packed_slot_bytes(BSMM_PREC_TF32X3);
-        float* fwd = reinterpret_cast<float*>(packed + slot * slot_bytes);
-        float* dgr = reinterpret_cast<float*>(packed + (nnz + slot) * slot_bytes);
+    if (kTf32) {
+        float* fwd = reinterpret_cast<float*>(packed + slot * (int64_t)kImage32Bytes);
+        float* dgr = reinterpret_cast<float*>(packed + (nnz + slot) * (int64_t)kImage32Bytes);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t w = tid + 256 * i;  // 32-bit word of the image
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t w = tid + 256 * i;  // 32-bit word of the image: coalesced writes
             const uint32_t byte = w * 4;
-            const uint32_t k = (byte / 512u) * 4u + (byte % 16u) / 4u;
+            const uint32_t k = (byte / 1024u) * 4u + (byte % 16u) / 4u;
+            const uint32_t lo_part = (byte % 1024u) / 512u;
             const uint32_t mn = ((byte % 512u) / 128u) * 8u + (byte % 128u) / 16u;
             const float wf = T[k][mn];
             const float hf = tf32_rna(wf);
-            fwd[w] = hf;
-            fwd[1024 + w] = tf32_rna(wf - hf);
+            fwd[w] = lo_part ? tf32_rna(wf - hf) : hf;
             const float wd = T[mn][k];
             const float hd = tf32_rna(wd);
-            dgr[w] = hd;
-            dgr[1024 + w] = tf32_rna(wd - hd);
+            dgr[w] = lo_part ? tf32_rna(wd - hd) : hd;
         }
-    } else if (kPrecision == BSMM_PREC_BF16) {
-        const int64_t slot_bytes = packed_slot_bytes(BSMM_PREC_BF16);
-        __nv_bfloat162* fwd = reinterpret_cast<__nv_bfloat162*>(packed + slot * slot_bytes);
-        __nv_bfloat162* dgr = reinterpret_cast<__nv_bfloat162*>(packed + (nnz + slot) * slot_bytes);
+    } else {
+        __nv_bfloat162* fwd = reinterpret_cast<__nv_bfloat162*>(packed + slot * (int64_t)kImage16Bytes);
+        __nv_bfloat162* dgr = reinterpret_cast<__nv_bfloat162*>(packed + (nnz + slot) * (int64_t)kImage16Bytes);
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const uint32_t w = tid + 256 * i;  // 32-bit word = two consecutive k of one mn
@@ -92,10 +89,10 @@ cudaError_t launch_pack(const float* data, int64_t nnz, uint32_t precision, void
                         cudaStream_t stream) {
     if (nnz == 0) return cudaSuccess;
     uint8_t* p = static_cast<uint8_t*>(packed);
-    if (precision == BSMM_PREC_TF32X3)
-        pack_kernel<BSMM_PREC_TF32X3><<<(unsigned)nnz, 256, 0, stream>>>(data, nnz, p, block_sumsq);
+    if (is_tf32_precision(precision))
+        pack_kernel<true><<<(unsigned)nnz, 256, 0, stream>>>(data, nnz, p, block_sumsq);
     else if (precision == BSMM_PREC_BF16)
-        pack_kernel<BSMM_PREC_BF16><<<(unsigned)nnz, 256, 0, stream>>>(data, nnz, p, block_sumsq);
+        pack_kernel<false><<<(unsigned)nnz, 256, 0, stream>>>(data, nnz, p, block_sumsq);
     else
         return cudaErrorInvalidValue;
     return cudaGetLastError();

@@ -4,7 +4,7 @@
 //
 //   out[slot][c][r] = sum over tokens t of X[t, C*32 + c] * dY[t, R*32 + r]
 //
-// A CTA owns one "item": up to 32 blocks of ONE block-row R (a CSR row segment) and one range of
+// A CTA owns one "item": up to 16 blocks of ONE block-row R (a CSR row segment) and one range of
 // tokens.  Four blocks of the row form a chunk and fill the 128 rows of one MMA:
 //   D[128 = 4 blocks x 32 c, 32 = r] += A[128 x K] * B[32 x K]^T,   K = tokens, 8 per instruction,
 // A = the four blocks' X slabs, transposed on the way into tensor memory (lane = feature c, column =
@@ -13,11 +13,13 @@
 //
 //   warp 0    producer : TMA tensor loads of [32 tokens x 32 features] fp32 boxes: one dY slab per
 //                        step, four X slabs per chunk
-//   warps 2-5 transform: per step the dY slab -> tf32 hi/lo operand images in shared memory (K-major,
+//   warps 2-5 transform: per step the dY slab -> tf32 operand image [hi ; lo] in shared memory (K-major,
 //                        un-swizzled); per chunk the X slabs, read column-wise, split hi/lo, tcgen05.st
-//   warp 1    MMA      : per chunk and step 4 k-steps x 3 passes of tcgen05.mma kind::tf32 M=128 N=32 K=8
-//   warps 6-9 drain    : every 256 tokens tcgen05.ld each chunk's partial sum and add it (fp32, round to
-//                        nearest) to the chunk's master tile in shared memory; final store to global
+//   warp 1    MMA      : per chunk and k-step  x_hi x [dy_hi ; dy_lo] (N = 64) and x_lo x dy_hi (N = 32),
+//                        tcgen05.mma kind::tf32, M = 128: main | correction columns of the chunk
+//   warps 6-9 drain    : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
+//                        (fp32, round to nearest) to the chunk's master tile in shared memory; final
+//                        store of the master tiles to global
 //
 // The promotion bounds the tensor core's systematic accumulate error (about 2e-8 relative per MMA).
 // Token ranges (grid.y > 1) write partial results to the workspace; a second kernel sums them in a
@@ -30,25 +32,25 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kChunks = 8;                 // chunks (of 4 blocks) per item
-constexpr int kItemBlocks = 4 * kChunks;   // 32
+constexpr int kChunks = 4;                 // chunks (of 4 blocks) per item
+constexpr int kItemBlocks = 4 * kChunks;   // 16
 constexpr int kStepTokens = 32;
-constexpr int kDrainSteps = 8;             // promote every 256 tokens: 96 MMAs per partial sum
+constexpr int kDrainSteps = 32;            // promote every 1024 tokens: 128 accumulations of the main term
 constexpr uint32_t kSlabBytes = 32 * 32 * 4;            // 4 KiB: [32 tokens][32 features]
 constexpr uint32_t kXStageBytes = 4 * kSlabBytes;       // one chunk's X slabs
-constexpr uint32_t kBImgBytes = 2 * kImage32Bytes;      // hi + lo images of the dY slab
 constexpr uint32_t kMasterBytes = 128 * 32 * 4;         // 16 KiB per chunk
-constexpr int kXStages = 4, kDyStages = 2, kBStages = 2, kAStages = 4;
+constexpr int kXStages = 6, kDyStages = 2, kBStages = 2, kAStages = 4;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kAccCols = kChunks * 32;             // 256
-constexpr uint32_t kAStageCols = 64;
+constexpr uint32_t kChunkCols = 64;                     // main | correction
+constexpr uint32_t kAccCols = kChunks * kChunkCols;     // 256
+constexpr uint32_t kAStageCols = 64;                    // hi | lo
 constexpr int kThreads = 320;
 
 constexpr uint32_t kOffMaster = 0;
 constexpr uint32_t kOffX = kOffMaster + kChunks * kMasterBytes;
 constexpr uint32_t kOffDy = kOffX + kXStages * kXStageBytes;
 constexpr uint32_t kOffBImg = kOffDy + kDyStages * kSlabBytes;
-constexpr uint32_t kOffBar = kOffBImg + kBStages * kBImgBytes;
+constexpr uint32_t kOffBar = kOffBImg + kBStages * kImage32Bytes;
 constexpr int kNumBars = 2 * kXStages + 2 * kDyStages + 2 * kBStages + 2 * kAStages + 2 * kChunks;
 constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
@@ -63,7 +65,7 @@ struct SddmmParams {
     float* block_sumsq;    // may be null; only written when the token axis is not split
     unsigned int* status;
     int64_t tokens;
-    int64_t tokens_per_split;  // multiple of kStepTokens * kDrainSteps
+    int64_t tokens_per_split;  // multiple of kStepTokens
     int64_t split_stride;      // floats between two splits' partial results
 };
 
@@ -119,48 +121,60 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     const uint32_t tmem = misc[0];
     volatile uint32_t* abort_flag = &misc[1];
 
-    // a step is a promotion point when it closes a 256-token segment or the token range
+    // the item's CSR entries, one per lane (at most 16), handed out by shuffle
+    const int2 my_ent = lane < nblk ? __ldg(p.idx + ent0 + lane) : make_int2(0, 0);
+
+    // a step is a promotion point when it closes a 1024-token segment or the token range
     auto drain_step = [&](int step) { return ((step + 1) % kDrainSteps) == 0 || step + 1 == nsteps; };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            int xs = 0, ds = 0;
-            uint32_t xph = 0, dph = 0;
-            bool ok = true;
-            for (int step = 0; step < nsteps && ok; ++step) {
-                const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
-                if (!mbar_wait(dy_empty(ds), dph ^ 1u, abort_flag)) break;
-                mbar_arrive_expect_tx(dy_full(ds), kSlabBytes);
-                tma_load_2d(smem_base + kOffDy + ds * kSlabBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
-                if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
-                for (int ch = 0; ch < nchunks; ++ch) {
-                    const int nb = min(4, nblk - ch * 4);
-                    if (!mbar_wait(x_empty(xs), xph ^ 1u, abort_flag)) { ok = false; break; }
-                    mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
-                    for (int j = 0; j < nb; ++j) {
-                        const int bcol = p.idx[ent0 + ch * 4 + j].x;
-                        tma_load_2d(smem_base + kOffX + xs * kXStageBytes + j * kSlabBytes, &tmap_x, bcol * 32, tok,
-                                    x_full(xs));
-                    }
-                    if (++xs == kXStages) { xs = 0; xph ^= 1u; }
+        int xs = 0, ds = 0;
+        uint32_t xph = 0, dph = 0;
+        int ok = 1;
+        for (int step = 0; step < nsteps && ok; ++step) {
+            const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
+            if (lane == 0) {
+                ok = mbar_wait(dy_empty(ds), dph ^ 1u, abort_flag);
+                if (ok) {
+                    mbar_arrive_expect_tx(dy_full(ds), kSlabBytes);
+                    tma_load_2d(smem_base + kOffDy + ds * kSlabBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
                 }
             }
+            if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
+            for (int ch = 0; ch < nchunks; ++ch) {
+                const int nb = min(4, nblk - ch * 4);
+                int bcol[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) bcol[j] = __shfl_sync(0xffffffffu, my_ent.x, ch * 4 + j);
+                if (lane == 0 && ok) {
+                    ok = mbar_wait(x_empty(xs), xph ^ 1u, abort_flag);
+                    if (ok) {
+                        mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (j < nb)
+                                tma_load_2d(smem_base + kOffX + xs * kXStageBytes + j * kSlabBytes, &tmap_x,
+                                            bcol[j] * 32, tok, x_full(xs));
+                    }
+                }
+                if (++xs == kXStages) { xs = 0; xph ^= 1u; }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(2u, 128u, 32u, false, false);
+            constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
+            constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
             int bs = 0, as = 0;
             uint32_t bph = 0, aph = 0;
             uint32_t pending = 0, taken_ph = 0;
             bool ok = true;
             for (int step = 0; step < nsteps && ok; ++step) {
                 if (!mbar_wait(b_full(bs), bph, abort_flag)) break;
-                const uint32_t b_addr = smem_base + kOffBImg + bs * kBImgBytes;
-                const uint64_t b_hi = smem_desc_noswizzle(b_addr, 512, 128);
-                const uint64_t b_lo = smem_desc_noswizzle(b_addr + kImage32Bytes, 512, 128);
-                const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites P
+                const uint32_t b_addr = smem_base + kOffBImg + bs * kImage32Bytes;
+                const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
                 const bool drain = drain_step(step);
                 for (int ch = 0; ch < nchunks; ++ch) {
                     if (!mbar_wait(a_full(as), aph, abort_flag)) { ok = false; break; }
@@ -171,14 +185,13 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                     }
                     tc_fence_after();
                     const uint32_t a_hi = tmem + kAccCols + as * kAStageCols;
-                    const uint32_t d = tmem + ch * 32;
+                    const uint32_t d = tmem + ch * kChunkCols;
                     uint32_t accumulate = fresh ? 0u : 1u;
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
-                        const uint64_t koff = (uint64_t)((s * 1024) >> 4);
-                        mma_ts_tf32(d, a_hi + 32 + s * 8, b_hi + koff, idesc, accumulate);  // lo * hi
-                        mma_ts_tf32(d, a_hi + s * 8, b_lo + koff, idesc, 1u);               // hi * lo
-                        mma_ts_tf32(d, a_hi + s * 8, b_hi + koff, idesc, 1u);               // hi * hi
+                        const uint64_t b = smem_desc_noswizzle(b_addr + s * kImage32StepBytes, kImage32Lbo, kImage32Sbo);
+                        mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, accumulate);       // x_hi x [dy_hi ; dy_lo]
+                        mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);   // x_lo x dy_hi
                         accumulate = 1u;
                     }
                     mma_commit(a_empty(as));
@@ -201,7 +214,7 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         uint32_t xph = 0, dph = 0, bph = 0, aph = 0;
         bool ok = true;
         for (int step = 0; step < nsteps && ok; ++step) {
-            // dY slab [32 tokens][32 r] -> B operand images B[n = r][k = token], hi and lo
+            // dY slab [32 tokens][32 r] -> B operand image B[n = r][k = token], hi and lo parts
             ok = __all_sync(0xffffffffu, mbar_wait(dy_full(ds), dph, abort_flag));
             if (!ok) break;
             ok = __all_sync(0xffffffffu, mbar_wait(b_empty(bs), bph ^ 1u, abort_flag));
@@ -213,13 +226,13 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                 const float4 v0 = *reinterpret_cast<const float4*>(src);
                 const float4 v1 = *reinterpret_cast<const float4*>(src + 4);
                 const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                uint8_t* img = smem_gen + kOffBImg + bs * kBImgBytes;
+                uint8_t* img = smem_gen + kOffBImg + bs * kImage32Bytes;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const uint32_t off = image32_offset((uint32_t)(r0 + i), (uint32_t)kk);
                     const uint32_t h = tf32_rna_bits(f[i]);
-                    *reinterpret_cast<uint32_t*>(img + off) = h;
-                    *reinterpret_cast<uint32_t*>(img + kImage32Bytes + off) = tf32_rna_bits(f[i] - __uint_as_float(h));
+                    *reinterpret_cast<uint32_t*>(img + image32_offset((uint32_t)(r0 + i), (uint32_t)kk, 0u)) = h;
+                    *reinterpret_cast<uint32_t*>(img + image32_offset((uint32_t)(r0 + i), (uint32_t)kk, 1u)) =
+                        tf32_rna_bits(f[i] - __uint_as_float(h));
                 }
             }
             fence_proxy_async_smem();  // generic-proxy writes, read by the MMA through the async proxy
@@ -284,8 +297,9 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                 if (!ok) break;
                 ready_ph ^= 1u << ch;
                 tc_fence_after();
-                uint32_t acc[32];
-                tmem_ld32(tmem_lane + ch * 32, acc);
+                uint32_t acc[32], corr[32];
+                tmem_ld32(tmem_lane + ch * kChunkCols, acc);
+                tmem_ld32(tmem_lane + ch * kChunkCols + 32, corr);
                 tmem_wait_ld();
                 tc_fence_before();
                 mbar_arrive(p_taken(ch));
@@ -293,10 +307,10 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                 for (int j = 0; j < 8; ++j) {
                     float4* mp = reinterpret_cast<float4*>(master + ch * (kMasterBytes / 4) + ((j ^ swz) << 2));
                     float4 v = *mp;
-                    v.x += __uint_as_float(acc[j * 4 + 0]);
-                    v.y += __uint_as_float(acc[j * 4 + 1]);
-                    v.z += __uint_as_float(acc[j * 4 + 2]);
-                    v.w += __uint_as_float(acc[j * 4 + 3]);
+                    v.x += __uint_as_float(acc[j * 4 + 0]) + __uint_as_float(corr[j * 4 + 0]);
+                    v.y += __uint_as_float(acc[j * 4 + 1]) + __uint_as_float(corr[j * 4 + 1]);
+                    v.z += __uint_as_float(acc[j * 4 + 2]) + __uint_as_float(corr[j * 4 + 2]);
+                    v.w += __uint_as_float(acc[j * 4 + 3]) + __uint_as_float(corr[j * 4 + 3]);
                     *mp = v;
                 }
             }
@@ -306,8 +320,8 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
             float* out = p.out + (int64_t)blockIdx.y * p.split_stride;
             for (int ch = 0; ch < nchunks; ++ch) {
                 const int nb = min(4, nblk - ch * 4);
+                const int slot = __shfl_sync(0xffffffffu, my_ent.y, ch * 4 + min(quarter, 3));
                 if (quarter >= nb) continue;  // warp-uniform
-                const int slot = p.idx[ent0 + ch * 4 + quarter].y;
                 float4* dst = reinterpret_cast<float4*>(out + ((int64_t)slot * 32 + lane) * 32);
                 float ss = 0.f;
 #pragma unroll
@@ -377,10 +391,10 @@ sddmm_reduce_kernel(const float* __restrict__ ws, int splits, int64_t split_stri
                     float* __restrict__ block_sumsq) {
     __shared__ float red[8];
     const int64_t slot = blockIdx.x;
-    const float4* src = reinterpret_cast<const float4*>(ws + slot * kBlockElems) + threadIdx.x;
-    float4 acc = *src;
+    const float* src = ws + slot * kBlockElems + threadIdx.x * 4;
+    float4 acc = *reinterpret_cast<const float4*>(src);
     for (int s = 1; s < splits; ++s) {
-        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + s * split_stride);
+        const float4 v = *reinterpret_cast<const float4*>(src + s * split_stride);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     reinterpret_cast<float4*>(out + slot * kBlockElems)[threadIdx.x] = acc;
@@ -401,18 +415,17 @@ sddmm_reduce_kernel(const float* __restrict__ ws, int splits, int64_t split_stri
 
 int64_t max_items(int64_t n_rows, int64_t nnz) { return nnz / kItemBlocks + n_rows; }
 
-// token ranges: enough CTAs for a few waves over 148 SMs, each range a multiple of the 256-token segment
+// token ranges: enough CTAs for a few waves over 148 SMs, each range a multiple of 256 tokens
 void choose_splits(int64_t n_rows, int64_t nnz, int64_t tokens, int64_t* splits, int64_t* tokens_per_split) {
-    const int64_t seg = (int64_t)kStepTokens * kDrainSteps;
     int64_t est_items = (nnz + kItemBlocks - 1) / kItemBlocks;
     if (est_items < n_rows && nnz >= n_rows) est_items = n_rows;
     if (est_items < 1) est_items = 1;
     int64_t want = (4 * 148 + est_items - 1) / est_items;
-    const int64_t max_splits = (tokens + 4 * seg - 1) / (4 * seg);  // at least 1024 tokens per range
+    const int64_t max_splits = (tokens + 1023) / 1024;  // about 1024 tokens per range at least
     if (want > max_splits) want = max_splits;
     if (want < 1) want = 1;
     int64_t per = (tokens + want - 1) / want;
-    per = (per + seg - 1) / seg * seg;
+    per = (per + 255) / 256 * 256;
     *tokens_per_split = per;
     *splits = (tokens + per - 1) / per;
     if (*splits < 1) *splits = 1;
@@ -437,9 +450,9 @@ int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, i
 }
 
 cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens,
-                              float* sparse_c, const int32_t* idx, const void* plan, int64_t nnz,
+                              float* sparse_c, const int32_t* csr_idx, const void* plan, int64_t nnz,
                               float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream) {
-    if (precision != BSMM_PREC_TF32X3 || plan == nullptr || idx == nullptr) return cudaErrorNotSupported;
+    if (precision != BSMM_PREC_TF32X3 || plan == nullptr || csr_idx == nullptr) return cudaErrorNotSupported;
     if (tokens < kStepTokens) return cudaErrorNotSupported;  // a box may not exceed its tensor
     if (tokens > 0x7fffffffll) return cudaErrorInvalidValue;
     const int64_t n_rows = rows / 32;
@@ -461,7 +474,7 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
 
     SddmmParams p;
     p.items = static_cast<const int32_t*>(plan);
-    p.idx = reinterpret_cast<const int2*>(idx);
+    p.idx = reinterpret_cast<const int2*>(csr_idx);
     p.out = splits > 1 ? static_cast<float*>(workspace) : sparse_c;
     p.block_sumsq = splits > 1 ? nullptr : block_sumsq;
     err = device_status_address(&p.status);

@@ -7,21 +7,24 @@
 // block (the plan lists them, bsmm_plan.cu).
 //
 //   warp 0    producer : TMA tensor load of the [128 x 32] fp32 activation slab (128-B swizzle) and
-//                        one 8 KiB linear bulk copy per block of its packed hi/lo weight images
+//                        one 8 KiB linear bulk copy per block of its packed weight image
 //   warps 2-5 transform: slab smem -> registers, split into tf32 hi/lo, tcgen05.st into tensor
 //                        memory (lane = token, column = k), which makes it the MMA's A operand
-//   warp 1    MMA      : per block 4 k-steps x 3 passes (lo*hi, hi*lo, hi*hi) of
-//                        tcgen05.mma kind::tf32 M=128 N=32 K=8, A from tensor memory, B from smem,
-//                        accumulating the row's partial sum P[row] (32 fp32 columns of tensor memory)
-//   warps 6-9 drain    : every kDrainEvery blocks of a row, tcgen05.ld P[row] and add it (fp32, round
-//                        to nearest) to the row's master tile in shared memory; at the end the
-//                        master tiles (initialised with the bias) leave through TMA tensor stores
+//   warp 1    MMA      : tcgen05.mma kind::tf32, M = 128, A from tensor memory, B from smem.
+//                        3xTF32: per k-step (8 values of k) two instructions,
+//                          a_hi x [w_hi ; w_lo]  (N = 64) -> main | correction columns of the row,
+//                          a_lo x  w_hi          (N = 32) -> correction columns,
+//                        which cost 2 x 45 clk instead of 3 x 45 (an MMA costs max(45, N/2) clk).
+//                        single-pass TF32: one N = 32 instruction per k-step.
+//   warps 6-9 drain    : after every kDrainEvery-th block of a row and after its last one,
+//                        tcgen05.ld the row's columns, main + correction (+ bias, or + the output
+//                        written by the row's previous promotion), 128-byte row stores to global
 //
-// Why A from tensor memory: with both operands in shared memory an N=32 MMA re-reads 4 KiB of A per
-// instruction and is bound by shared-memory bandwidth; from tensor memory only the 1 KiB weight
-// image is read.  Why promotion: the tensor core's fp32 accumulate loses about 2e-8 (relative) per
-// MMA, systematically, so a long row (96 blocks = 1152 MMAs) would exceed the 1e-5 error bound.
-// Every mbarrier wait is bounded; on expiry the CTA raises the device status word and drains.
+// Keeping the main term apart from the corrections and promoting it every 32 blocks bounds the
+// tensor core's systematic fp32-accumulate error (about 2e-8 relative per accumulation).
+// Plan entries are fetched 32 at a time by whole warps and broadcast with shuffles, so no role
+// waits on a dependent global load per block.  Every mbarrier wait is bounded; on expiry the CTA
+// raises the device status word and drains.
 #include "bsmm_ptx.cuh"
 #include "bsmm_umma.cuh"
 
@@ -35,33 +38,31 @@ using namespace ptx;
 
 constexpr int kTileTokens = 128;
 constexpr uint32_t kXStageBytes = kTileTokens * 32 * 4;  // 16 KiB
-constexpr uint32_t kWStageBytes = 2 * kImage32Bytes;     // 8 KiB: hi image, lo image
-constexpr uint32_t kMasterBytes = kTileTokens * 32 * 4;  // 16 KiB per output block-row
+constexpr uint32_t kWStageBytes = kImage32Bytes;         // 8 KiB: hi and lo parts interleaved
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kAStageCols = 64;                     // hi: 32 columns, lo: 32 columns
 constexpr int kThreads = 320;
+constexpr int kXStages = 6;
+constexpr int kWStages = 14;
 
-// Shared memory is split between the master tiles (G x 16 KiB) and the two load rings; tensor
-// memory between the partial sums (G x 32 columns) and the split activation slabs.
-template <int G>
+template <int G, int kPasses>
 struct Cfg {
-    static constexpr int kXStages = 7 - G / 2;        // G=8: 3, 6: 4, 4: 5
-    static constexpr int kWStages = 2 * kXStages;     // G=8: 6, 6: 8, 4: 10
-    static constexpr int kAStages = 8 - G / 2;        // G=8: 4, 6: 5, 4: 6
-    static constexpr uint32_t kAccCols = G * 32;
-    static constexpr uint32_t kOffMaster = 0;
-    static constexpr uint32_t kOffX = kOffMaster + G * kMasterBytes;
+    static constexpr uint32_t kRowCols = kPasses == 3 ? 64 : 32;     // main | correction
+    static constexpr uint32_t kAStageCols = kPasses == 3 ? 64 : 32;  // hi | lo
+    static constexpr uint32_t kAccCols = G * kRowCols;
+    static constexpr int kAStagesMax = (int)((kTmemCols - kAccCols) / kAStageCols);
+    static constexpr int kAStages = kAStagesMax > 6 ? 6 : kAStagesMax;
+    static constexpr uint32_t kOffX = 0;
     static constexpr uint32_t kOffW = kOffX + kXStages * kXStageBytes;
     static constexpr uint32_t kOffBar = kOffW + kWStages * kWStageBytes;
     static constexpr int kNumBars = 2 * kXStages + 2 * kWStages + 2 * kAStages + 2 * G;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
     static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;  // + slack to align the base to 1 KiB
-    static_assert(kAccCols + kAStages * kAStageCols <= kTmemCols, "tensor memory over-subscribed");
+    static_assert(kAStages >= 2, "tensor memory over-subscribed");
     static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
 };
 
 struct DsdParams {
-    const uint8_t* packed;     // image sets of this orientation, slot-major
+    const uint8_t* packed;     // weight images of this orientation, slot-major
     const int32_t* group_off;  // [groups + 1]
     const PlanEntry* entries;
     const float* bias;         // may be null
@@ -73,24 +74,56 @@ struct DsdParams {
     uint32_t x_bytes;          // bytes one activation-slab load delivers: min(128, m) rows of 128 B
 };
 
-template <int G>
+// Plan entries [e0, e1) read 32 at a time (one per lane, next chunk already in flight) and handed
+// out by shuffle.  get() must be called by all 32 lanes with a non-decreasing e.
+struct EntryStream {
+    const int4* ents;
+    int e1, base, lane;
+    int4 cur, nxt;
+    __device__ __forceinline__ int4 fetch(int i) const {
+        return i < e1 ? __ldg(ents + i) : make_int4(0, 0, 0, 0);
+    }
+    __device__ __forceinline__ void init(const PlanEntry* entries, int e0, int e1_, int lane_) {
+        ents = reinterpret_cast<const int4*>(entries);
+        e1 = e1_;
+        base = e0;
+        lane = lane_;
+        cur = fetch(e0 + lane);
+        nxt = fetch(e0 + 32 + lane);
+    }
+    __device__ __forceinline__ PlanEntry get(int e) {
+        if (e - base >= 32) {
+            base += 32;
+            cur = nxt;
+            nxt = fetch(base + 32 + lane);
+        }
+        const int src = e - base;
+        PlanEntry r;
+        r.inner = __shfl_sync(0xffffffffu, cur.x, src);
+        r.slot = __shfl_sync(0xffffffffu, cur.y, src);
+        r.row = __shfl_sync(0xffffffffu, cur.z, src);
+        r.flags = __shfl_sync(0xffffffffu, cur.w, src);
+        return r;
+    }
+};
+
+template <int G, int kPasses>
 __global__ void __launch_bounds__(kThreads, 1)
-dsd_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_out,
-                       const DsdParams p) {
-    using C = Cfg<G>;
+dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams p) {
+    using C = Cfg<G, kPasses>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
     const uint32_t bar0 = smem_base + C::kOffBar;
     auto x_full = [&](int s) { return bar0 + 8u * s; };
-    auto x_empty = [&](int s) { return bar0 + 8u * (C::kXStages + s); };
-    auto w_full = [&](int s) { return bar0 + 8u * (2 * C::kXStages + s); };
-    auto w_empty = [&](int s) { return bar0 + 8u * (2 * C::kXStages + C::kWStages + s); };
-    auto a_full = [&](int s) { return bar0 + 8u * (2 * C::kXStages + 2 * C::kWStages + s); };
-    auto a_empty = [&](int s) { return bar0 + 8u * (2 * C::kXStages + 2 * C::kWStages + C::kAStages + s); };
-    auto p_ready = [&](int r) { return bar0 + 8u * (2 * C::kXStages + 2 * C::kWStages + 2 * C::kAStages + r); };
-    auto p_taken = [&](int r) { return bar0 + 8u * (2 * C::kXStages + 2 * C::kWStages + 2 * C::kAStages + G + r); };
+    auto x_empty = [&](int s) { return bar0 + 8u * (kXStages + s); };
+    auto w_full = [&](int s) { return bar0 + 8u * (2 * kXStages + s); };
+    auto w_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + kWStages + s); };
+    auto a_full = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + s); };
+    auto a_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + C::kAStages + s); };
+    auto p_ready = [&](int r) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + 2 * C::kAStages + r); };
+    auto p_taken = [&](int r) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + 2 * C::kAStages + G + r); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kOffMisc);
     // misc[0]: tensor-memory base address, misc[1]: abort flag
 
@@ -103,8 +136,8 @@ dsd_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     const int nrows = min(G, p.n_out_blocks - g * G);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::kXStages; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); }
-        for (int s = 0; s < C::kWStages; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1); }
+        for (int s = 0; s < kXStages; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); }
+        for (int s = 0; s < kWStages; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1); }
         for (int s = 0; s < C::kAStages; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), 1); }
         for (int r = 0; r < G; ++r) { mbar_init(p_ready(r), 1); mbar_init(p_taken(r), 128); }
         misc[1] = 0;
@@ -120,77 +153,86 @@ dsd_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     const uint32_t tmem = misc[0];
     volatile uint32_t* abort_flag = &misc[1];
 
+    EntryStream es;
+    es.init(p.entries, e0, e1, lane);
+
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            int xs = 0, ws = 0;
-            uint32_t xph = 0, wph = 0;
-            for (int e = e0; e < e1; ++e) {
-                const PlanEntry ent = p.entries[e];
+        int xs = 0, ws = 0;
+        uint32_t xph = 0, wph = 0;
+        for (int e = e0; e < e1; ++e) {
+            const PlanEntry ent = es.get(e);
+            int ok = 1;
+            if (lane == 0) {
                 if (ent.flags & kPlanFirst) {
-                    if (!mbar_wait(x_empty(xs), xph ^ 1u, abort_flag)) break;
-                    mbar_arrive_expect_tx(x_full(xs), p.x_bytes);
-                    tma_load_2d(smem_base + C::kOffX + xs * kXStageBytes, &tmap_a, ent.inner * 32, (int32_t)tok0,
-                                x_full(xs));
-                    if (++xs == C::kXStages) { xs = 0; xph ^= 1u; }
+                    ok = mbar_wait(x_empty(xs), xph ^ 1u, abort_flag);
+                    if (ok) {
+                        mbar_arrive_expect_tx(x_full(xs), p.x_bytes);
+                        tma_load_2d(smem_base + C::kOffX + xs * kXStageBytes, &tmap_a, ent.inner * 32, (int32_t)tok0,
+                                    x_full(xs));
+                    }
                 }
-                if (!mbar_wait(w_empty(ws), wph ^ 1u, abort_flag)) break;
-                mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
-                bulk_load(smem_base + C::kOffW + ws * kWStageBytes, p.packed + (int64_t)ent.slot * kWStageBytes,
-                          kWStageBytes, w_full(ws));
-                if (++ws == C::kWStages) { ws = 0; wph ^= 1u; }
+                if (ok) ok = mbar_wait(w_empty(ws), wph ^ 1u, abort_flag);
+                if (ok) {
+                    mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
+                    bulk_load(smem_base + C::kOffW + ws * kWStageBytes, p.packed + (int64_t)ent.slot * kWStageBytes,
+                              kWStageBytes, w_full(ws));
+                }
             }
+            if (ent.flags & kPlanFirst) { if (++xs == kXStages) { xs = 0; xph ^= 1u; } }
+            if (++ws == kWStages) { ws = 0; wph ^= 1u; }
+            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(2u, 128u, 32u, false, false);
-            int ws = 0, as = 0;
-            uint32_t wph = 0, aph = 0;
-            uint32_t started = 0;   // bit r: P[r] holds a partial sum of the current segment
-            uint32_t pending = 0;   // bit r: a promotion of P[r] was requested and not yet seen taken
-            uint32_t taken_ph = 0;  // bit r: parity of the next p_taken[r] phase to wait for
-            uint32_t a_hi = 0;
-            for (int e = e0; e < e1; ++e) {
-                const PlanEntry ent = p.entries[e];
-                const uint32_t rbit = 1u << ent.row;
+        constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
+        constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
+        int ws = 0, as = 0;
+        uint32_t wph = 0, aph = 0;
+        uint32_t started = 0;   // bit r: the row's columns hold a partial sum of the current segment
+        uint32_t pending = 0;   // bit r: a promotion of the row was requested and not yet seen taken
+        uint32_t taken_ph = 0;  // bit r: parity of the next p_taken[r] phase to wait for
+        uint32_t a_hi = 0;
+        for (int e = e0; e < e1; ++e) {
+            const PlanEntry ent = es.get(e);
+            const uint32_t rbit = 1u << ent.row;
+            int ok = 1;
+            if (lane == 0) {
                 if (ent.flags & kPlanFirst) {
-                    if (!mbar_wait(a_full(as), aph, abort_flag)) break;
-                    a_hi = tmem + C::kAccCols + as * kAStageCols;
+                    ok = mbar_wait(a_full(as), aph, abort_flag);
+                    a_hi = tmem + C::kAccCols + as * C::kAStageCols;
                 }
-                if (!mbar_wait(w_full(ws), wph, abort_flag)) break;
-                if (pending & rbit) {  // the drain warps must have read P[row] before it is overwritten
-                    if (!mbar_wait(p_taken(ent.row), (taken_ph >> ent.row) & 1u, abort_flag)) break;
-                    taken_ph ^= rbit;
-                    pending &= ~rbit;
+                if (ok) ok = mbar_wait(w_full(ws), wph, abort_flag);
+                if (ok && (pending & rbit)) {  // the drain warps must have read the row before it is overwritten
+                    ok = mbar_wait(p_taken(ent.row), (taken_ph >> ent.row) & 1u, abort_flag);
                 }
-                tc_fence_after();
-                const uint32_t w_addr = smem_base + C::kOffW + ws * kWStageBytes;
-                const uint64_t b_hi = smem_desc_noswizzle(w_addr, 512, 128);
-                const uint64_t b_lo = smem_desc_noswizzle(w_addr + kImage32Bytes, 512, 128);
-                const uint32_t d = tmem + ent.row * 32;
-                uint32_t accumulate = (started & rbit) ? 1u : 0u;
-                started |= rbit;
+                if (ok) {
+                    tc_fence_after();
+                    const uint32_t w_addr = smem_base + C::kOffW + ws * kWStageBytes;
+                    const uint32_t d = tmem + ent.row * C::kRowCols;
+                    uint32_t accumulate = (started & rbit) ? 1u : 0u;
 #pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    const uint64_t koff = (uint64_t)((s * 1024) >> 4);  // two 512-B k-chunks per step
-                    mma_ts_tf32(d, a_hi + 32 + s * 8, b_hi + koff, idesc, accumulate);  // lo * hi
-                    mma_ts_tf32(d, a_hi + s * 8, b_lo + koff, idesc, 1u);               // hi * lo
-                    mma_ts_tf32(d, a_hi + s * 8, b_hi + koff, idesc, 1u);               // hi * hi
-                    accumulate = 1u;
-                }
-                mma_commit(w_empty(ws));
-                if (++ws == C::kWStages) { ws = 0; wph ^= 1u; }
-                if (ent.flags & kPlanLast) {
-                    mma_commit(a_empty(as));
-                    if (++as == C::kAStages) { as = 0; aph ^= 1u; }
-                }
-                if (ent.flags & kPlanDrain) {
-                    mma_commit(p_ready(ent.row));
-                    pending |= rbit;
-                    started &= ~rbit;
+                    for (int s = 0; s < 4; ++s) {
+                        const uint64_t b = smem_desc_noswizzle(w_addr + s * kImage32StepBytes, kImage32Lbo, kImage32Sbo);
+                        if (kPasses == 3) {
+                            mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, accumulate);        // hi x [hi ; lo]
+                            mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // lo x hi
+                        } else {
+                            mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, accumulate);
+                        }
+                        accumulate = 1u;
+                    }
+                    mma_commit(w_empty(ws));
+                    if (ent.flags & kPlanLast) mma_commit(a_empty(as));
+                    if (ent.flags & kPlanDrain) mma_commit(p_ready(ent.row));
                 }
             }
+            if (pending & rbit) { taken_ph ^= rbit; pending &= ~rbit; }
+            started |= rbit;
+            if (++ws == kWStages) { ws = 0; wph ^= 1u; }
+            if (ent.flags & kPlanLast) { if (++as == C::kAStages) { as = 0; aph ^= 1u; } }
+            if (ent.flags & kPlanDrain) { pending |= rbit; started &= ~rbit; }
+            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------------ transform
@@ -200,8 +242,8 @@ dsd_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         int xs = 0, as = 0;
         uint32_t xph = 0, aph = 0;
         for (int e = e0; e < e1; ++e) {
-            const int flags = p.entries[e].flags;
-            if (!(flags & kPlanFirst)) continue;
+            const PlanEntry ent = es.get(e);
+            if (!(ent.flags & kPlanFirst)) continue;
             if (!__all_sync(0xffffffffu, mbar_wait(x_full(xs), xph, abort_flag))) break;
             uint32_t hi[32], lo[32];
             {
@@ -215,100 +257,93 @@ dsd_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     for (int q = 0; q < 4; ++q) {
                         const uint32_t h = tf32_rna_bits(f[q]);
                         hi[j * 4 + q] = h;
-                        lo[j * 4 + q] = tf32_rna_bits(f[q] - __uint_as_float(h));
+                        if (kPasses == 3) lo[j * 4 + q] = tf32_rna_bits(f[q] - __uint_as_float(h));
                     }
                 }
             }
             mbar_arrive(x_empty(xs));
-            if (++xs == C::kXStages) { xs = 0; xph ^= 1u; }
+            if (++xs == kXStages) { xs = 0; xph ^= 1u; }
             if (!__all_sync(0xffffffffu, mbar_wait(a_empty(as), aph ^ 1u, abort_flag))) break;
             tc_fence_after();
-            const uint32_t a_hi = tmem_lane + C::kAccCols + as * kAStageCols;
+            const uint32_t a_hi = tmem_lane + C::kAccCols + as * C::kAStageCols;
             tmem_st32(a_hi, hi);
-            tmem_st32(a_hi + 32, lo);
+            if (kPasses == 3) tmem_st32(a_hi + 32, lo);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(a_full(as));
             if (++as == C::kAStages) { as = 0; aph ^= 1u; }
         }
     } else {
-        // ------------------------------------------------------------------ drain + epilogue
+        // ------------------------------------------------------------------ drain (promotion + epilogue)
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
-        // this thread's 128-B row of master tile r is at master + r * kMasterBytes, its 16-B chunks
-        // swizzled like TMA's 128-B mode so that the tile can leave through a tensor store
-        uint8_t* master = smem_gen + C::kOffMaster + row * 128;
-        const int swz = row & 7;
+        const int64_t tok = tok0 + row;
+        const bool live = tok < p.m;
 
-        // master tiles start as the bias (or zero): rows without any block come out right by themselves
-        for (int r = 0; r < nrows; ++r) {
-            const float* brow = p.bias != nullptr ? p.bias + ((int64_t)g * G + r) * 32 : nullptr;
+        // v (+ bias on a row's first promotion, + previous output afterwards) -> out[tok, col0 .. col0+31]
+        auto emit = [&](int r, const float (&v)[32], bool first) {
+            if (!live) return;
+            const int64_t col0 = ((int64_t)g * G + r) * 32;
+            if (!p.out_colmajor) {
+                float4* dst = reinterpret_cast<float4*>(p.out + tok * p.n + col0);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (brow != nullptr) b = __ldg(reinterpret_cast<const float4*>(brow) + j);
-                *reinterpret_cast<float4*>(master + r * kMasterBytes + ((j ^ swz) << 4)) = b;
+                for (int j = 0; j < 8; ++j) {
+                    float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (!first) add = dst[j];
+                    else if (p.bias != nullptr) add = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+                    dst[j] = make_float4(v[j * 4 + 0] + add.x, v[j * 4 + 1] + add.y, v[j * 4 + 2] + add.z,
+                                         v[j * 4 + 3] + add.w);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float* dst = p.out + (col0 + j) * p.m + tok;
+                    float add = 0.f;
+                    if (!first) add = *dst;
+                    else if (p.bias != nullptr) add = __ldg(p.bias + col0 + j);
+                    *dst = v[j] + add;
+                }
             }
-        }
+        };
 
         uint32_t ready_ph = 0;  // bit r: parity of the next p_ready[r] phase
+        uint32_t seen = 0;      // bit r: the row has been written once
         bool ok = true;
         for (int e = e0; e < e1; ++e) {
-            const PlanEntry ent = p.entries[e];
+            const PlanEntry ent = es.get(e);
             if (!(ent.flags & kPlanDrain)) continue;
             const int r = ent.row;
             ok = __all_sync(0xffffffffu, mbar_wait(p_ready(r), (ready_ph >> r) & 1u, abort_flag));
             if (!ok) break;
             ready_ph ^= 1u << r;
             tc_fence_after();
-            uint32_t acc[32];
-            tmem_ld32(tmem_lane + r * 32, acc);
-            tmem_wait_ld();
+            uint32_t main_[32];
+            float v[32];
+            tmem_ld32(tmem_lane + r * C::kRowCols, main_);
+            if (kPasses == 3) {
+                uint32_t corr[32];
+                tmem_ld32(tmem_lane + r * C::kRowCols + 32, corr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]) + __uint_as_float(corr[j]);
+            } else {
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]);
+            }
             tc_fence_before();
             mbar_arrive(p_taken(r));
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float4* mp = reinterpret_cast<float4*>(master + r * kMasterBytes + ((j ^ swz) << 4));
-                float4 v = *mp;
-                v.x += __uint_as_float(acc[j * 4 + 0]);
-                v.y += __uint_as_float(acc[j * 4 + 1]);
-                v.z += __uint_as_float(acc[j * 4 + 2]);
-                v.w += __uint_as_float(acc[j * 4 + 3]);
-                *mp = v;
-            }
+            emit(r, v, !((seen >> r) & 1u));
+            seen |= 1u << r;
         }
-
-        // every drain warp reaches this barrier, also after giving up on a wait (its loop above is bounded)
-        fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ok && *abort_flag == 0) {
-            if (!p.out_colmajor) {
-                // master tiles -> global through TMA tensor stores (rows beyond m are clipped by the map)
-                if (warp == 6 && lane == 0) {
-                    for (int r = 0; r < nrows; ++r)
-                        tma_store_2d(&tmap_out, smem_base + C::kOffMaster + r * kMasterBytes,
-                                     (int32_t)(((int64_t)g * G + r) * 32), (int32_t)tok0);
-                    bulk_commit_group();
-                    bulk_wait_group<0>();
-                }
-            } else {
-                const int64_t tok = tok0 + row;
-                if (tok < p.m) {
-                    for (int r = 0; r < nrows; ++r) {
-                        const int64_t col0 = ((int64_t)g * G + r) * 32;
+        if (ok) {
+            // block-rows without any block: bias (or zero)
+            float z[32];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float4 v =
-                                *reinterpret_cast<const float4*>(master + r * kMasterBytes + ((j ^ swz) << 4));
-                            p.out[(col0 + j * 4 + 0) * p.m + tok] = v.x;
-                            p.out[(col0 + j * 4 + 1) * p.m + tok] = v.y;
-                            p.out[(col0 + j * 4 + 2) * p.m + tok] = v.z;
-                            p.out[(col0 + j * 4 + 3) * p.m + tok] = v.w;
-                        }
-                    }
-                }
-            }
+            for (int j = 0; j < 32; ++j) z[j] = 0.f;
+            for (int r = 0; r < nrows; ++r)
+                if (!((seen >> r) & 1u)) emit(r, z, true);
         }
     }
 
@@ -340,15 +375,15 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-template <int G>
-cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const CUtensorMap& tmap_out, const DsdParams& p, int64_t tiles,
-                         cudaStream_t stream) {
+template <int G, int kPasses>
+cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const DsdParams& p, int64_t tiles, cudaStream_t stream) {
     // per call: the attribute is per device and the caller may switch devices
-    cudaError_t err = cudaFuncSetAttribute(dsd_umma_tf32x3_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)Cfg<G>::kSmemBytes);
+    cudaError_t err = cudaFuncSetAttribute(dsd_umma_tf32_kernel<G, kPasses>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)Cfg<G, kPasses>::kSmemBytes);
     if (err != cudaSuccess) return err;
-    dsd_umma_tf32x3_kernel<G>
-        <<<(unsigned)(p.groups * tiles), kThreads, Cfg<G>::kSmemBytes, stream>>>(tmap_a, tmap_out, p);
+    dsd_umma_tf32_kernel<G, kPasses>
+        <<<(unsigned)(p.groups * tiles), kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, p);
     return cudaGetLastError();
 }
 
@@ -389,7 +424,7 @@ cudaError_t device_status_address(unsigned int** addr) {
 cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
                             bool out_colmajor, cudaStream_t stream) {
-    if (precision != BSMM_PREC_TF32X3) return cudaErrorNotSupported;
+    if (!is_tf32_precision(precision)) return cudaErrorNotSupported;
     if (!plan_group_valid(group)) return cudaErrorInvalidValue;
     if (m == 0 || n == 0) return cudaSuccess;
     if (k == 0) return cudaErrorInvalidValue;  // nothing to contract over; a tensor map cannot describe it
@@ -398,24 +433,16 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     const int64_t tiles = (m + kTileTokens - 1) / kTileTokens;
     if (groups * tiles > 0x7fffffffll || m > 0x7fffffffll) return cudaErrorInvalidValue;
 
-    // The boxes never exceed the tensors: with fewer than 128 tokens the slab load fills only the
-    // first m rows; the remaining tensor-memory lanes hold stale values whose outputs are never stored.
+    // The box never exceeds the tensor: with fewer than 128 tokens the slab load fills only the first
+    // m rows; the remaining tensor-memory lanes hold stale values whose outputs are never stored.
     const uint32_t box_rows = (uint32_t)(m < kTileTokens ? m : kTileTokens);
-    CUtensorMap tmap_a, tmap_out;
+    CUtensorMap tmap_a;
     cudaError_t err = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)k, (uint64_t)m, 32,
                                    box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess) return err;
-    if (!out_colmajor) {
-        err = make_tmap_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, (uint64_t)n, (uint64_t)m, 32, box_rows,
-                           CU_TENSOR_MAP_SWIZZLE_128B);
-        if (err != cudaSuccess) return err;
-    } else {
-        tmap_out = tmap_a;  // unused by the kernel in this mode
-    }
 
     DsdParams p;
-    const int64_t slot_bytes = packed_slot_bytes(BSMM_PREC_TF32X3);
-    p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * slot_bytes : 0);
+    p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * (int64_t)kImage32Bytes : 0);
     p.group_off = static_cast<const int32_t*>(plan);
     p.entries = reinterpret_cast<const PlanEntry*>(static_cast<const uint8_t*>(plan) +
                                                    plan_entries_offset(n_out_blocks, group));
@@ -429,11 +456,9 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     p.groups = (int32_t)groups;
     p.out_colmajor = out_colmajor ? 1 : 0;
     p.x_bytes = box_rows * 128u;
-    switch (group) {
-        case 4: return launch_dsd_g<4>(tmap_a, tmap_out, p, tiles, stream);
-        case 6: return launch_dsd_g<6>(tmap_a, tmap_out, p, tiles, stream);
-        default: return launch_dsd_g<8>(tmap_a, tmap_out, p, tiles, stream);
-    }
+    const bool split = precision == BSMM_PREC_TF32X3;
+    if (group == 4) return split ? launch_dsd_g<4, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, p, tiles, stream);
+    return split ? launch_dsd_g<6, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, p, tiles, stream);
 }
 
 cudaError_t read_device_status(unsigned int* status, bool clear) {
@@ -444,13 +469,6 @@ cudaError_t read_device_status(unsigned int* status, bool clear) {
         err = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(unsigned int));
     }
     return err;
-}
-
-int64_t sddmm_umma_workspace_bytes(int64_t, int64_t, int64_t, int64_t, uint32_t) { return 0; }
-
-cudaError_t launch_sddmm_umma(const void*, const void*, int64_t, int64_t, int64_t, float*, const int32_t*, int64_t,
-                              float*, void*, uint32_t, cudaStream_t) {
-    return cudaErrorNotSupported;
 }
 
 }  // namespace bsmm

@@ -1,4 +1,4 @@
-// Launchers of the tcgen05 / TMA kernels and of the plan builder they consume.
+// Launchers of the tcgen05 / TMA kernels and of the plan builders they consume.
 #pragma once
 #include <cuda.h>
 
@@ -18,11 +18,12 @@ constexpr int32_t kPlanFirst = 1;  // first entry of its activation slab
 constexpr int32_t kPlanLast = 2;   // last entry of its activation slab
 constexpr int32_t kPlanDrain = 4;  // after this entry the row's tensor-memory partial sum is promoted
 // Blocks of one output row accumulated in tensor memory between two promotions.  The tensor core
-// adds into its fp32 accumulator with a rounding error that grows linearly with the number of
-// accumulations (measured: about 2e-8 relative per MMA); 8 blocks x 12 MMAs keep it near 2e-6.
-constexpr int kDrainEvery = 8;
+// adds into its fp32 accumulator with a systematic rounding error of about 2e-8 (relative) per
+// accumulation.  The kernel keeps the main term (hi*hi: 4 accumulations per block) apart from the
+// small correction terms, so 32 blocks cost 128 accumulations of the main term: about 3e-6.
+constexpr int kDrainEvery = 32;
 
-inline bool plan_group_valid(int group) { return group == 4 || group == 6 || group == 8; }
+inline bool plan_group_valid(int group) { return group == 4 || group == 6; }
 
 // Plan buffer: [group offsets: n_groups + 1 int32, padded to 16 B][entries: nnz PlanEntry]
 __host__ __device__ constexpr int64_t plan_groups(int64_t n_out_blocks, int group) {
@@ -42,10 +43,14 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
                             bool out_colmajor, cudaStream_t stream);
 
+// SDDMM: item table built from the CSR offsets (one item = up to 16 blocks of one block-row)
+int64_t sddmm_plan_bytes(int64_t n_rows, int64_t nnz);
+cudaError_t launch_build_sddmm_plan(const int32_t* ptr, int64_t n_rows, int64_t nnz, void* plan, cudaStream_t stream);
 int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t precision);
+// returns cudaErrorNotSupported for shapes it does not take (fewer than 32 tokens, missing plan)
 cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens,
-                              float* sparse_c, const int32_t* blocks, int64_t nnz, float* block_sumsq,
-                              void* workspace, uint32_t precision, cudaStream_t stream);
+                              float* sparse_c, const int32_t* csr_idx, const void* plan, int64_t nnz,
+                              float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream);
 
 // 2-D tiled tensor map over a row-major [outer, inner] array.
 cudaError_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,

@@ -15,11 +15,11 @@ LIB_PATH = os.path.join(_PKG_DIR, "libbsmm_b200.so")
 # mirrors include/bsmm_b200.h
 ABI_VERSION = 1
 OK = 0
-PREC_FP32_SIMT, PREC_TF32X3, PREC_BF16 = 0, 1, 2
+PREC_FP32_SIMT, PREC_TF32X3, PREC_BF16, PREC_TF32 = 0, 1, 2, 3
 DSD_DGRAD, DSD_OUT_COLMAJOR = 0x10, 0x20
 SDDMM_A_COLMAJOR, SDDMM_B_COLMAJOR = 0x10, 0x20
 
-PRECISIONS = {"fp32": PREC_FP32_SIMT, "simt": PREC_FP32_SIMT, "tf32x3": PREC_TF32X3, "bf16": PREC_BF16}
+PRECISIONS = {"fp32": PREC_FP32_SIMT, "simt": PREC_FP32_SIMT, "tf32x3": PREC_TF32X3, "tf32": PREC_TF32, "bf16": PREC_BF16}
 EXPORTS = (
     "bsmm_abi_version",
     "bsmm_status_string",
@@ -31,6 +31,8 @@ EXPORTS = (
     "bsmm_plan_bytes",
     "bsmm_build_plan",
     "bsmm_dsd",
+    "bsmm_sddmm_plan_bytes",
+    "bsmm_build_sddmm_plan",
     "bsmm_sddmm_workspace_bytes",
     "bsmm_sddmm",
 )
@@ -79,7 +81,11 @@ def load():
     lib.bsmm_sddmm_workspace_bytes.restype = i64
     lib.bsmm_sddmm_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
     lib.bsmm_sddmm.restype = i32
-    lib.bsmm_sddmm.argtypes = [vp, vp, i64, i64, i64, vp, vp, i64, vp, vp, u32, vp]
+    lib.bsmm_sddmm.argtypes = [vp, vp, i64, i64, i64, vp, vp, i64, vp, vp, vp, vp, u32, vp]
+    lib.bsmm_sddmm_plan_bytes.restype = i64
+    lib.bsmm_sddmm_plan_bytes.argtypes = [i64, i64]
+    lib.bsmm_build_sddmm_plan.restype = i32
+    lib.bsmm_build_sddmm_plan.argtypes = [vp, i64, i64, vp, vp]
     if lib.bsmm_abi_version() != ABI_VERSION:
         raise NativeError("libbsmm_b200.so has ABI %d, this package expects %d" % (lib.bsmm_abi_version(), ABI_VERSION))
     _lib = lib
@@ -105,7 +111,8 @@ def device_status(clear=True):
 
 
 def set_default_precision(name):
-    """'tf32x3' (default; fp32-class accuracy on tensor cores), 'fp32' (CUDA-core FMA) or 'bf16'."""
+    """'tf32x3' (default; fp32-class accuracy on tensor cores), 'fp32' (CUDA-core FMA), 'tf32' (single
+    tensor-core pass, the accuracy class of cuBLAS with allow_tf32) or 'bf16'."""
     global _default_precision
     if name not in PRECISIONS:
         raise ValueError("unknown precision %r, expected one of %s" % (name, sorted(PRECISIONS)))
@@ -229,29 +236,48 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
     return out
 
 
-def sddmm(a, a_rowmajor, b, b_rowmajor, blocks, out, precision=None, block_sumsq=None):
+class SddmmPlan:
+    """Item table of the tensor-core SDDMM kernel for one CSR (offsets, indices) pair."""
+
+    def __init__(self, ptr, idx):
+        _need_cuda(ptr, "ptr")
+        lib = load()
+        self.ptr = ptr
+        self.idx = idx
+        n_rows = ptr.shape[0] - 1
+        nnz = idx.shape[0]
+        self.buffer = torch.empty(lib.bsmm_sddmm_plan_bytes(n_rows, nnz), dtype=torch.uint8, device=ptr.device)
+        with torch.cuda.device(ptr.device):
+            check(
+                lib.bsmm_build_sddmm_plan(_ptr(ptr), n_rows, nnz, _ptr(self.buffer), _stream(ptr.device)),
+                "bsmm_build_sddmm_plan",
+            )
+
+
+def sddmm(a, a_rowmajor, b, b_rowmajor, blocks, out, precision=None, block_sumsq=None, plan=None):
     """``out[s] = (a.T @ b)[block s]`` in ``data`` layout through ``bsmm_sddmm``.
 
     ``a``: dY ``[tokens, rows]``, ``b``: X ``[tokens, cols]``; ``*_rowmajor`` False means the tensor's
-    transpose is the contiguous one."""
+    transpose is the contiguous one.  ``plan`` (:class:`SddmmPlan`) enables the tensor-core kernel."""
     _need_cuda(a, "dense_a")
     lib = load()
     prec = resolve_precision(precision) if not isinstance(precision, int) else precision
+    if prec in (PREC_TF32, PREC_BF16):
+        prec = PREC_TF32X3  # the weight gradient is always accumulated in the fp32-class mode
     tokens, rows = a.shape
     cols = b.shape[1]
     nnz = blocks.shape[0] // 2
-    flags = prec | (0 if a_rowmajor else SDDMM_A_COLMAJOR) | (0 if b_rowmajor else SDDMM_B_COLMAJOR)
-    if (not a_rowmajor or not b_rowmajor or a.dtype != torch.float32) and prec != PREC_FP32_SIMT:
-        # the tensor-core SDDMM takes token-major fp32 operands only
-        flags = (flags & ~0xF) | PREC_FP32_SIMT
+    if a.dtype != torch.float32 or b.dtype != torch.float32:
         a, b = a.float(), b.float()
-    ws_bytes = lib.bsmm_sddmm_workspace_bytes(rows, cols, tokens, nnz, flags)
+    flags = prec | (0 if a_rowmajor else SDDMM_A_COLMAJOR) | (0 if b_rowmajor else SDDMM_B_COLMAJOR)
+    ws_bytes = lib.bsmm_sddmm_workspace_bytes(rows, cols, tokens, nnz, flags) if plan is not None else 0
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes > 0 else None
     with torch.cuda.device(a.device):
         check(
             lib.bsmm_sddmm(
-                _ptr(a), _ptr(b), rows, cols, tokens, _ptr(out), _ptr(blocks), nnz, _ptr(block_sumsq), _ptr(ws),
-                flags, _stream(a.device),
+                _ptr(a), _ptr(b), rows, cols, tokens, _ptr(out), _ptr(blocks), nnz,
+                _ptr(plan.idx) if plan is not None else None, _ptr(plan.buffer) if plan is not None else None,
+                _ptr(block_sumsq), _ptr(ws), flags, _stream(a.device),
             ),
             "bsmm_sddmm",
         )

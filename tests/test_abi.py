@@ -40,11 +40,13 @@ def test_size_queries():
     assert lib.bsmm_packed_bytes(10, native.PREC_BF16) == 2 * 10 * 2048
     assert lib.bsmm_packed_bytes(10, native.PREC_FP32_SIMT) == 0
     assert lib.bsmm_packed_bytes(-1, native.PREC_TF32X3) == -1
-    assert lib.bsmm_plan_bytes(16, 100, 8) == 16 + 100 * 16
+    assert lib.bsmm_plan_bytes(16, 100, 6) == 16 + 100 * 16
     assert lib.bsmm_plan_bytes(16, 100, 4) == 32 + 100 * 16
-    assert lib.bsmm_plan_bytes(16, 100, 5) == -1
-    assert lib.bsmm_plan_group(16384, 128, 4096) == 8
+    assert lib.bsmm_plan_bytes(16, 100, 8) == -1
+    assert lib.bsmm_plan_group(16384, 128, 4096) == 6
     assert lib.bsmm_plan_group(128, 24, 288) == 4
+    assert lib.bsmm_packed_bytes(10, native.PREC_TF32) == 2 * 10 * 8192
+    assert lib.bsmm_sddmm_plan_bytes(8, 100) == 16 + 16 * (100 // 16 + 8)
     assert lib.bsmm_sddmm_workspace_bytes(64, 64, 100, 2, native.PREC_FP32_SIMT) == 0
 
 
@@ -57,15 +59,17 @@ def test_argument_validation_without_device():
     # null output
     assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, null, null, 32, null, null, 0, null) == 1
     # tensor-core precision without packed images / plan, or without the plan's group size in the flags
-    assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, null, null, 32, fake, null, native.PREC_TF32X3 | (8 << 8), null) == 1
+    assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, null, null, 32, fake, null, native.PREC_TF32X3 | (6 << 8), null) == 1
     assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, fake, fake, 32, fake, null, native.PREC_TF32X3, null) == 1
     # bias with dgrad
     assert lib.bsmm_dsd(fake, 4, 32, fake, fake, 1, fake, null, null, 32, fake, fake, native.DSD_DGRAD, null) == 2
     # empty problem is a no-op
     assert lib.bsmm_dsd(null, 0, 32, fake, null, 0, null, null, null, 32, fake, null, 0, null) == 0
     # misaligned pointer
-    assert lib.bsmm_sddmm(ctypes.c_void_p(0x1004), fake, 32, 32, 8, fake, fake, 1, null, null, 0, null) == 1
-    assert lib.bsmm_sddmm(fake, fake, 48, 32, 8, fake, fake, 1, null, null, 0, null) == 1
+    assert lib.bsmm_sddmm(ctypes.c_void_p(0x1004), fake, 32, 32, 8, fake, fake, 1, null, null, null, null, 0, null) == 1
+    assert lib.bsmm_sddmm(fake, fake, 48, 32, 8, fake, fake, 1, null, null, null, null, 0, null) == 1
+    assert lib.bsmm_sddmm(fake, fake, 32, 32, 8, fake, fake, 1, null, null, null, null, native.PREC_BF16, null) == 2
+    assert lib.bsmm_build_sddmm_plan(null, 4, 4, fake, null) == 1
     assert lib.bsmm_pack_weights(null, 3, native.PREC_TF32X3, fake, null, null) == 1
-    assert lib.bsmm_build_plan(null, fake, 4, 4, 8, fake, null) == 1
+    assert lib.bsmm_build_plan(null, fake, 4, 4, 6, fake, null) == 1
     assert lib.bsmm_build_plan(fake, fake, 4, 4, 7, fake, null) == 1
