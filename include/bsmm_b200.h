@@ -61,6 +61,13 @@ int bsmm_last_cuda_error(void);
  * semaphore spins without a limit (cutlass/gemm/k_split_control.h:147-156).
  */
 int bsmm_device_status(unsigned int* status, int clear);
+/*
+ * Diagnostics, no counterpart in the reference: while `device_buffer` (32 int64 on the device) is set,
+ * every tensor-core bsmm_dsd launch records for its CTA number `block` how many cycles each warp role
+ * (producer, MMA issuer, transform, drain) spent in each of its waits, and each role's total.
+ * NULL switches tracing off.  Process-wide, not thread-safe.
+ */
+int bsmm_debug_trace_dsd(void* device_buffer, int block);
 
 /*
  * Kernel-ready weight images + the per-slot sum of squares used by block_norm
@@ -75,14 +82,15 @@ int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* 
 
 /*
  * Per-pattern launch plan of the tensor-core dsd kernel: for every group of `group`
- * consecutive output block-rows (group = 4 or 6: the kernel's tile is 128 tokens x group*32
+ * consecutive output block-rows (group = 4, 6 or 8: the kernel's tile is 128 tokens x group*32
  * columns), the group's index entries re-ordered by (inner block index, row-in-group), with the
  * points at which the kernel promotes its tensor-memory partial sums.  `plan` must hold
  * bsmm_plan_bytes(n_out_blocks, nnz, group) bytes, 16-byte aligned.  Depends only on ptr/idx
  * (each row's entries in ascending inner index, as the reference builds them); rebuild after
- * block_replace / load_state_dict.  bsmm_plan_group suggests a group size for a problem shape.
+ * block_replace / load_state_dict.  bsmm_plan_group suggests a group size for a problem shape and
+ * precision (BSMM_PREC_TF32X3 takes 4 or 6: its rows occupy 64 tensor-memory columns each).
  */
-int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz);
+int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz, uint32_t precision);
 int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz, int group);
 int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, int group, void* plan,
                     bsmm_stream_t stream);

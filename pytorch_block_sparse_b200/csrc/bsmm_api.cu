@@ -38,6 +38,11 @@ int bsmm_device_status(unsigned int* status, int clear) {
     return cuda_status(bsmm::read_device_status(status, clear != 0));
 }
 
+int bsmm_debug_trace_dsd(void* device_buffer, int block) {
+    bsmm::set_dsd_trace(static_cast<long long*>(device_buffer), block);
+    return BSMM_OK;
+}
+
 int64_t bsmm_packed_bytes(int64_t nnz, uint32_t precision) {
     if (nnz < 0) return -1;
     return 2 * nnz * bsmm::packed_slot_bytes(precision & BSMM_PREC_MASK);
@@ -58,13 +63,18 @@ int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* 
     return cuda_status(bsmm::launch_pack(data, nnz, precision, packed, block_sumsq, s));
 }
 
-int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz) {
+int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz, uint32_t precision) {
     (void)nnz;
-    if (m <= 0 || n_out_blocks <= 0) return 6;
+    const bool wide_ok = (precision & BSMM_PREC_MASK) != BSMM_PREC_TF32X3;  // 3xTF32 rows take 64 columns
+    if (m <= 0 || n_out_blocks <= 0) return wide_ok ? 8 : 6;
     // The widest tile re-uses each activation slab most; narrower tiles are only worth it when the
     // wide one would leave most of the 148 SMs without a CTA.
     const int64_t tiles = (m + 127) / 128;
-    return tiles * ((n_out_blocks + 5) / 6) >= 148 ? 6 : 4;
+    for (int g : {8, 6}) {
+        if (g == 8 && !wide_ok) continue;
+        if (tiles * ((n_out_blocks + g - 1) / g) >= 148) return g;
+    }
+    return 4;
 }
 
 int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz, int group) {
@@ -109,7 +119,7 @@ int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int3
                                                      static_cast<float*>(out), bias, dgrad, colmajor, s));
         const int group = (int)((flags >> 8) & 0xFFu);
         if (packed == nullptr || plan == nullptr || !aligned(packed, 256) || !aligned(plan, 16) ||
-            !bsmm::plan_group_valid(group))
+            !bsmm::plan_group_valid(group) || (group == 8 && precision == BSMM_PREC_TF32X3))
             return BSMM_ERR_INVALID_ARGUMENT;
         return cuda_status(bsmm::launch_dsd_umma(a, m, k, nnz, packed, plan, group, n, out, bias, precision, dgrad,
                                                  colmajor, s));

@@ -14,8 +14,11 @@ constexpr int kMaxGroup = 8;
 
 __global__ void __launch_bounds__(128)
 build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx, int n_out_blocks, int G,
-                  int32_t* __restrict__ group_off, PlanEntry* __restrict__ entries) {
+                  int32_t* __restrict__ group_off, int32_t* __restrict__ group_slabs,
+                  PlanEntry* __restrict__ entries) {
     __shared__ int rp[kMaxGroup + 1];
+    __shared__ int slabs;
+    if (threadIdx.x == 0) slabs = 0;
     const int g = blockIdx.x;
     const int r0 = g * G;
     const int nrows = min(G, n_out_blocks - r0);
@@ -53,7 +56,10 @@ build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx,
         const bool drain = ((ord + 1) % kDrainEvery) == 0 || e + 1 == rp[r + 1];
         pe.flags = (before ? 0 : kPlanFirst) | (after ? 0 : kPlanLast) | (drain ? kPlanDrain : 0);
         entries[base + rank] = pe;
+        if (!before) atomicAdd(&slabs, 1);
     }
+    __syncthreads();
+    if (threadIdx.x == 0) group_slabs[g] = slabs;
 }
 
 }  // namespace
@@ -65,10 +71,11 @@ cudaError_t launch_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_
     const int64_t groups = plan_groups(n_out_blocks, group);
     if (groups == 0) return cudaSuccess;
     int32_t* group_off = static_cast<int32_t*>(plan);
+    int32_t* group_slabs = group_off + groups + 1;
     PlanEntry* entries =
         reinterpret_cast<PlanEntry*>(static_cast<uint8_t*>(plan) + plan_entries_offset(n_out_blocks, group));
     build_plan_kernel<<<(unsigned)groups, 128, 0, stream>>>(ptr, reinterpret_cast<const int2*>(idx), (int)n_out_blocks,
-                                                            group, group_off, entries);
+                                                            group, group_off, group_slabs, entries);
     return cudaGetLastError();
 }
 

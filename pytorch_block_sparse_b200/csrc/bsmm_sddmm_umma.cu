@@ -127,19 +127,20 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     // a step is a promotion point when it closes a 1024-token segment or the token range
     auto drain_step = [&](int step) { return ((step + 1) % kDrainSteps) == 0 || step + 1 == nsteps; };
 
+    // The producer and MMA warps run their loops with all 32 lanes in lock-step and elect one lane only
+    // for the single-thread instructions, which keeps those instructions' operands in uniform registers.
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         int xs = 0, ds = 0;
         uint32_t xph = 0, dph = 0;
-        int ok = 1;
+        bool ok = true;
         for (int step = 0; step < nsteps && ok; ++step) {
             const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
-            if (lane == 0) {
-                ok = mbar_wait(dy_empty(ds), dph ^ 1u, abort_flag);
-                if (ok) {
-                    mbar_arrive_expect_tx(dy_full(ds), kSlabBytes);
-                    tma_load_2d(smem_base + kOffDy + ds * kSlabBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
-                }
+            ok = mbar_wait(dy_empty(ds), dph ^ 1u, abort_flag);
+            if (!ok) break;
+            if (elect_one()) {
+                mbar_arrive_expect_tx(dy_full(ds), kSlabBytes);
+                tma_load_2d(smem_base + kOffDy + ds * kSlabBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
             }
             if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
             for (int ch = 0; ch < nchunks; ++ch) {
@@ -147,63 +148,63 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                 int bcol[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) bcol[j] = __shfl_sync(0xffffffffu, my_ent.x, ch * 4 + j);
-                if (lane == 0 && ok) {
-                    ok = mbar_wait(x_empty(xs), xph ^ 1u, abort_flag);
-                    if (ok) {
-                        mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
+                ok = mbar_wait(x_empty(xs), xph ^ 1u, abort_flag);
+                if (!ok) break;
+                const uint32_t dst = smem_base + kOffX + xs * kXStageBytes;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (j < nb)
-                                tma_load_2d(smem_base + kOffX + xs * kXStageBytes + j * kSlabBytes, &tmap_x,
-                                            bcol[j] * 32, tok, x_full(xs));
-                    }
+                    for (int j = 0; j < 4; ++j)
+                        if (j < nb) tma_load_2d(dst + j * kSlabBytes, &tmap_x, bcol[j] * 32, tok, x_full(xs));
                 }
                 if (++xs == kXStages) { xs = 0; xph ^= 1u; }
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
-            constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
-            int bs = 0, as = 0;
-            uint32_t bph = 0, aph = 0;
-            uint32_t pending = 0, taken_ph = 0;
-            bool ok = true;
-            for (int step = 0; step < nsteps && ok; ++step) {
-                if (!mbar_wait(b_full(bs), bph, abort_flag)) break;
-                const uint32_t b_addr = smem_base + kOffBImg + bs * kImage32Bytes;
-                const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
-                const bool drain = drain_step(step);
-                for (int ch = 0; ch < nchunks; ++ch) {
-                    if (!mbar_wait(a_full(as), aph, abort_flag)) { ok = false; break; }
-                    if (fresh && ((pending >> ch) & 1u)) {
-                        if (!mbar_wait(p_taken(ch), (taken_ph >> ch) & 1u, abort_flag)) { ok = false; break; }
-                        taken_ph ^= 1u << ch;
-                        pending &= ~(1u << ch);
-                    }
-                    tc_fence_after();
-                    const uint32_t a_hi = tmem + kAccCols + as * kAStageCols;
-                    const uint32_t d = tmem + ch * kChunkCols;
-                    uint32_t accumulate = fresh ? 0u : 1u;
+        constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
+        constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
+        int bs = 0, as = 0;
+        uint32_t bph = 0, aph = 0;
+        uint32_t pending = 0, taken_ph = 0;
+        bool ok = true;
+        for (int step = 0; step < nsteps && ok; ++step) {
+            ok = mbar_wait(b_full(bs), bph, abort_flag);
+            if (!ok) break;
+            const uint64_t b_desc = smem_desc_noswizzle(smem_base + kOffBImg + bs * kImage32Bytes, kImage32Lbo, kImage32Sbo);
+            const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
+            const bool drain = drain_step(step);
+            for (int ch = 0; ch < nchunks; ++ch) {
+                ok = mbar_wait(a_full(as), aph, abort_flag);
+                if (!ok) break;
+                if (fresh && ((pending >> ch) & 1u)) {
+                    ok = mbar_wait(p_taken(ch), (taken_ph >> ch) & 1u, abort_flag);
+                    if (!ok) break;
+                    taken_ph ^= 1u << ch;
+                    pending &= ~(1u << ch);
+                }
+                tc_fence_after();
+                const uint32_t a_hi = tmem + kAccCols + as * kAStageCols;
+                const uint32_t d = tmem + ch * kChunkCols;
+                const uint32_t acc0 = fresh ? 0u : 1u;
+                const uint32_t a_bar = a_empty(as), p_bar = p_ready(ch);
+                if (elect_one()) {
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
-                        const uint64_t b = smem_desc_noswizzle(b_addr + s * kImage32StepBytes, kImage32Lbo, kImage32Sbo);
-                        mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, accumulate);       // x_hi x [dy_hi ; dy_lo]
-                        mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);   // x_lo x dy_hi
-                        accumulate = 1u;
+                        const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
+                        mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);   // x_hi x [dy_hi ; dy_lo]
+                        mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);       // x_lo x dy_hi
                     }
-                    mma_commit(a_empty(as));
-                    if (++as == kAStages) { as = 0; aph ^= 1u; }
-                    if (drain) {
-                        mma_commit(p_ready(ch));
-                        pending |= 1u << ch;
-                    }
+                    mma_commit(a_bar);
+                    if (drain) mma_commit(p_bar);
                 }
-                mma_commit(b_empty(bs));
-                if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+                if (++as == kAStages) { as = 0; aph ^= 1u; }
+                if (drain) pending |= 1u << ch;
             }
+            if (!ok) break;
+            const uint32_t b_bar = b_empty(bs);
+            if (elect_one()) mma_commit(b_bar);
+            if (++bs == kBStages) { bs = 0; bph ^= 1u; }
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------------ transform

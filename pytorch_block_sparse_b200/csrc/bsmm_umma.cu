@@ -2,29 +2,34 @@
 // block-sparse Linear; replaces the reference's cutlass::gemm::kernel<block_task>,
 // cutlass/gemm/dispatch.h:185-218 and block_task.h:647-715).
 //
-// Tile: 128 tokens x G output block-rows (G*32 columns) per CTA.  The contraction axis is walked
-// one 32-wide activation slab at a time, visiting only slabs for which the group has at least one
-// block (the plan lists them, bsmm_plan.cu).
+// Tile: 128 tokens x G output block-rows (G*32 columns) per CTA, accumulated in tensor memory.  The
+// contraction axis is walked one 32-wide activation slab at a time, visiting only slabs for which
+// the group has at least one block (the plan lists them, bsmm_plan.cu).
 //
-//   warp 0    producer : TMA tensor load of the [128 x 32] fp32 activation slab (128-B swizzle) and
-//                        one 8 KiB linear bulk copy per block of its packed weight image
-//   warps 2-5 transform: slab smem -> registers, split into tf32 hi/lo, tcgen05.st into tensor
-//                        memory (lane = token, column = k), which makes it the MMA's A operand
-//   warp 1    MMA      : tcgen05.mma kind::tf32, M = 128, A from tensor memory, B from smem.
-//                        3xTF32: per k-step (8 values of k) two instructions,
-//                          a_hi x [w_hi ; w_lo]  (N = 64) -> main | correction columns of the row,
-//                          a_lo x  w_hi          (N = 32) -> correction columns,
-//                        which cost 2 x 45 clk instead of 3 x 45 (an MMA costs max(45, N/2) clk).
-//                        single-pass TF32: one N = 32 instruction per k-step.
-//   warps 6-9 drain    : after every kDrainEvery-th block of a row and after its last one,
-//                        tcgen05.ld the row's columns, main + correction (+ bias, or + the output
-//                        written by the row's previous promotion), 128-byte row stores to global
+//   warp 0     producer : TMA tensor load of the [128 x 32] fp32 activation slab (128-byte swizzle)
+//                         and one 8 KiB linear bulk copy per block of its packed weight image
+//   warps 3-6  transform: slab smem -> registers -> tensor memory (lane = token, column = k) with
+//                         tcgen05.st, which makes it the MMA's A operand; for 3xTF32 also
+//                         lo = x - trunc_tf32(x) (the tensor core reads only the tf32 bits of an
+//                         operand, so the raw slab is x_hi)
+//   warps 1-2  MMA      : tcgen05.mma kind::tf32, M = 128, A from tensor memory, B from smem; the
+//                         two warps take the blocks of even and odd output rows.
+//                         3xTF32, per k-step (8 values of k) two instructions:
+//                           x_hi x [w_hi ; w_lo]  (N = 64) -> main | correction columns of the row
+//                           x_lo x  w_hi          (N = 32) -> correction columns
+//                         single-pass TF32: one N = 32 instruction per k-step.
+//   warps 7-10 drain    : after every kDrainEvery-th block of a row and after its last one,
+//                         tcgen05.ld the row's columns, main + correction (+ bias, or + the output
+//                         written by the row's previous promotion), 128-byte row stores to global
 //
+// Measured on an idle SM, one block costs the tensor pipe 255 clk (3xTF32) or 165 clk (single pass)
+// in this form, against 422 / 232 clk with A read from shared memory (4 KiB per instruction).
 // Keeping the main term apart from the corrections and promoting it every 32 blocks bounds the
 // tensor core's systematic fp32-accumulate error (about 2e-8 relative per accumulation).
-// Plan entries are fetched 32 at a time by whole warps and broadcast with shuffles, so no role
-// waits on a dependent global load per block.  Every mbarrier wait is bounded; on expiry the CTA
-// raises the device status word and drains.
+// The producer and MMA warps run warp-uniform loops and elect one lane only for the instruction
+// itself, so the operands of TMA / tcgen05.mma stay in uniform registers; plan entries are read
+// four blocks ahead.  Every mbarrier wait is bounded; on expiry the CTA raises the device status
+// word and drains.
 #include "bsmm_ptx.cuh"
 #include "bsmm_umma.cuh"
 
@@ -37,22 +42,22 @@ namespace {
 using namespace ptx;
 
 constexpr int kTileTokens = 128;
-constexpr uint32_t kXStageBytes = kTileTokens * 32 * 4;  // 16 KiB
-constexpr uint32_t kWStageBytes = kImage32Bytes;         // 8 KiB: hi and lo parts interleaved
+constexpr uint32_t kSlabBytes = kTileTokens * 32 * 4;  // 16 KiB: [128 tokens][32 k] fp32
+constexpr uint32_t kWStageBytes = kImage32Bytes;       // 8 KiB: hi and lo parts interleaved
 constexpr uint32_t kTmemCols = 512;
-constexpr int kThreads = 320;
+constexpr int kThreads = 352;  // producer, two MMA issuers, four split warps, four drain warps
 constexpr int kXStages = 6;
 constexpr int kWStages = 14;
 
 template <int G, int kPasses>
 struct Cfg {
     static constexpr uint32_t kRowCols = kPasses == 3 ? 64 : 32;     // main | correction
-    static constexpr uint32_t kAStageCols = kPasses == 3 ? 64 : 32;  // hi | lo
+    static constexpr uint32_t kAStageCols = kPasses == 3 ? 64 : 32;  // x_hi | x_lo
     static constexpr uint32_t kAccCols = G * kRowCols;
     static constexpr int kAStagesMax = (int)((kTmemCols - kAccCols) / kAStageCols);
-    static constexpr int kAStages = kAStagesMax > 6 ? 6 : kAStagesMax;
+    static constexpr int kAStages = kAStagesMax > 8 ? 8 : kAStagesMax;
     static constexpr uint32_t kOffX = 0;
-    static constexpr uint32_t kOffW = kOffX + kXStages * kXStageBytes;
+    static constexpr uint32_t kOffW = kOffX + kXStages * kSlabBytes;
     static constexpr uint32_t kOffBar = kOffW + kWStages * kWStageBytes;
     static constexpr int kNumBars = 2 * kXStages + 2 * kWStages + 2 * kAStages + 2 * G;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
@@ -62,68 +67,49 @@ struct Cfg {
 };
 
 struct DsdParams {
-    const uint8_t* packed;     // weight images of this orientation, slot-major
-    const int32_t* group_off;  // [groups + 1]
+    const uint8_t* packed;      // weight images of this orientation, slot-major
+    const int32_t* group_off;   // [groups + 1]
+    const int32_t* group_slabs; // [groups]
     const PlanEntry* entries;
-    const float* bias;         // may be null
+    const float* bias;          // may be null
     float* out;
-    unsigned int* status;      // device status word
+    unsigned int* status;       // device status word
     int64_t m, n;
     int32_t n_out_blocks, groups;
     int32_t out_colmajor;
-    uint32_t x_bytes;          // bytes one activation-slab load delivers: min(128, m) rows of 128 B
+    uint32_t x_bytes;           // bytes one activation-slab load delivers: min(128, m) rows of 128 B
+    long long* trace;           // diagnostics: 32 wait-cycle counters of CTA `trace_block`, or null
+    int32_t trace_block;
 };
 
-// Plan entries [e0, e1) read 32 at a time (one per lane, next chunk already in flight) and handed
-// out by shuffle.  get() must be called by all 32 lanes with a non-decreasing e.
-struct EntryStream {
-    const int4* ents;
-    int e1, base, lane;
-    int4 cur, nxt;
-    __device__ __forceinline__ int4 fetch(int i) const {
-        return i < e1 ? __ldg(ents + i) : make_int4(0, 0, 0, 0);
-    }
-    __device__ __forceinline__ void init(const PlanEntry* entries, int e0, int e1_, int lane_) {
-        ents = reinterpret_cast<const int4*>(entries);
-        e1 = e1_;
-        base = e0;
-        lane = lane_;
-        cur = fetch(e0 + lane);
-        nxt = fetch(e0 + 32 + lane);
-    }
-    __device__ __forceinline__ PlanEntry get(int e) {
-        if (e - base >= 32) {
-            base += 32;
-            cur = nxt;
-            nxt = fetch(base + 32 + lane);
-        }
-        const int src = e - base;
-        PlanEntry r;
-        r.inner = __shfl_sync(0xffffffffu, cur.x, src);
-        r.slot = __shfl_sync(0xffffffffu, cur.y, src);
-        r.row = __shfl_sync(0xffffffffu, cur.z, src);
-        r.flags = __shfl_sync(0xffffffffu, cur.w, src);
-        return r;
-    }
+// Counters written when tracing: cycles the role spent inside each kind of wait, and its loop total.
+enum TraceSlot {
+    kTrProdXEmpty = 0, kTrProdWEmpty, kTrProdTotal, kTrProdIssue,
+    kTrMmaAFull = 4, kTrMmaWFull, kTrMmaPTaken, kTrMmaTotal,
+    kTrMmaIssue = 14,
+    kTrXfXFull = 8, kTrXfAEmpty, kTrXfTotal,
+    kTrDrainPReady = 12, kTrDrainTotal,
 };
 
 template <int G, int kPasses>
 __global__ void __launch_bounds__(kThreads, 1)
 dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams p) {
     using C = Cfg<G, kPasses>;
+    constexpr int XS = kXStages;
+    constexpr int AS = C::kAStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
     const uint32_t bar0 = smem_base + C::kOffBar;
-    auto x_full = [&](int s) { return bar0 + 8u * s; };
-    auto x_empty = [&](int s) { return bar0 + 8u * (kXStages + s); };
-    auto w_full = [&](int s) { return bar0 + 8u * (2 * kXStages + s); };
-    auto w_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + kWStages + s); };
-    auto a_full = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + s); };
-    auto a_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + C::kAStages + s); };
-    auto p_ready = [&](int r) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + 2 * C::kAStages + r); };
-    auto p_taken = [&](int r) { return bar0 + 8u * (2 * kXStages + 2 * kWStages + 2 * C::kAStages + G + r); };
+    auto x_full = [&](int s) { return bar0 + 8u * s; };                      // TMA delivered the slab
+    auto x_empty = [&](int s) { return bar0 + 8u * (XS + s); };              // transform warps read it
+    auto w_full = [&](int s) { return bar0 + 8u * (2 * XS + s); };
+    auto w_empty = [&](int s) { return bar0 + 8u * (2 * XS + kWStages + s); };
+    auto a_full = [&](int s) { return bar0 + 8u * (2 * XS + 2 * kWStages + s); };       // slab is in tensor memory
+    auto a_empty = [&](int s) { return bar0 + 8u * (2 * XS + 2 * kWStages + AS + s); }; // both MMA warps are past it
+    auto p_ready = [&](int r) { return bar0 + 8u * (2 * XS + 2 * kWStages + 2 * AS + r); };
+    auto p_taken = [&](int r) { return bar0 + 8u * (2 * XS + 2 * kWStages + 2 * AS + G + r); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kOffMisc);
     // misc[0]: tensor-memory base address, misc[1]: abort flag
 
@@ -133,12 +119,13 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
     const int g = blockIdx.x % p.groups;
     const int64_t tok0 = (int64_t)(blockIdx.x / p.groups) * kTileTokens;
     const int e0 = p.group_off[g], e1 = p.group_off[g + 1];
+    const int nslabs = p.group_slabs[g];
     const int nrows = min(G, p.n_out_blocks - g * G);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kXStages; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); }
+        for (int s = 0; s < XS; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); }
+        for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), 2); }
         for (int s = 0; s < kWStages; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1); }
-        for (int s = 0; s < C::kAStages; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), 1); }
         for (int r = 0; r < G; ++r) { mbar_init(p_ready(r), 1); mbar_init(p_taken(r), 128); }
         misc[1] = 0;
         fence_mbar_init();
@@ -153,117 +140,177 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
     const uint32_t tmem = misc[0];
     volatile uint32_t* abort_flag = &misc[1];
 
-    EntryStream es;
-    es.init(p.entries, e0, e1, lane);
+    const bool tracing = p.trace != nullptr && (int)blockIdx.x == p.trace_block;
+    long long tr[4] = {0, 0, 0, 0};
+    const long long t_role0 = tracing ? clock64() : 0;
+    auto wait = [&](uint32_t bar, uint32_t parity, int which) -> bool {
+        if (!tracing) return mbar_wait(bar, parity, abort_flag);
+        const long long t = clock64();
+        const bool r = mbar_wait(bar, parity, abort_flag);
+        tr[which] += clock64() - t;
+        return r;
+    };
+    const int4* ents = reinterpret_cast<const int4*>(p.entries);
+    auto fetch = [&](int i) { return i < e1 ? __ldg(ents + i) : make_int4(0, 0, 0, 0); };  // x inner, y slot, z row, w flags
 
+    // The producer and MMA warps run their loops with all 32 lanes in lock-step (every lane loads the
+    // same plan entry and polls the same barriers) and elect one lane only for the instruction itself.
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         int xs = 0, ws = 0;
         uint32_t xph = 0, wph = 0;
-        for (int e = e0; e < e1; ++e) {
-            const PlanEntry ent = es.get(e);
-            int ok = 1;
-            if (lane == 0) {
-                if (ent.flags & kPlanFirst) {
-                    ok = mbar_wait(x_empty(xs), xph ^ 1u, abort_flag);
-                    if (ok) {
-                        mbar_arrive_expect_tx(x_full(xs), p.x_bytes);
-                        tma_load_2d(smem_base + C::kOffX + xs * kXStageBytes, &tmap_a, ent.inner * 32, (int32_t)tok0,
-                                    x_full(xs));
-                    }
+        bool ok = true;
+        auto issue = [&](const int4& ent) {
+            if (ent.w & kPlanFirst) {
+                ok = wait(x_empty(xs), xph ^ 1u, 0);
+                if (!ok) return;
+                const uint32_t dst = smem_base + C::kOffX + xs * kSlabBytes;
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(x_full(xs), p.x_bytes);
+                    tma_load_2d(dst, &tmap_a, ent.x * 32, (int32_t)tok0, x_full(xs));
                 }
-                if (ok) ok = mbar_wait(w_empty(ws), wph ^ 1u, abort_flag);
-                if (ok) {
-                    mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
-                    bulk_load(smem_base + C::kOffW + ws * kWStageBytes, p.packed + (int64_t)ent.slot * kWStageBytes,
-                              kWStageBytes, w_full(ws));
-                }
+                if (++xs == XS) { xs = 0; xph ^= 1u; }
             }
-            if (ent.flags & kPlanFirst) { if (++xs == kXStages) { xs = 0; xph ^= 1u; } }
+            ok = wait(w_empty(ws), wph ^ 1u, 1);
+            if (!ok) return;
+            const uint32_t dst = smem_base + C::kOffW + ws * kWStageBytes;
+            const uint8_t* src = p.packed + (int64_t)ent.y * kWStageBytes;
+            const long long ti = tracing ? clock64() : 0;
+            if (elect_one()) {
+                mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
+                bulk_load(dst, src, kWStageBytes, w_full(ws));
+            }
+            if (tracing) tr[3] += clock64() - ti;
             if (++ws == kWStages) { ws = 0; wph ^= 1u; }
-            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+        };
+        int4 q0 = fetch(e0), q1 = fetch(e0 + 1), q2 = fetch(e0 + 2), q3 = fetch(e0 + 3);
+        for (int e = e0; e < e1 && ok; e += 4) {
+            issue(q0); q0 = fetch(e + 4);
+            if (e + 1 < e1 && ok) { issue(q1); q1 = fetch(e + 5); }
+            if (e + 2 < e1 && ok) { issue(q2); q2 = fetch(e + 6); }
+            if (e + 3 < e1 && ok) { issue(q3); q3 = fetch(e + 7); }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+        if (tracing && lane == 0) {
+            p.trace[kTrProdXEmpty] = tr[0];
+            p.trace[kTrProdWEmpty] = tr[1];
+            p.trace[kTrProdTotal] = clock64() - t_role0;
+            p.trace[kTrProdIssue] = tr[3];
+        }
+    } else if (warp <= 2) {
+        // ------------------------------------------------------------------ MMA issuers
+        // Two warps share the issue work by output row parity: while one is between blocks (barrier
+        // polls, descriptor arithmetic, commits) the other keeps the tensor pipe fed.  Both walk the
+        // whole plan so that their stage counters agree; a slab's stage is released when both passed it.
+        const uint32_t mw = (uint32_t)(warp - 1);
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
-        int ws = 0, as = 0;
-        uint32_t wph = 0, aph = 0;
+        int ws = 0, as = -1;
+        uint32_t wph = 0, aph = 1;  // as/aph advance at every first-of-slab entry
         uint32_t started = 0;   // bit r: the row's columns hold a partial sum of the current segment
         uint32_t pending = 0;   // bit r: a promotion of the row was requested and not yet seen taken
         uint32_t taken_ph = 0;  // bit r: parity of the next p_taken[r] phase to wait for
         uint32_t a_hi = 0;
-        for (int e = e0; e < e1; ++e) {
-            const PlanEntry ent = es.get(e);
-            const uint32_t rbit = 1u << ent.row;
-            int ok = 1;
-            if (lane == 0) {
-                if (ent.flags & kPlanFirst) {
-                    ok = mbar_wait(a_full(as), aph, abort_flag);
-                    a_hi = tmem + C::kAccCols + as * C::kAStageCols;
-                }
-                if (ok) ok = mbar_wait(w_full(ws), wph, abort_flag);
-                if (ok && (pending & rbit)) {  // the drain warps must have read the row before it is overwritten
-                    ok = mbar_wait(p_taken(ent.row), (taken_ph >> ent.row) & 1u, abort_flag);
-                }
-                if (ok) {
-                    tc_fence_after();
-                    const uint32_t w_addr = smem_base + C::kOffW + ws * kWStageBytes;
-                    const uint32_t d = tmem + ent.row * C::kRowCols;
-                    uint32_t accumulate = (started & rbit) ? 1u : 0u;
-#pragma unroll
-                    for (int s = 0; s < 4; ++s) {
-                        const uint64_t b = smem_desc_noswizzle(w_addr + s * kImage32StepBytes, kImage32Lbo, kImage32Sbo);
-                        if (kPasses == 3) {
-                            mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, accumulate);        // hi x [hi ; lo]
-                            mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // lo x hi
-                        } else {
-                            mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, accumulate);
-                        }
-                        accumulate = 1u;
-                    }
-                    mma_commit(w_empty(ws));
-                    if (ent.flags & kPlanLast) mma_commit(a_empty(as));
-                    if (ent.flags & kPlanDrain) mma_commit(p_ready(ent.row));
-                }
+        bool ok = true;
+        auto issue = [&](const int4& ent) {
+            const uint32_t row = (uint32_t)ent.z;
+            const uint32_t rbit = 1u << row;
+            if (ent.w & kPlanFirst) {
+                if (++as == AS) as = 0;
+                if (as == 0) aph ^= 1u;
+                ok = wait(a_full(as), aph, 0);
+                if (!ok) return;
+                tc_fence_after();  // the transform warps' tcgen05.st precede the MMAs that read the slab
+                a_hi = tmem + C::kAccCols + as * C::kAStageCols;
             }
-            if (pending & rbit) { taken_ph ^= rbit; pending &= ~rbit; }
+            const bool mine = (row & 1u) == mw;
+            const bool last = (ent.w & kPlanLast) != 0, drain = (ent.w & kPlanDrain) != 0;
+            if (!mine) {
+                if (last) {  // nothing of this warp may still be reading the slab once its earlier MMAs completed
+                    const uint32_t a_bar = a_empty(as);
+                    if (elect_one()) mma_commit(a_bar);
+                }
+                if (++ws == kWStages) { ws = 0; wph ^= 1u; }
+                return;
+            }
+            ok = wait(w_full(ws), wph, 1);
+            if (!ok) return;
+            if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
+                ok = wait(p_taken(row), (taken_ph >> row) & 1u, 2);
+                if (!ok) return;
+                taken_ph ^= rbit;
+                pending &= ~rbit;
+                tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the row
+            }
+            const uint64_t b_desc =
+                smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
+            const uint32_t d = tmem + row * C::kRowCols;
+            const uint32_t acc0 = (started & rbit) ? 1u : 0u;
+            const uint32_t w_bar = w_empty(ws), a_bar = a_empty(as), p_bar = p_ready(row);
+            const long long ti = tracing ? clock64() : 0;
+            if (elect_one()) {
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    // k-step s: 8 columns further in the slab's tensor-memory copy, 2 KiB further in the image
+                    const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
+                    const uint32_t acc = s == 0 ? acc0 : 1u;
+                    if (kPasses == 3) {
+                        mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, acc);               // x_hi x [w_hi ; w_lo]
+                        mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // x_lo x w_hi
+                    } else {
+                        mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, acc);
+                    }
+                }
+                mma_commit(w_bar);
+                if (last) mma_commit(a_bar);
+                if (drain) mma_commit(p_bar);
+            }
+            if (tracing) tr[3] += clock64() - ti;
             started |= rbit;
             if (++ws == kWStages) { ws = 0; wph ^= 1u; }
-            if (ent.flags & kPlanLast) { if (++as == C::kAStages) { as = 0; aph ^= 1u; } }
-            if (ent.flags & kPlanDrain) { pending |= rbit; started &= ~rbit; }
-            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            if (drain) { pending |= rbit; started &= ~rbit; }
+        };
+        int4 q0 = fetch(e0), q1 = fetch(e0 + 1), q2 = fetch(e0 + 2), q3 = fetch(e0 + 3);
+        for (int e = e0; e < e1 && ok; e += 4) {
+            issue(q0); q0 = fetch(e + 4);
+            if (e + 1 < e1 && ok) { issue(q1); q1 = fetch(e + 5); }
+            if (e + 2 < e1 && ok) { issue(q2); q2 = fetch(e + 6); }
+            if (e + 3 < e1 && ok) { issue(q3); q3 = fetch(e + 7); }
         }
-    } else if (warp < 6) {
+        if (tracing && lane == 0 && mw == 0) {
+            p.trace[kTrMmaAFull] = tr[0];
+            p.trace[kTrMmaWFull] = tr[1];
+            p.trace[kTrMmaPTaken] = tr[2];
+            p.trace[kTrMmaTotal] = clock64() - t_role0;
+            p.trace[kTrMmaIssue] = tr[3];
+        }
+    } else if (warp < 7) {
         // ------------------------------------------------------------------ transform
-        const int quarter = warp & 3;              // tensor-memory lane quarter this warp may access
-        const int row = quarter * 32 + lane;       // token inside the tile = tensor-memory lane
+        const int quarter = warp & 3;           // tensor-memory lane quarter this warp may access
+        const int row = quarter * 32 + lane;    // token inside the tile = tensor-memory lane
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         int xs = 0, as = 0;
         uint32_t xph = 0, aph = 0;
-        for (int e = e0; e < e1; ++e) {
-            const PlanEntry ent = es.get(e);
-            if (!(ent.flags & kPlanFirst)) continue;
-            if (!__all_sync(0xffffffffu, mbar_wait(x_full(xs), xph, abort_flag))) break;
+        for (int s = 0; s < nslabs; ++s) {
+            if (!__all_sync(0xffffffffu, wait(x_full(xs), xph, 0))) break;
             uint32_t hi[32], lo[32];
             {
-                const uint8_t* xrow = smem_gen + C::kOffX + xs * kXStageBytes + row * 128;
+                const uint8_t* xrow = smem_gen + C::kOffX + xs * kSlabBytes + row * 128;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    // 128-B swizzle: the 16-B chunk index is XORed with (row mod 8)
-                    const float4 v = *reinterpret_cast<const float4*>(xrow + ((j ^ (row & 7)) << 4));
-                    const float f[4] = {v.x, v.y, v.z, v.w};
+                    // 128-byte swizzle: the 16-byte chunk index is XORed with (row mod 8)
+                    const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((j ^ (row & 7)) << 4));
+                    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        const uint32_t h = tf32_rna_bits(f[q]);
-                        hi[j * 4 + q] = h;
-                        if (kPasses == 3) lo[j * 4 + q] = tf32_rna_bits(f[q] - __uint_as_float(h));
+                        hi[j * 4 + q] = u[q];
+                        if (kPasses == 3)
+                            lo[j * 4 + q] = __float_as_uint(__uint_as_float(u[q]) - __uint_as_float(u[q] & 0xffffe000u));
                     }
                 }
             }
             mbar_arrive(x_empty(xs));
-            if (++xs == kXStages) { xs = 0; xph ^= 1u; }
-            if (!__all_sync(0xffffffffu, mbar_wait(a_empty(as), aph ^ 1u, abort_flag))) break;
+            if (++xs == XS) { xs = 0; xph ^= 1u; }
+            if (!__all_sync(0xffffffffu, wait(a_empty(as), aph ^ 1u, 1))) break;
             tc_fence_after();
             const uint32_t a_hi = tmem_lane + C::kAccCols + as * C::kAStageCols;
             tmem_st32(a_hi, hi);
@@ -271,12 +318,17 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(a_full(as));
-            if (++as == C::kAStages) { as = 0; aph ^= 1u; }
+            if (++as == AS) { as = 0; aph ^= 1u; }
+        }
+        if (tracing && warp == 3 && lane == 0) {
+            p.trace[kTrXfXFull] = tr[0];
+            p.trace[kTrXfAEmpty] = tr[1];
+            p.trace[kTrXfTotal] = clock64() - t_role0;
         }
     } else {
         // ------------------------------------------------------------------ drain (promotion + epilogue)
-        const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;
+        const int quarter = warp & 3;          // tensor-memory lane quarter this warp may access
+        const int row = quarter * 32 + lane;   // token inside the tile = tensor-memory lane
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         const int64_t tok = tok0 + row;
         const bool live = tok < p.m;
@@ -310,32 +362,36 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         uint32_t ready_ph = 0;  // bit r: parity of the next p_ready[r] phase
         uint32_t seen = 0;      // bit r: the row has been written once
         bool ok = true;
-        for (int e = e0; e < e1; ++e) {
-            const PlanEntry ent = es.get(e);
-            if (!(ent.flags & kPlanDrain)) continue;
-            const int r = ent.row;
-            ok = __all_sync(0xffffffffu, mbar_wait(p_ready(r), (ready_ph >> r) & 1u, abort_flag));
-            if (!ok) break;
-            ready_ph ^= 1u << r;
-            tc_fence_after();
-            uint32_t main_[32];
-            float v[32];
-            tmem_ld32(tmem_lane + r * C::kRowCols, main_);
-            if (kPasses == 3) {
-                uint32_t corr[32];
-                tmem_ld32(tmem_lane + r * C::kRowCols + 32, corr);
-                tmem_wait_ld();
+        for (int base = e0; base < e1 && ok; base += 32) {
+            const int4 mine = fetch(base + lane);  // 32 entries per warp-wide load
+            const int count = min(32, e1 - base);
+            for (int i = 0; i < count; ++i) {
+                const int flags = __shfl_sync(0xffffffffu, mine.w, i);
+                if (!(flags & kPlanDrain)) continue;
+                const int r = __shfl_sync(0xffffffffu, mine.z, i);
+                ok = __all_sync(0xffffffffu, wait(p_ready(r), (ready_ph >> r) & 1u, 0));
+                if (!ok) break;
+                ready_ph ^= 1u << r;
+                tc_fence_after();
+                uint32_t main_[32];
+                float v[32];
+                tmem_ld32(tmem_lane + r * C::kRowCols, main_);
+                if (kPasses == 3) {
+                    uint32_t corr[32];
+                    tmem_ld32(tmem_lane + r * C::kRowCols + 32, corr);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]) + __uint_as_float(corr[j]);
-            } else {
-                tmem_wait_ld();
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]) + __uint_as_float(corr[j]);
+                } else {
+                    tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]);
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]);
+                }
+                tc_fence_before();
+                mbar_arrive(p_taken(r));
+                emit(r, v, !((seen >> r) & 1u));
+                seen |= 1u << r;
             }
-            tc_fence_before();
-            mbar_arrive(p_taken(r));
-            emit(r, v, !((seen >> r) & 1u));
-            seen |= 1u << r;
         }
         if (ok) {
             // block-rows without any block: bias (or zero)
@@ -344,6 +400,10 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
             for (int j = 0; j < 32; ++j) z[j] = 0.f;
             for (int r = 0; r < nrows; ++r)
                 if (!((seen >> r) & 1u)) emit(r, z, true);
+        }
+        if (tracing && warp == 7 && lane == 0) {
+            p.trace[kTrDrainPReady] = tr[0];
+            p.trace[kTrDrainTotal] = clock64() - t_role0;
         }
     }
 
@@ -387,7 +447,15 @@ cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const DsdParams& p, int64_t 
     return cudaGetLastError();
 }
 
+long long* g_trace_buffer = nullptr;  // host-side: device buffer the next dsd launches trace into
+int g_trace_block = 0;
+
 }  // namespace
+
+void set_dsd_trace(long long* device_buffer, int block) {
+    g_trace_buffer = device_buffer;
+    g_trace_block = block;
+}
 
 cudaError_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,
                          uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
@@ -434,7 +502,7 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     if (groups * tiles > 0x7fffffffll || m > 0x7fffffffll) return cudaErrorInvalidValue;
 
     // The box never exceeds the tensor: with fewer than 128 tokens the slab load fills only the first
-    // m rows; the remaining tensor-memory lanes hold stale values whose outputs are never stored.
+    // m rows; the remaining accumulator lanes see stale values and their outputs are never stored.
     const uint32_t box_rows = (uint32_t)(m < kTileTokens ? m : kTileTokens);
     CUtensorMap tmap_a;
     cudaError_t err = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)k, (uint64_t)m, 32,
@@ -444,6 +512,7 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     DsdParams p;
     p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * (int64_t)kImage32Bytes : 0);
     p.group_off = static_cast<const int32_t*>(plan);
+    p.group_slabs = p.group_off + groups + 1;
     p.entries = reinterpret_cast<const PlanEntry*>(static_cast<const uint8_t*>(plan) +
                                                    plan_entries_offset(n_out_blocks, group));
     p.bias = bias;
@@ -456,9 +525,15 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     p.groups = (int32_t)groups;
     p.out_colmajor = out_colmajor ? 1 : 0;
     p.x_bytes = box_rows * 128u;
+    p.trace = g_trace_buffer;
+    p.trace_block = g_trace_block;
     const bool split = precision == BSMM_PREC_TF32X3;
-    if (group == 4) return split ? launch_dsd_g<4, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, p, tiles, stream);
-    return split ? launch_dsd_g<6, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, p, tiles, stream);
+    if (split && group == 8) return cudaErrorInvalidValue;  // 8 rows x 64 columns leave no tensor memory for A
+    switch (group) {
+        case 4: return split ? launch_dsd_g<4, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, p, tiles, stream);
+        case 6: return split ? launch_dsd_g<6, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, p, tiles, stream);
+        default: return launch_dsd_g<8, 1>(tmap_a, p, tiles, stream);
+    }
 }
 
 cudaError_t read_device_status(unsigned int* status, bool clear) {

@@ -23,14 +23,15 @@ constexpr int32_t kPlanDrain = 4;  // after this entry the row's tensor-memory p
 // small correction terms, so 32 blocks cost 128 accumulations of the main term: about 3e-6.
 constexpr int kDrainEvery = 32;
 
-inline bool plan_group_valid(int group) { return group == 4 || group == 6; }
+inline bool plan_group_valid(int group) { return group == 4 || group == 6 || group == 8; }
 
-// Plan buffer: [group offsets: n_groups + 1 int32, padded to 16 B][entries: nnz PlanEntry]
+// Plan buffer: [group offsets: n_groups + 1 int32][slabs per group: n_groups int32][pad to 16 B]
+//              [entries: nnz PlanEntry]
 __host__ __device__ constexpr int64_t plan_groups(int64_t n_out_blocks, int group) {
     return (n_out_blocks + group - 1) / group;
 }
 __host__ __device__ constexpr int64_t plan_entries_offset(int64_t n_out_blocks, int group) {
-    return ((plan_groups(n_out_blocks, group) + 1) * 4 + 15) / 16 * 16;
+    return ((2 * plan_groups(n_out_blocks, group) + 1) * 4 + 15) / 16 * 16;
 }
 __host__ __device__ constexpr int64_t plan_bytes(int64_t n_out_blocks, int64_t nnz, int group) {
     return plan_entries_offset(n_out_blocks, group) + (nnz > 0 ? nnz : 1) * (int64_t)sizeof(PlanEntry);
@@ -51,6 +52,10 @@ int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, i
 cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens,
                               float* sparse_c, const int32_t* csr_idx, const void* plan, int64_t nnz,
                               float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream);
+
+// Diagnostics: the following dsd launches record, for CTA `block`, the cycles each warp role spent in
+// each kind of wait into `device_buffer` (32 int64, see TraceSlot in bsmm_umma.cu); null switches it off.
+void set_dsd_trace(long long* device_buffer, int block);
 
 // 2-D tiled tensor map over a row-major [outer, inner] array.
 cudaError_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* base,

@@ -25,6 +25,7 @@ EXPORTS = (
     "bsmm_status_string",
     "bsmm_last_cuda_error",
     "bsmm_device_status",
+    "bsmm_debug_trace_dsd",
     "bsmm_packed_bytes",
     "bsmm_pack_weights",
     "bsmm_plan_group",
@@ -66,12 +67,14 @@ def load():
     lib.bsmm_last_cuda_error.argtypes = []
     lib.bsmm_device_status.restype = i32
     lib.bsmm_device_status.argtypes = [c.POINTER(c.c_uint), i32]
+    lib.bsmm_debug_trace_dsd.restype = i32
+    lib.bsmm_debug_trace_dsd.argtypes = [vp, i32]
     lib.bsmm_packed_bytes.restype = i64
     lib.bsmm_packed_bytes.argtypes = [i64, u32]
     lib.bsmm_pack_weights.restype = i32
     lib.bsmm_pack_weights.argtypes = [vp, i64, u32, vp, vp, vp]
     lib.bsmm_plan_group.restype = i32
-    lib.bsmm_plan_group.argtypes = [i64, i64, i64]
+    lib.bsmm_plan_group.argtypes = [i64, i64, i64, u32]
     lib.bsmm_plan_bytes.restype = i64
     lib.bsmm_plan_bytes.argtypes = [i64, i64, i32]
     lib.bsmm_build_plan.restype = i32
@@ -179,11 +182,11 @@ class DsdPlan:
         self.nnz = idx.shape[0]
         self._buffers = {}
 
-    def group_for(self, m):
+    def group_for(self, m, precision):
         forced = os.environ.get("BSMM_PLAN_GROUP")
         if forced:
-            return int(forced)
-        return load().bsmm_plan_group(m, self.n_out_blocks, self.nnz)
+            return min(int(forced), 6) if precision == PREC_TF32X3 else int(forced)
+        return load().bsmm_plan_group(m, self.n_out_blocks, self.nnz, precision)
 
     def buffer(self, group):
         buf = self._buffers.get(group)
@@ -219,7 +222,7 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
     flags = prec | (0 if transpose else DSD_DGRAD) | (DSD_OUT_COLMAJOR if out_colmajor else 0)
     plan_buf = None
     if prec != PREC_FP32_SIMT:
-        group = plan.group_for(m)
+        group = plan.group_for(m, prec)
         plan_buf = plan.buffer(group)
         flags |= group << 8
     if bias is not None and bias.dtype != torch.float32:

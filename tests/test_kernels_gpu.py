@@ -219,7 +219,7 @@ def test_pack_statistic_matches_block_norm():
         assert np.allclose(got, want, rtol=1e-5)
 
 
-@pytest.mark.parametrize("group", [4, 6])
+@pytest.mark.parametrize("group", [4, 6, 8])
 def test_plan_is_the_group_merge_of_the_csr(group):
     m = make_matrix((512, 2048), n_blocks=700, seed=8)  # rows of ~44 blocks: promotions inside a row
     plan = m._plan(True)
@@ -228,7 +228,8 @@ def test_plan_is_the_group_merge_of_the_csr(group):
     raw = raw.cpu().numpy()
     groups = (16 + group - 1) // group
     off = raw[: (groups + 1) * 4].view(np.int32)
-    ent_off = ((groups + 1) * 4 + 15) // 16 * 16
+    slabs = raw[(groups + 1) * 4: (2 * groups + 1) * 4].view(np.int32)
+    ent_off = ((2 * groups + 1) * 4 + 15) // 16 * 16
     ent = raw[ent_off: ent_off + plan.nnz * 16].view(np.int32).reshape(-1, 4)
     ptr = m.row_start_ends_a.cpu().numpy()
     idx = m.cols_a.cpu().numpy()
@@ -239,6 +240,7 @@ def test_plan_is_the_group_merge_of_the_csr(group):
         assert off[g] == ptr[g * group]
         got = ent[off[g]: off[g + 1]]
         assert [(int(c), int(r), int(s)) for c, s, r, _ in got] == want
+        assert slabs[g] == len({c for c, _, _ in want})
         seen = {}
         for i, (c, s, r, flags) in enumerate(got):
             first = i == 0 or got[i - 1][0] != c
@@ -249,7 +251,7 @@ def test_plan_is_the_group_merge_of_the_csr(group):
             assert flags == (1 if first else 0) | (2 if last else 0) | (4 if drain else 0)
 
 
-@pytest.mark.parametrize("group", ["4", "6"])
+@pytest.mark.parametrize("group", ["4", "6", "8"])
 def test_dsd_every_tile_width(group, monkeypatch):
     monkeypatch.setenv("BSMM_PLAN_GROUP", group)
     m = make_matrix((416, 352), n_blocks=70, seed=21)  # 13 x 11 blocks: ragged last group for every width
