@@ -134,6 +134,32 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
                const int32_t* blocks, int64_t nnz, const int32_t* csr_idx, const void* plan, float* block_sumsq,
                void* workspace, uint32_t flags, bsmm_stream_t stream);
 
+/*
+ * bsmm_sddmm for callers that cannot allocate device memory.  No counterpart in the reference.
+ *
+ * Some hosts of this library may not call cudaMalloc at the point where the weight gradient is
+ * needed: code running while a CUDA graph is being captured, or inside a memory pool / allocator
+ * callback, an inference or training runtime that hands out all device memory up front and forbids
+ * later allocation, a real-time loop that must not take the allocator's locks.  bsmm_sddmm asks such
+ * a caller for a `workspace`; this variant takes none.  The partial results of the token ranges go to
+ * a scratch array that is part of the library image (file scope, BSMM_SDDMM_STATIC_MAX_BYTES, held by
+ * every GPU that loads the library until the process exits).
+ *
+ * Same arguments and result as bsmm_sddmm without `workspace`; the caller still owns every input and
+ * the output.  Returns BSMM_ERR_TOO_LARGE when bsmm_sddmm_workspace_bytes(...) for the problem exceeds
+ * BSMM_SDDMM_STATIC_MAX_BYTES.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current) and keeps it; make that first call before any stream capture begins.
+ * All calls on one device share the one array and nothing is cleared between calls (every byte a call
+ * reads it has written itself first): two calls whose kernels overlap on the GPU -- different streams,
+ * or different host threads -- race on it and corrupt each other's result.  Serialise them.
+ */
+#define BSMM_SDDMM_STATIC_MAX_BYTES (64u << 20)
+int bsmm_sddmm_static(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens, float* sparse_c,
+                      const int32_t* blocks, int64_t nnz, const int32_t* csr_idx, const void* plan,
+                      float* block_sumsq, uint32_t flags, bsmm_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -174,4 +174,23 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
                                                b_col, rows, cols, tokens, sparse_c, blocks, nnz, block_sumsq, s));
 }
 
+int bsmm_sddmm_static(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens, float* sparse_c,
+                      const int32_t* blocks, int64_t nnz, const int32_t* csr_idx, const void* plan,
+                      float* block_sumsq, uint32_t flags, bsmm_stream_t stream) {
+    // How much scratch would bsmm_sddmm want for this problem?  (Zero when the token axis is not split or
+    // the CUDA-core kernel will run: then the static array is not touched at all.)
+    const int64_t need = (csr_idx != nullptr && plan != nullptr)
+                             ? bsmm_sddmm_workspace_bytes(rows, cols, tokens, nnz, flags)
+                             : 0;
+    if (need < 0) return BSMM_ERR_INVALID_ARGUMENT;
+    if (need > (int64_t)BSMM_SDDMM_STATIC_MAX_BYTES) return BSMM_ERR_TOO_LARGE;
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    // first call on this device: resolves the device address of the file-scope array
+    const cudaError_t err = bsmm::sddmm_static_scratch(&scratch, &scratch_bytes);
+    if (err != cudaSuccess) return cuda_status(err);
+    return bsmm_sddmm(a, b, rows, cols, tokens, sparse_c, blocks, nnz, csr_idx, plan, block_sumsq,
+                      need > 0 ? scratch : nullptr, flags, stream);
+}
+
 }  // extern "C"

@@ -414,6 +414,11 @@ sddmm_reduce_kernel(const float* __restrict__ ws, int splits, int64_t split_stri
     }
 }
 
+// Scratch of bsmm_sddmm_static: the per-token-range partial results live here instead of in a
+// caller-provided workspace.  Every GPU that loads the library holds these bytes until exit.
+constexpr size_t kStaticScratchBytes = BSMM_SDDMM_STATIC_MAX_BYTES;
+static __device__ __align__(256) unsigned char g_sddmm_static_scratch[kStaticScratchBytes];
+
 int64_t max_items(int64_t n_rows, int64_t nnz) { return nnz / kItemBlocks + n_rows; }
 
 // token ranges: enough CTAs for a few waves over 148 SMs, each range a multiple of 256 tokens
@@ -433,6 +438,27 @@ void choose_splits(int64_t n_rows, int64_t nnz, int64_t tokens, int64_t* splits,
 }
 
 }  // namespace
+
+// Device address of the static scratch array on the current device.  In host code the array's name
+// is only a host-side stand-in for the symbol; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+cudaError_t sddmm_static_scratch(void** ptr, size_t* bytes) {
+    constexpr int kMaxDevices = 64;
+    static void* cache[kMaxDevices] = {nullptr};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (cache[dev] == nullptr) {
+        void* p = nullptr;
+        err = cudaGetSymbolAddress(&p, g_sddmm_static_scratch);
+        if (err != cudaSuccess) return err;
+        cache[dev] = p;
+    }
+    *ptr = cache[dev];
+    *bytes = kStaticScratchBytes;
+    return cudaSuccess;
+}
 
 int64_t sddmm_plan_bytes(int64_t n_rows, int64_t nnz) { return 16 + 16 * max_items(n_rows, nnz); }
 

@@ -53,6 +53,10 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
                               float* sparse_c, const int32_t* csr_idx, const void* plan, int64_t nnz,
                               float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream);
 
+// Address and size of the library's static scratch array on the current device (first call per
+// device resolves the symbol).
+cudaError_t sddmm_static_scratch(void** ptr, size_t* bytes);
+
 // Diagnostics: the following dsd launches record, for CTA `block`, the cycles each warp role spent in
 // each kind of wait into `device_buffer` (32 int64, see TraceSlot in bsmm_umma.cu); null switches it off.
 void set_dsd_trace(long long* device_buffer, int block);

@@ -36,6 +36,7 @@ EXPORTS = (
     "bsmm_build_sddmm_plan",
     "bsmm_sddmm_workspace_bytes",
     "bsmm_sddmm",
+    "bsmm_sddmm_static",
 )
 
 _lib = None
@@ -85,6 +86,8 @@ def load():
     lib.bsmm_sddmm_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
     lib.bsmm_sddmm.restype = i32
     lib.bsmm_sddmm.argtypes = [vp, vp, i64, i64, i64, vp, vp, i64, vp, vp, vp, vp, u32, vp]
+    lib.bsmm_sddmm_static.restype = i32
+    lib.bsmm_sddmm_static.argtypes = [vp, vp, i64, i64, i64, vp, vp, i64, vp, vp, vp, u32, vp]
     lib.bsmm_sddmm_plan_bytes.restype = i64
     lib.bsmm_sddmm_plan_bytes.argtypes = [i64, i64]
     lib.bsmm_build_sddmm_plan.restype = i32
@@ -255,6 +258,32 @@ class SddmmPlan:
                 lib.bsmm_build_sddmm_plan(_ptr(ptr), n_rows, nnz, _ptr(self.buffer), _stream(ptr.device)),
                 "bsmm_build_sddmm_plan",
             )
+
+
+SDDMM_STATIC_MAX_BYTES = 64 << 20
+
+
+def sddmm_static(a, b, blocks, out, plan, block_sumsq=None):
+    """``bsmm_sddmm_static``: the weight gradient for callers that may not allocate device memory (stream
+    capture in progress, a runtime that owns all device memory, allocator callbacks).  The token-range
+    partial sums go to a scratch array inside the library image instead of a torch-allocated workspace;
+    this wrapper itself allocates nothing.  ``a``: dY ``[tokens, rows]``, ``b``: X ``[tokens, cols]``, both
+    contiguous fp32; problems whose scratch need exceeds ``SDDMM_STATIC_MAX_BYTES`` are refused.  Calls
+    that overlap on the GPU share the array and race; make the first call per device outside any capture."""
+    _need_cuda(a, "dense_a")
+    lib = load()
+    tokens, rows = a.shape
+    cols = b.shape[1]
+    nnz = blocks.shape[0] // 2
+    with torch.cuda.device(a.device):
+        check(
+            lib.bsmm_sddmm_static(
+                _ptr(a), _ptr(b), rows, cols, tokens, _ptr(out), _ptr(blocks), nnz, _ptr(plan.idx), _ptr(plan.buffer),
+                _ptr(block_sumsq), PREC_TF32X3, _stream(a.device),
+            ),
+            "bsmm_sddmm_static",
+        )
+    return out
 
 
 def sddmm(a, a_rowmajor, b, b_rowmajor, blocks, out, precision=None, block_sumsq=None, plan=None):
