@@ -380,6 +380,18 @@ def run_gpu_arm(args, cfg):
         comparators["cublas_dense_bf16_ms"] = time_op(dense_bf16, 3)
         del xb, dyb, wb, yb, dxb, wd
 
+        # the reference's own SIMT kernels rebuilt for sm_100a (oracle/_ref, built by oracle/build_ref.py);
+        # they launch on the legacy default stream, which is the stream timed here
+        from oracle import ref_cuda
+
+        if ref_cuda.available() and m * max(n, k) < 2 ** 31:
+            def reference_step():
+                ref_cuda.reverse_matmul(w, x, True)
+                ref_cuda.reverse_matmul(w, dy, False)
+                ref_cuda.sddmm(w, dy, x)
+
+            comparators["reference_cuda_kernels_ms"] = time_op(reference_step, 3)
+
     # ---- roofline of the dominant kernel ----
     peaks = measured_peaks()
     op_names = {"fwd_ms": "dsd forward", "dgrad_ms": "dsd dgrad", "wgrad_ms": "sddmm wgrad"}
