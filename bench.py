@@ -242,7 +242,7 @@ def run_gpu_arm(args, cfg):
     y = torch.empty(m, n, device=dev)
     dx = torch.empty(m, k, device=dev)
     dw = torch.empty_like(w.data)
-    plan_f, plan_d = w._plan(True), w._plan(False)
+    plan_f, plan_d, plan_w = w._plan(True), w._plan(False), w._sddmm_plan()
     bias = lin.bias.detach()
     data = w.data.detach()
 
@@ -252,13 +252,13 @@ def run_gpu_arm(args, cfg):
         packed = native.pack_weights(data, prec)
         native.dsd_matmul(x, plan_f, packed, n, True, bias=bias, out=y)
         native.dsd_matmul(dy, plan_d, packed, k, False, out=dx)
-        native.sddmm(dy, True, x, True, w.blocks, dw, precision=prec)
+        native.sddmm(dy, True, x, True, w.blocks, dw, precision=prec, plan=plan_w)
         if world > 1:
             dist.all_reduce(dw)
         return packed
 
-    # kernels of this library launched per step: pack, fwd, dgrad, wgrad
-    launches_per_step = 4
+    # kernels of this library launched per step: pack, fwd, dgrad, wgrad (+ its token-range reduction)
+    launches_per_step = 5 if native.load().bsmm_sddmm_workspace_bytes(n, k, m, nnz, prec) > 0 else 4
 
     def barrier():
         if world > 1:
@@ -310,7 +310,7 @@ def run_gpu_arm(args, cfg):
         "pack_ms": time_op(lambda: native.pack_weights(data, prec), reps),
         "fwd_ms": time_op(lambda: native.dsd_matmul(x, plan_f, packed, n, True, bias=bias, out=y), reps),
         "dgrad_ms": time_op(lambda: native.dsd_matmul(dy, plan_d, packed, k, False, out=dx), reps),
-        "wgrad_ms": time_op(lambda: native.sddmm(dy, True, x, True, w.blocks, dw, precision=prec), reps),
+        "wgrad_ms": time_op(lambda: native.sddmm(dy, True, x, True, w.blocks, dw, precision=prec, plan=plan_w), reps),
     }
 
     # ---- end to end through the public layer API with host buffers ----

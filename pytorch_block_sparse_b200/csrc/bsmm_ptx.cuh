@@ -162,6 +162,12 @@ __device__ __forceinline__ uint64_t smem_desc_noswizzle(uint32_t addr, uint32_t 
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     return smem_desc_noswizzle(addr, lbo_bytes, sbo_bytes) | (2ull << 61);
 }
+// Same with the "128-byte swizzle, 32-byte atomicity" mode (layout type 1), the only layout the tensor
+// core accepts for MN-major operands of 32-bit element types; TMA writes it with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.  Its swizzle atom is 4 k-rows of 128 bytes.
+__device__ __forceinline__ uint64_t smem_desc_sw128_base32(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return smem_desc_noswizzle(addr, lbo_bytes, sbo_bytes) | (1ull << 61);
+}
 // Instruction descriptor, fp32 accumulate.  fmt: 0 f16, 1 bf16, 2 tf32.  *_mn_major: operand is
 // MN-major (its M/N index is the contiguous one) instead of K-major.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t m, uint32_t n, bool a_mn_major,

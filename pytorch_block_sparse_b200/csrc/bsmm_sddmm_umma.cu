@@ -6,16 +6,17 @@
 //
 // A CTA owns one "item": up to 16 blocks of ONE block-row R (a CSR row segment) and one range of
 // tokens.  Four blocks of the row form a chunk and fill the 128 rows of one MMA:
-//   D[128 = 4 blocks x 32 c, 32 = r] += A[128 x K] * B[32 x K]^T,   K = tokens, 8 per instruction,
-// A = the four blocks' X slabs, transposed on the way into tensor memory (lane = feature c, column =
-// token), B = the dY slab of row R, shared by every chunk of the item.  D is already the block's
-// storage layout (row c holds 32 consecutive r), so the epilogue writes plain 128-byte rows.
+//   D[128 = 4 blocks x 32 c, 32 = r] += A[128 x K] * B[32 x K]^T,   K = tokens, 8 per instruction.
+// Both operands are token-major in memory, i.e. MN-major for the MMA: a TMA box of 32 tokens x 32
+// features with the 128-byte / 32-byte-atom swizzle IS the canonical MN-major tf32 operand tile (one 128-byte row per
+// token), so the slabs are consumed where TMA put them, without transposition:
+//   A = the four X slabs of the chunk (atoms 4 KiB apart), B = the dY slab of row R.
+// D is already the block's storage layout (row c holds 32 consecutive r).
 //
-//   warp 0    producer : TMA tensor loads of [32 tokens x 32 features] fp32 boxes: one dY slab per
-//                        step, four X slabs per chunk
-//   warps 2-5 transform: per step the dY slab -> tf32 operand image [hi ; lo] in shared memory (K-major,
-//                        un-swizzled); per chunk the X slabs, read column-wise, split hi/lo, tcgen05.st
-//   warp 1    MMA      : per chunk and k-step  x_hi x [dy_hi ; dy_lo] (N = 64) and x_lo x dy_hi (N = 32),
+//   warp 0    producer : TMA tensor loads: one dY slab per 32-token step, four X slabs per chunk
+//   warps 2-5 split    : lo = v - trunc_tf32(v) of every slab into a second tile of the same layout
+//                        (the tensor core reads only the tf32 bits of an operand, so the raw slab is hi)
+//   warp 1    MMA      : per chunk and k-step (8 tokens)  x x [dy ; dy_lo] (N = 64) and x_lo x dy (N = 32),
 //                        tcgen05.mma kind::tf32, M = 128: main | correction columns of the chunk
 //   warps 6-9 drain    : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
 //                        (fp32, round to nearest) to the chunk's master tile in shared memory; final
@@ -36,26 +37,26 @@ constexpr int kChunks = 4;                 // chunks (of 4 blocks) per item
 constexpr int kItemBlocks = 4 * kChunks;   // 16
 constexpr int kStepTokens = 32;
 constexpr int kDrainSteps = 32;            // promote every 1024 tokens: 128 accumulations of the main term
-constexpr uint32_t kSlabBytes = 32 * 32 * 4;            // 4 KiB: [32 tokens][32 features]
-constexpr uint32_t kXStageBytes = 4 * kSlabBytes;       // one chunk's X slabs
+constexpr uint32_t kSlabBytes = 32 * 32 * 4;            // 4 KiB: [32 tokens][32 features], 128-byte rows
+constexpr uint32_t kKStepBytes = 8 * 128;               // one MMA k-step = 8 token rows
+constexpr uint32_t kXHalfBytes = 4 * kSlabBytes;        // one chunk's four X slabs
+constexpr uint32_t kXStageBytes = 2 * kXHalfBytes;      // raw slabs | their lo parts
+constexpr uint32_t kDyStageBytes = 2 * kSlabBytes;      // raw slab | its lo part
 constexpr uint32_t kMasterBytes = 128 * 32 * 4;         // 16 KiB per chunk
-constexpr int kXStages = 6, kDyStages = 2, kBStages = 2, kAStages = 4;
-constexpr uint32_t kTmemCols = 512;
+constexpr int kXStages = 4, kDyStages = 3;
+constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kChunkCols = 64;                     // main | correction
-constexpr uint32_t kAccCols = kChunks * kChunkCols;     // 256
-constexpr uint32_t kAStageCols = 64;                    // hi | lo
 constexpr int kThreads = 320;
 
 constexpr uint32_t kOffMaster = 0;
 constexpr uint32_t kOffX = kOffMaster + kChunks * kMasterBytes;
 constexpr uint32_t kOffDy = kOffX + kXStages * kXStageBytes;
-constexpr uint32_t kOffBImg = kOffDy + kDyStages * kSlabBytes;
-constexpr uint32_t kOffBar = kOffBImg + kBStages * kImage32Bytes;
-constexpr int kNumBars = 2 * kXStages + 2 * kDyStages + 2 * kBStages + 2 * kAStages + 2 * kChunks;
+constexpr uint32_t kOffBar = kOffDy + kDyStages * kDyStageBytes;
+constexpr int kNumBars = 3 * kXStages + 3 * kDyStages + 2 * kChunks;
 constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
 static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
-static_assert(kAccCols + kAStages * kAStageCols <= kTmemCols, "tensor memory over-subscribed");
+static_assert(kChunks * kChunkCols <= kTmemCols, "tensor memory over-subscribed");
 
 // Item table: [0] = item count; item i at int32 offsets 4 + 4*i: {block-row, first CSR entry, blocks, 0}
 struct SddmmParams {
@@ -68,6 +69,13 @@ struct SddmmParams {
     int64_t tokens_per_split;  // multiple of kStepTokens
     int64_t split_stride;      // floats between two splits' partial results
 };
+
+// MN-major tf32 operand made of swizzle atoms of 4 k-rows x 128 bytes of the M/N axis (128-byte swizzle
+// with 32-byte atomicity): atoms along M/N are `atom_stride` bytes apart (leading byte offset), the
+// 4-row groups along K follow each other at 512 bytes (stride byte offset).
+__device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint32_t atom_stride) {
+    return smem_desc_sw128_base32(addr, atom_stride, 512);
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
@@ -85,28 +93,22 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar0 = smem_base + kOffBar;
-    auto x_full = [&](int s) { return bar0 + 8u * s; };
-    auto x_empty = [&](int s) { return bar0 + 8u * (kXStages + s); };
-    auto dy_full = [&](int s) { return bar0 + 8u * (2 * kXStages + s); };
-    auto dy_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + kDyStages + s); };
-    auto b_full = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + s); };
-    auto b_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + kBStages + s); };
-    auto a_full = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + 2 * kBStages + s); };
-    auto a_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + 2 * kBStages + kAStages + s); };
-    auto p_ready = [&](int c) { return bar0 + 8u * (2 * kXStages + 2 * kDyStages + 2 * kBStages + 2 * kAStages + c); };
-    auto p_taken = [&](int c) {
-        return bar0 + 8u * (2 * kXStages + 2 * kDyStages + 2 * kBStages + 2 * kAStages + kChunks + c);
-    };
+    auto x_full = [&](int s) { return bar0 + 8u * s; };                       // TMA delivered the chunk's slabs
+    auto xlo_full = [&](int s) { return bar0 + 8u * (kXStages + s); };        // split warps wrote their lo parts
+    auto x_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + s); };     // the MMAs reading the stage completed
+    auto dy_full = [&](int s) { return bar0 + 8u * (3 * kXStages + s); };
+    auto dylo_full = [&](int s) { return bar0 + 8u * (3 * kXStages + kDyStages + s); };
+    auto dy_empty = [&](int s) { return bar0 + 8u * (3 * kXStages + 2 * kDyStages + s); };
+    auto p_ready = [&](int c) { return bar0 + 8u * (3 * kXStages + 3 * kDyStages + c); };
+    auto p_taken = [&](int c) { return bar0 + 8u * (3 * kXStages + 3 * kDyStages + kChunks + c); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + kOffMisc);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kXStages; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); }
-        for (int s = 0; s < kDyStages; ++s) { mbar_init(dy_full(s), 1); mbar_init(dy_empty(s), 128); }
-        for (int s = 0; s < kBStages; ++s) { mbar_init(b_full(s), 128); mbar_init(b_empty(s), 1); }
-        for (int s = 0; s < kAStages; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), 1); }
+        for (int s = 0; s < kXStages; ++s) { mbar_init(x_full(s), 1); mbar_init(xlo_full(s), 128); mbar_init(x_empty(s), 1); }
+        for (int s = 0; s < kDyStages; ++s) { mbar_init(dy_full(s), 1); mbar_init(dylo_full(s), 128); mbar_init(dy_empty(s), 1); }
         for (int c = 0; c < kChunks; ++c) { mbar_init(p_ready(c), 1); mbar_init(p_taken(c), 128); }
         misc[1] = 0;
         fence_mbar_init();
@@ -140,7 +142,7 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
             if (!ok) break;
             if (elect_one()) {
                 mbar_arrive_expect_tx(dy_full(ds), kSlabBytes);
-                tma_load_2d(smem_base + kOffDy + ds * kSlabBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
+                tma_load_2d(smem_base + kOffDy + ds * kDyStageBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
             }
             if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
             for (int ch = 0; ch < nchunks; ++ch) {
@@ -162,123 +164,95 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
-        constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
-        int bs = 0, as = 0;
-        uint32_t bph = 0, aph = 0;
+        constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, true, true);
+        constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, true, true);
+        int xs = 0, ds = 0;
+        uint32_t xph = 0, dph = 0;
         uint32_t pending = 0, taken_ph = 0;
         bool ok = true;
         for (int step = 0; step < nsteps && ok; ++step) {
-            ok = mbar_wait(b_full(bs), bph, abort_flag);
+            ok = mbar_wait(dylo_full(ds), dph, abort_flag);
             if (!ok) break;
-            const uint64_t b_desc = smem_desc_noswizzle(smem_base + kOffBImg + bs * kImage32Bytes, kImage32Lbo, kImage32Sbo);
+            // B: atom 0 = the raw dY slab, atom 1 (N = 64 only) = its lo part, one slab further
+            const uint64_t b_desc = smem_desc_mnmajor_sw128(smem_base + kOffDy + ds * kDyStageBytes, kSlabBytes);
             const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
             const bool drain = drain_step(step);
             for (int ch = 0; ch < nchunks; ++ch) {
-                ok = mbar_wait(a_full(as), aph, abort_flag);
+                ok = mbar_wait(xlo_full(xs), xph, abort_flag);
                 if (!ok) break;
                 if (fresh && ((pending >> ch) & 1u)) {
                     ok = mbar_wait(p_taken(ch), (taken_ph >> ch) & 1u, abort_flag);
                     if (!ok) break;
                     taken_ph ^= 1u << ch;
                     pending &= ~(1u << ch);
+                    tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the columns
                 }
-                tc_fence_after();
-                const uint32_t a_hi = tmem + kAccCols + as * kAStageCols;
+                // A: four atoms (the chunk's slabs) one slab apart; the lo parts follow kXHalfBytes further
+                const uint64_t a_desc = smem_desc_mnmajor_sw128(smem_base + kOffX + xs * kXStageBytes, kSlabBytes);
                 const uint32_t d = tmem + ch * kChunkCols;
                 const uint32_t acc0 = fresh ? 0u : 1u;
-                const uint32_t a_bar = a_empty(as), p_bar = p_ready(ch);
+                const uint32_t x_bar = x_empty(xs), p_bar = p_ready(ch);
                 if (elect_one()) {
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
-                        const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
-                        mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);   // x_hi x [dy_hi ; dy_lo]
-                        mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);       // x_lo x dy_hi
+                        const uint64_t a = a_desc + (uint64_t)(s * (kKStepBytes >> 4));
+                        const uint64_t b = b_desc + (uint64_t)(s * (kKStepBytes >> 4));
+                        mma_ss_tf32(d, a, b, idesc_wide, s == 0 ? acc0 : 1u);                          // x x [dy ; dy_lo]
+                        mma_ss_tf32(d + 32, a + (uint64_t)(kXHalfBytes >> 4), b, idesc_narrow, 1u);    // x_lo x dy
                     }
-                    mma_commit(a_bar);
+                    mma_commit(x_bar);
                     if (drain) mma_commit(p_bar);
                 }
-                if (++as == kAStages) { as = 0; aph ^= 1u; }
+                if (++xs == kXStages) { xs = 0; xph ^= 1u; }
                 if (drain) pending |= 1u << ch;
             }
             if (!ok) break;
-            const uint32_t b_bar = b_empty(bs);
-            if (elect_one()) mma_commit(b_bar);
-            if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+            const uint32_t dy_bar = dy_empty(ds);
+            if (elect_one()) mma_commit(dy_bar);
+            if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
         }
     } else if (warp < 6) {
-        // ------------------------------------------------------------------ transform
-        const int quarter = warp & 3;  // block position inside the chunk = tensor-memory lane quarter
-        const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
-        const int tt = (warp - 2) * 32 + lane;  // 0..127 over the four transform warps
-        int xs = 0, ds = 0, bs = 0, as = 0;
-        uint32_t xph = 0, dph = 0, bph = 0, aph = 0;
+        // ------------------------------------------------------------------ split
+        const int tt = (warp - 2) * 32 + lane;  // 0..127 over the four split warps
+        int xs = 0, ds = 0;
+        uint32_t xph = 0, dph = 0;
         bool ok = true;
+        // lo = v - trunc_tf32(v), elementwise at the same offset of the stage's second half: the 128-byte
+        // swizzle needs no decoding; consecutive threads take consecutive 16-byte chunks
+        auto split16 = [](const uint8_t* src, uint8_t* dst) {
+            const float4 v = *reinterpret_cast<const float4*>(src);
+            float4 l;
+            l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+            l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+            l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+            l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+            *reinterpret_cast<float4*>(dst) = l;
+        };
         for (int step = 0; step < nsteps && ok; ++step) {
-            // dY slab [32 tokens][32 r] -> B operand image B[n = r][k = token], hi and lo parts
             ok = __all_sync(0xffffffffu, mbar_wait(dy_full(ds), dph, abort_flag));
             if (!ok) break;
-            ok = __all_sync(0xffffffffu, mbar_wait(b_empty(bs), bph ^ 1u, abort_flag));
-            if (!ok) break;
             {
-                const int kk = tt >> 2;          // token of the step
-                const int r0 = (tt & 3) * 8;     // eight features
-                const float* src = reinterpret_cast<const float*>(smem_gen + kOffDy + ds * kSlabBytes) + kk * 32 + r0;
-                const float4 v0 = *reinterpret_cast<const float4*>(src);
-                const float4 v1 = *reinterpret_cast<const float4*>(src + 4);
-                const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                uint8_t* img = smem_gen + kOffBImg + bs * kImage32Bytes;
+                uint8_t* base = smem_gen + kOffDy + ds * kDyStageBytes;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t h = tf32_rna_bits(f[i]);
-                    *reinterpret_cast<uint32_t*>(img + image32_offset((uint32_t)(r0 + i), (uint32_t)kk, 0u)) = h;
-                    *reinterpret_cast<uint32_t*>(img + image32_offset((uint32_t)(r0 + i), (uint32_t)kk, 1u)) =
-                        tf32_rna_bits(f[i] - __uint_as_float(h));
-                }
+                for (int i = 0; i < 2; ++i) split16(base + (tt + 128 * i) * 16, base + kSlabBytes + (tt + 128 * i) * 16);
             }
             fence_proxy_async_smem();  // generic-proxy writes, read by the MMA through the async proxy
-            mbar_arrive(b_full(bs));
-            mbar_arrive(dy_empty(ds));
-            if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+            mbar_arrive(dylo_full(ds));
             if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
-
             for (int ch = 0; ch < nchunks; ++ch) {
                 const int nb = min(4, nblk - ch * 4);
                 ok = __all_sync(0xffffffffu, mbar_wait(x_full(xs), xph, abort_flag));
                 if (!ok) break;
-                uint32_t hi[32], lo[32];
-                if (quarter < nb) {
-                    // column `lane` of this quarter's slab: one feature, 32 tokens
-                    const float* col = reinterpret_cast<const float*>(smem_gen + kOffX + xs * kXStageBytes +
-                                                                      quarter * kSlabBytes) + lane;
-#pragma unroll
-                    for (int kk = 0; kk < 32; ++kk) {
-                        const float f = col[kk * 32];
-                        const uint32_t h = tf32_rna_bits(f);
-                        hi[kk] = h;
-                        lo[kk] = tf32_rna_bits(f - __uint_as_float(h));
-                    }
-                } else {
-#pragma unroll
-                    for (int kk = 0; kk < 32; ++kk) { hi[kk] = 0u; lo[kk] = 0u; }
-                }
-                mbar_arrive(x_empty(xs));
+                uint8_t* base = smem_gen + kOffX + xs * kXStageBytes;
+                for (int i = 0; i < 2 * nb; ++i) split16(base + (tt + 128 * i) * 16, base + kXHalfBytes + (tt + 128 * i) * 16);
+                fence_proxy_async_smem();
+                mbar_arrive(xlo_full(xs));
                 if (++xs == kXStages) { xs = 0; xph ^= 1u; }
-                ok = __all_sync(0xffffffffu, mbar_wait(a_empty(as), aph ^ 1u, abort_flag));
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t a_hi = tmem_lane + kAccCols + as * kAStageCols;
-                tmem_st32(a_hi, hi);
-                tmem_st32(a_hi + 32, lo);
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(a_full(as));
-                if (++as == kAStages) { as = 0; aph ^= 1u; }
             }
         }
     } else {
         // ------------------------------------------------------------------ drain + epilogue
-        const int quarter = warp & 3;
+        const int quarter = warp & 3;  // block position inside the chunk = tensor-memory lane quarter
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         // this thread's row (feature c = lane of block `quarter`) of chunk ch's master tile
         float* master = reinterpret_cast<float*>(smem_gen + kOffMaster) + (quarter * 32 + lane) * 32;
@@ -493,10 +467,10 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     if (err != cudaSuccess) return err;
     CUtensorMap tmap_x, tmap_dy;
     err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)cols, (uint64_t)tokens, 32,
-                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_NONE);
+                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (err != cudaSuccess) return err;
     err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)rows, (uint64_t)tokens, 32,
-                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_NONE);
+                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (err != cudaSuccess) return err;
 
     SddmmParams p;
