@@ -14,11 +14,11 @@
 // D is already the block's storage layout (row c holds 32 consecutive r).
 //
 //   warp 0    producer : TMA tensor loads: one dY slab per 32-token step, four X slabs per chunk
-//   warps 2-5 split    : lo = v - trunc_tf32(v) of every slab into a second tile of the same layout
+//   warps 3-6 split    : lo = v - trunc_tf32(v) of every slab into a second tile of the same layout
 //                        (the tensor core reads only the tf32 bits of an operand, so the raw slab is hi)
-//   warp 1    MMA      : per chunk and k-step (8 tokens)  x x [dy ; dy_lo] (N = 64) and x_lo x dy (N = 32),
+//   warps 1-2 MMA      : (chunks by parity) per chunk and k-step (8 tokens)  x x [dy ; dy_lo] (N = 64) and x_lo x dy (N = 32),
 //                        tcgen05.mma kind::tf32, M = 128: main | correction columns of the chunk
-//   warps 6-9 drain    : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
+//   warps 7-10 drain   : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
 //                        (fp32, round to nearest) to the chunk's master tile in shared memory; final
 //                        store of the master tiles to global
 //
@@ -46,7 +46,7 @@ constexpr uint32_t kMasterBytes = 128 * 32 * 4;         // 16 KiB per chunk
 constexpr int kXStages = 4, kDyStages = 3;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kChunkCols = 64;                     // main | correction
-constexpr int kThreads = 320;
+constexpr int kThreads = 352;  // producer, two MMA issuers, four split warps, four drain warps
 
 constexpr uint32_t kOffMaster = 0;
 constexpr uint32_t kOffX = kOffMaster + kChunks * kMasterBytes;
@@ -108,7 +108,7 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kXStages; ++s) { mbar_init(x_full(s), 1); mbar_init(xlo_full(s), 128); mbar_init(x_empty(s), 1); }
-        for (int s = 0; s < kDyStages; ++s) { mbar_init(dy_full(s), 1); mbar_init(dylo_full(s), 128); mbar_init(dy_empty(s), 1); }
+        for (int s = 0; s < kDyStages; ++s) { mbar_init(dy_full(s), 1); mbar_init(dylo_full(s), 128); mbar_init(dy_empty(s), 2); }
         for (int c = 0; c < kChunks; ++c) { mbar_init(p_ready(c), 1); mbar_init(p_taken(c), 128); }
         misc[1] = 0;
         fence_mbar_init();
@@ -162,8 +162,10 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                 if (++xs == kXStages) { xs = 0; xph ^= 1u; }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp <= 2) {
+        // ------------------------------------------------------------------ MMA issuers
+        // two warps share the chunks by parity; both walk every chunk so that their stage counters agree
+        const int mw = warp - 1;
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, true, true);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, true, true);
         int xs = 0, ds = 0;
@@ -178,6 +180,10 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
             const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
             const bool drain = drain_step(step);
             for (int ch = 0; ch < nchunks; ++ch) {
+                if ((ch & 1) != mw) {
+                    if (++xs == kXStages) { xs = 0; xph ^= 1u; }
+                    continue;
+                }
                 ok = mbar_wait(xlo_full(xs), xph, abort_flag);
                 if (!ok) break;
                 if (fresh && ((pending >> ch) & 1u)) {
@@ -211,9 +217,9 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
             if (elect_one()) mma_commit(dy_bar);
             if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
         }
-    } else if (warp < 6) {
+    } else if (warp < 7) {
         // ------------------------------------------------------------------ split
-        const int tt = (warp - 2) * 32 + lane;  // 0..127 over the four split warps
+        const int tt = (warp - 3) * 32 + lane;  // 0..127 over the four split warps
         int xs = 0, ds = 0;
         uint32_t xph = 0, dph = 0;
         bool ok = true;
