@@ -401,12 +401,21 @@ static __device__ __align__(256) unsigned char g_sddmm_static_scratch[kStaticScr
 
 int64_t max_items(int64_t n_rows, int64_t nnz) { return nnz / kItemBlocks + n_rows; }
 
-// token ranges: enough CTAs for a few waves over 148 SMs, each range a multiple of 256 tokens
-void choose_splits(int64_t n_rows, int64_t nnz, int64_t tokens, int64_t* splits, int64_t* tokens_per_split) {
+// Token ranges.  Two constraints: enough CTAs for a few waves over 148 SMs, and a range whose slice of
+// X and dY (tokens x (rows + cols) x 4 bytes) stays L2-resident (at most 64 MiB) while the successive
+// waves of items walk it -- otherwise every wave streams the slice from HBM again.
+void choose_splits(int64_t n_rows, int64_t cols, int64_t nnz, int64_t tokens, int64_t* splits,
+                   int64_t* tokens_per_split) {
     int64_t est_items = (nnz + kItemBlocks - 1) / kItemBlocks;
     if (est_items < n_rows && nnz >= n_rows) est_items = n_rows;
     if (est_items < 1) est_items = 1;
     int64_t want = (4 * 148 + est_items - 1) / est_items;
+    if (est_items > 148) {  // more than one wave per range: keep the range in L2
+        const int64_t bytes_per_token = (n_rows * 32 + cols) * 4;
+        const int64_t l2_tokens = (64ll << 20) / (bytes_per_token > 0 ? bytes_per_token : 1);
+        const int64_t for_l2 = (tokens + l2_tokens - 1) / (l2_tokens > 0 ? l2_tokens : 1);
+        if (for_l2 > want) want = for_l2 < 8 ? for_l2 : 8;  // bounded: every range costs a partial result
+    }
     const int64_t max_splits = (tokens + 1023) / 1024;  // about 1024 tokens per range at least
     if (want > max_splits) want = max_splits;
     if (want < 1) want = 1;
@@ -449,10 +458,9 @@ cudaError_t launch_build_sddmm_plan(const int32_t* ptr, int64_t n_rows, int64_t 
 }
 
 int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t precision) {
-    (void)cols;
     if (precision != BSMM_PREC_TF32X3 || tokens < kStepTokens || nnz == 0) return 0;
     int64_t splits, per;
-    choose_splits(rows / 32, nnz, tokens, &splits, &per);
+    choose_splits(rows / 32, cols, nnz, tokens, &splits, &per);
     return splits > 1 ? splits * nnz * (int64_t)kBlockElems * 4 : 0;
 }
 
@@ -464,7 +472,7 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     if (tokens > 0x7fffffffll) return cudaErrorInvalidValue;
     const int64_t n_rows = rows / 32;
     int64_t splits, per;
-    choose_splits(n_rows, nnz, tokens, &splits, &per);
+    choose_splits(n_rows, cols, nnz, tokens, &splits, &per);
     if (splits > 1 && workspace == nullptr) return cudaErrorInvalidValue;
     if (splits > 65535) return cudaErrorInvalidValue;
 
