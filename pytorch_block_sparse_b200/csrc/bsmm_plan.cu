@@ -34,7 +34,8 @@ build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx,
         int r = 0;
         while (r + 1 < nrows && rp[r + 1] <= e) ++r;
         int rank = 0;
-        bool before = false, after = false;
+        bool before = false, after = false, warp_after = false;
+        uint32_t warps_present = 0;
         for (int q = 0; q < nrows; ++q) {
             int lo = rp[q], hi = rp[q + 1];
             const int row_end = hi;
@@ -46,6 +47,8 @@ build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx,
             const bool present = lo < row_end && idx[lo].x == ent.x;
             if (present && q < r) { ++rank; before = true; }
             if (present && q > r) after = true;
+            if (present && q > r && (q % kDsdMmaWarps) == (r % kDsdMmaWarps)) warp_after = true;
+            if (present || q == r) warps_present |= 1u << (q % kDsdMmaWarps);
         }
         PlanEntry pe;
         pe.inner = ent.x;
@@ -54,7 +57,9 @@ build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx,
         // promote the row's partial sum after every kDrainEvery-th block of the row and after its last one
         const int ord = e - rp[r];
         const bool drain = ((ord + 1) % kDrainEvery) == 0 || e + 1 == rp[r + 1];
-        pe.flags = (before ? 0 : kPlanFirst) | (after ? 0 : kPlanLast) | (drain ? kPlanDrain : 0);
+        const int idle = kDsdMmaWarps - __popc(warps_present);
+        pe.flags = (before ? 0 : kPlanFirst) | (after ? 0 : kPlanLast | (idle << kPlanIdleShift)) |
+                   (drain ? kPlanDrain : 0) | (warp_after ? 0 : kPlanWarpLast);
         entries[base + rank] = pe;
         if (!before) atomicAdd(&slabs, 1);
     }

@@ -37,6 +37,9 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -50,6 +53,43 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
+}
+
+// A counter in shared memory as a publication flag: writers add with release semantics, readers poll with
+// acquire semantics.  Unlike a phase-parity barrier it cannot be misread by a waiter that skipped phases.
+__device__ __forceinline__ void smem_add_release(uint32_t addr, uint32_t value) {
+    asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;" ::"r"(addr), "r"(value) : "memory");
+}
+__device__ __forceinline__ uint32_t smem_load_acquire(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// Non-blocking test of the same condition (try_wait may suspend the warp for a while when the phase is open).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// How many consecutive stages of a ring of `stages` barriers (8 bytes apart from `bar0`) have completed
+// their awaited phase, starting with stage `stage` whose awaited parity is `parity` (stages that wrap around
+// await the other parity).  One barrier per lane in a single instruction: a successful wait costs about 85
+// cycles of latency whether it tests one barrier or thirty-two, so a warp that consumes stages one by one
+// looks ahead with this and then skips the waits it already knows the answer to.  All lanes must call it.
+__device__ __forceinline__ int mbar_ring_ready(uint32_t bar0, int stages, int stage, uint32_t parity, int lane) {
+    int st = stage + lane;
+    uint32_t par = parity;
+    if (st >= stages) { st -= stages; par ^= 1u; }
+    const bool ok = lane < stages && mbar_test_wait(bar0 + 8u * (uint32_t)st, par);
+    const uint32_t mask = __ballot_sync(0xffffffffu, ok);
+    return __ffs(~mask) - 1;
 }
 
 // Bounded wait.  Gives up after ~2^31 SM cycles (about a second) or as soon as another thread of

@@ -45,9 +45,14 @@ constexpr int kTileTokens = 128;
 constexpr uint32_t kSlabBytes = kTileTokens * 32 * 4;  // 16 KiB: [128 tokens][32 k] fp32
 constexpr uint32_t kWStageBytes = kImage32Bytes;       // 8 KiB: hi and lo parts interleaved
 constexpr uint32_t kTmemCols = 512;
-constexpr int kThreads = 352;  // producer, two MMA issuers, four split warps, four drain warps
-constexpr int kXStages = 6;
-constexpr int kWStages = 14;
+constexpr int kMmaWarps = kDsdMmaWarps;
+constexpr int kFirstMmaWarp = 2;                  // warp 0 loads weight blocks, warp 1 activation slabs
+constexpr int kFirstSplitWarp = kFirstMmaWarp + kMmaWarps;
+constexpr int kFirstDrainWarp = kFirstSplitWarp + 4;
+constexpr int kThreads = 32 * (kFirstDrainWarp + 4);
+constexpr int kXStages = 5;
+constexpr int kWRing = 4;                     // weight stages per MMA warp (a ring of its own, a power of two)
+constexpr int kWStages = kMmaWarps * kWRing;
 
 template <int G, int kPasses>
 struct Cfg {
@@ -55,11 +60,11 @@ struct Cfg {
     static constexpr uint32_t kAStageCols = kPasses == 3 ? 64 : 32;  // x_hi | x_lo
     static constexpr uint32_t kAccCols = G * kRowCols;
     static constexpr int kAStagesMax = (int)((kTmemCols - kAccCols) / kAStageCols);
-    static constexpr int kAStages = kAStagesMax > 8 ? 8 : kAStagesMax;
+    static constexpr int kAStages = kAStagesMax >= 8 ? 8 : kAStagesMax >= 4 ? 4 : 2;  // a power of two
     static constexpr uint32_t kOffX = 0;
     static constexpr uint32_t kOffW = kOffX + kXStages * kSlabBytes;
     static constexpr uint32_t kOffBar = kOffW + kWStages * kWStageBytes;
-    static constexpr int kNumBars = 2 * kXStages + 2 * kWStages + 2 * kAStages + 2 * G;
+    static constexpr int kNumBars = 2 * kXStages + 2 * kWStages + kAStages + 2 * G;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
     static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;  // + slack to align the base to 1 KiB
     static_assert(kAStages >= 2, "tensor memory over-subscribed");
@@ -106,12 +111,13 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
     auto x_empty = [&](int s) { return bar0 + 8u * (XS + s); };              // transform warps read it
     auto w_full = [&](int s) { return bar0 + 8u * (2 * XS + s); };
     auto w_empty = [&](int s) { return bar0 + 8u * (2 * XS + kWStages + s); };
-    auto a_full = [&](int s) { return bar0 + 8u * (2 * XS + 2 * kWStages + s); };       // slab is in tensor memory
-    auto a_empty = [&](int s) { return bar0 + 8u * (2 * XS + 2 * kWStages + AS + s); }; // both MMA warps are past it
-    auto p_ready = [&](int r) { return bar0 + 8u * (2 * XS + 2 * kWStages + 2 * AS + r); };
-    auto p_taken = [&](int r) { return bar0 + 8u * (2 * XS + 2 * kWStages + 2 * AS + G + r); };
+    auto a_empty = [&](int s) { return bar0 + 8u * (2 * XS + 2 * kWStages + s); };  // every MMA warp is past the slab
+    auto p_ready = [&](int r) { return bar0 + 8u * (2 * XS + 2 * kWStages + AS + r); };
+    auto p_taken = [&](int r) { return bar0 + 8u * (2 * XS + 2 * kWStages + AS + G + r); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kOffMisc);
-    // misc[0]: tensor-memory base address, misc[1]: abort flag
+    // misc[0]: tensor-memory base address, misc[1]: abort flag, misc[2]: number of slabs whose tensor-memory
+    // copy is complete -- slab s may be read once it exceeds s
+    const uint32_t a_count = smem_base + C::kOffMisc + 8;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -124,13 +130,14 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < XS; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); }
-        for (int s = 0; s < AS; ++s) { mbar_init(a_full(s), 128); mbar_init(a_empty(s), 2); }
+        for (int s = 0; s < AS; ++s) mbar_init(a_empty(s), kMmaWarps);
         for (int s = 0; s < kWStages; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1); }
         for (int r = 0; r < G; ++r) { mbar_init(p_ready(r), 1); mbar_init(p_taken(r), 128); }
         misc[1] = 0;
+        misc[2] = 0;
         fence_mbar_init();
     }
-    if (warp == 1) {
+    if (warp == kFirstMmaWarp) {
         tmem_alloc(smem_base + C::kOffMisc, kTmemCols);
         tmem_relinquish();
     }
@@ -140,141 +147,188 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
     const uint32_t tmem = misc[0];
     volatile uint32_t* abort_flag = &misc[1];
 
+#ifdef BSMM_TRACE
     const bool tracing = p.trace != nullptr && (int)blockIdx.x == p.trace_block;
+#else
+    constexpr bool tracing = false;
+#endif
     long long tr[4] = {0, 0, 0, 0};
     const long long t_role0 = tracing ? clock64() : 0;
-    auto wait = [&](uint32_t bar, uint32_t parity, int which) -> bool {
-        if (!tracing) return mbar_wait(bar, parity, abort_flag);
-        const long long t = clock64();
-        const bool r = mbar_wait(bar, parity, abort_flag);
-        tr[which] += clock64() - t;
-        return r;
+    // Waits never branch on their result in the common case: a conditional branch costs a lone warp ~40 cycles.
+    // A wait that gives up (bounded, see mbar_wait) sets `bad`; the issuing instructions are predicated on it
+    // and the role loops test it once per chunk, slab or promotion.
+    uint32_t bad = 0;
+    auto wait = [&](uint32_t bar, uint32_t parity, int which) {
+        const long long t = tracing ? clock64() : 0;
+        if (!mbar_try_wait(bar, parity) && !mbar_wait(bar, parity, abort_flag)) bad = 1;
+        if (tracing) tr[which] += clock64() - t;
+    };
+    // bounded like mbar_wait: polls until the counter at `addr` has reached `target`
+    auto wait_count = [&](uint32_t addr, uint32_t target) {
+        const long long t = tracing ? clock64() : 0;
+        if ((int32_t)(smem_load_acquire(addr) - target) < 0) {
+            const long long t0 = clock64();
+            for (;;) {
+                if ((int32_t)(smem_load_acquire(addr) - target) >= 0) break;
+                if (*abort_flag != 0) { bad = 1; break; }
+                if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; bad = 1; break; }
+            }
+        }
+        if (tracing) tr[0] += clock64() - t;
     };
     const int4* ents = reinterpret_cast<const int4*>(p.entries);
     auto fetch = [&](int i) { return i < e1 ? __ldg(ents + i) : make_int4(0, 0, 0, 0); };  // x inner, y slot, z row, w flags
 
-    // The producer and MMA warps run their loops with all 32 lanes in lock-step (every lane loads the
-    // same plan entry and polls the same barriers) and elect one lane only for the instruction itself.
+    // Control warps are latency machines: one warp executing dependent scalar code retires an instruction
+    // every few cycles, a successful barrier wait costs ~85 cycles and a global load ~1000, while the tensor
+    // core needs only ~250 cycles for a block.  Hence: the plan is read 32 entries per load (lane i holds
+    // entry base + i) one chunk ahead of use; the flag bits and row numbers of a chunk become warp-uniform
+    // bit masks (ballots) and the per-entry decisions are bit tests; ring stages follow from entry and slab
+    // numbers, so a warp visits only the entries it has work for; the lane that holds an entry issues its loads.
     if (warp == 0) {
-        // ------------------------------------------------------------------ producer
-        int xs = 0, ws = 0;
-        uint32_t xph = 0, wph = 0;
-        bool ok = true;
-        auto issue = [&](const int4& ent) {
-            if (ent.w & kPlanFirst) {
-                ok = wait(x_empty(xs), xph ^ 1u, 0);
-                if (!ok) return;
-                const uint32_t dst = smem_base + C::kOffX + xs * kSlabBytes;
-                if (elect_one()) {
+        // ------------------------------------------------------------------ weight producer
+        // every MMA warp has a ring of kWRing stages of its own, filled in the order of that warp's blocks: a
+        // ring with one producer and one consumer, each seeing every phase, which a phase-parity barrier needs
+        uint32_t issued[kMmaWarps];  // blocks already loaded per MMA warp
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) issued[w] = 0;
+        int4 ahead = fetch(e0 + lane);
+        for (int base = e0; base < e1 && !bad; base += 32) {
+            const int4 mine = ahead;
+            ahead = fetch(base + 32 + lane);
+            const int count = min(32, e1 - base);
+            const uint32_t owner = (uint32_t)mine.z & (kMmaWarps - 1);
+            uint32_t seq = 0;  // this lane's block is the seq-th of its MMA warp
+#pragma unroll
+            for (int w = 0; w < kMmaWarps; ++w) {
+                const uint32_t same = __ballot_sync(0xffffffffu, owner == (uint32_t)w && lane < count);
+                if (owner == (uint32_t)w) seq = issued[w] + __popc(same & ((1u << lane) - 1u));
+                issued[w] += __popc(same);
+            }
+            const uint32_t stage_use = (owner * kWRing + (seq & (kWRing - 1))) | (((seq / kWRing) & 1u) << 8);
+            for (int i = 0; i < count; ++i) {
+                const uint32_t su = __shfl_sync(0xffffffffu, stage_use, i);
+                const int slot = __shfl_sync(0xffffffffu, mine.y, i);
+                const int ws = (int)(su & 0xffu);
+                wait(w_empty(ws), (su >> 8) ^ 1u, 1);
+                const uint8_t* src = p.packed + (int64_t)slot * kWStageBytes;
+                if (elect_one() && !bad) {
+                    mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
+                    bulk_load(smem_base + C::kOffW + ws * kWStageBytes, src, kWStageBytes, w_full(ws));
+                }
+            }
+        }
+        if (tracing && lane == 0) {
+            p.trace[kTrProdWEmpty] = tr[1];
+            p.trace[kTrProdTotal] = clock64() - t_role0;
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ activation producer
+        int xs = 0;
+        uint32_t xph = 0;
+        int4 ahead = fetch(e0 + lane);
+        for (int base = e0; base < e1 && !bad; base += 32) {
+            const int4 mine = ahead;
+            ahead = fetch(base + 32 + lane);
+            uint32_t firsts = __ballot_sync(0xffffffffu, (mine.w & kPlanFirst) != 0);
+            while (firsts != 0) {
+                const int i = __ffs(firsts) - 1;
+                firsts &= firsts - 1;
+                wait(x_empty(xs), xph ^ 1u, 0);
+                const int inner = __shfl_sync(0xffffffffu, mine.x, i);
+                if (elect_one() && !bad) {
                     mbar_arrive_expect_tx(x_full(xs), p.x_bytes);
-                    tma_load_2d(dst, &tmap_a, ent.x * 32, (int32_t)tok0, x_full(xs));
+                    tma_load_2d(smem_base + C::kOffX + xs * kSlabBytes, &tmap_a, inner * 32, (int32_t)tok0, x_full(xs));
                 }
                 if (++xs == XS) { xs = 0; xph ^= 1u; }
             }
-            ok = wait(w_empty(ws), wph ^ 1u, 1);
-            if (!ok) return;
-            const uint32_t dst = smem_base + C::kOffW + ws * kWStageBytes;
-            const uint8_t* src = p.packed + (int64_t)ent.y * kWStageBytes;
-            const long long ti = tracing ? clock64() : 0;
-            if (elect_one()) {
-                mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
-                bulk_load(dst, src, kWStageBytes, w_full(ws));
-            }
-            if (tracing) tr[3] += clock64() - ti;
-            if (++ws == kWStages) { ws = 0; wph ^= 1u; }
-        };
-        int4 q0 = fetch(e0), q1 = fetch(e0 + 1), q2 = fetch(e0 + 2), q3 = fetch(e0 + 3);
-        for (int e = e0; e < e1 && ok; e += 4) {
-            issue(q0); q0 = fetch(e + 4);
-            if (e + 1 < e1 && ok) { issue(q1); q1 = fetch(e + 5); }
-            if (e + 2 < e1 && ok) { issue(q2); q2 = fetch(e + 6); }
-            if (e + 3 < e1 && ok) { issue(q3); q3 = fetch(e + 7); }
         }
-        if (tracing && lane == 0) {
-            p.trace[kTrProdXEmpty] = tr[0];
-            p.trace[kTrProdWEmpty] = tr[1];
-            p.trace[kTrProdTotal] = clock64() - t_role0;
-            p.trace[kTrProdIssue] = tr[3];
-        }
-    } else if (warp <= 2) {
+        if (tracing && lane == 0) p.trace[kTrProdXEmpty] = tr[0];
+    } else if (warp < kFirstSplitWarp) {
         // ------------------------------------------------------------------ MMA issuers
-        // Two warps share the issue work by output row parity: while one is between blocks (barrier
-        // polls, descriptor arithmetic, commits) the other keeps the tensor pipe fed.  Both walk the
-        // whole plan so that their stage counters agree; a slab's stage is released when both passed it.
-        const uint32_t mw = (uint32_t)(warp - 1);
+        // The warps share the issue work by output row (row mod kMmaWarps): accumulations into one row stay
+        // in one thread's program order, and while one warp is between blocks the others keep the tensor pipe
+        // fed.  Each warp visits only its own blocks (ring stages follow from the entry and slab numbers); a
+        // slab's stage is released by one commit from every warp that read it plus, from the warp issuing the
+        // slab's last block, plain arrivals on behalf of the warps that had nothing in it.
+        const uint32_t mw = (uint32_t)(warp - kFirstMmaWarp);
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
-        int ws = 0, as = -1;
-        uint32_t wph = 0, aph = 1;  // as/aph advance at every first-of-slab entry
         uint32_t started = 0;   // bit r: the row's columns hold a partial sum of the current segment
         uint32_t pending = 0;   // bit r: a promotion of the row was requested and not yet seen taken
         uint32_t taken_ph = 0;  // bit r: parity of the next p_taken[r] phase to wait for
-        uint32_t a_hi = 0;
-        bool ok = true;
-        auto issue = [&](const int4& ent) {
-            const uint32_t row = (uint32_t)ent.z;
-            const uint32_t rbit = 1u << row;
-            if (ent.w & kPlanFirst) {
-                if (++as == AS) as = 0;
-                if (as == 0) aph ^= 1u;
-                ok = wait(a_full(as), aph, 0);
-                if (!ok) return;
-                tc_fence_after();  // the transform warps' tcgen05.st precede the MMAs that read the slab
-                a_hi = tmem + C::kAccCols + as * C::kAStageCols;
-            }
-            const bool mine = (row & 1u) == mw;
-            const bool last = (ent.w & kPlanLast) != 0, drain = (ent.w & kPlanDrain) != 0;
-            if (!mine) {
-                if (last) {  // nothing of this warp may still be reading the slab once its earlier MMAs completed
-                    const uint32_t a_bar = a_empty(as);
-                    if (elect_one()) mma_commit(a_bar);
+        int slab_base = -1;     // number of the last slab opened before this chunk
+        int cur_slab = -1;      // slab this warp has waited for
+        uint32_t seq = 0;       // this warp's blocks so far: position in its weight ring
+        int4 ahead = fetch(e0 + lane);
+        for (int base = e0; base < e1 && !bad; base += 32) {
+            const int4 mine4 = ahead;
+            ahead = fetch(base + 32 + lane);
+            const uint32_t valid = __ballot_sync(0xffffffffu, base + lane < e1);
+            const uint32_t firsts = __ballot_sync(0xffffffffu, (mine4.w & kPlanFirst) != 0);
+            const uint32_t lasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanLast) != 0);
+            const uint32_t wlasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanWarpLast) != 0);
+            const uint32_t drains = __ballot_sync(0xffffffffu, (mine4.w & kPlanDrain) != 0);
+            const uint32_t idle_b0 = __ballot_sync(0xffffffffu, (mine4.w & (1 << kPlanIdleShift)) != 0);
+            const uint32_t idle_b1 = __ballot_sync(0xffffffffu, (mine4.w & (2 << kPlanIdleShift)) != 0);
+            const uint32_t row_b0 = __ballot_sync(0xffffffffu, (mine4.z & 1) != 0);
+            const uint32_t row_b1 = __ballot_sync(0xffffffffu, (mine4.z & 2) != 0);
+            const uint32_t row_b2 = __ballot_sync(0xffffffffu, (mine4.z & 4) != 0);
+            uint32_t todo = __ballot_sync(0xffffffffu, (uint32_t)(mine4.z & (kMmaWarps - 1)) == mw) & valid;
+            while (todo != 0) {
+                const int i = __ffs(todo) - 1;
+                todo &= todo - 1;
+                const int slab = slab_base + __popc(firsts & (0xffffffffu >> (31 - i)));
+                const int as = slab & (AS - 1);
+                if (slab != cur_slab) {
+                    wait_count(a_count, (uint32_t)(slab + 1));
+                    tc_fence_after();  // the transform warps' tcgen05.st precede the MMAs that read the slab
+                    cur_slab = slab;
                 }
-                if (++ws == kWStages) { ws = 0; wph ^= 1u; }
-                return;
-            }
-            ok = wait(w_full(ws), wph, 1);
-            if (!ok) return;
-            if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
-                ok = wait(p_taken(row), (taken_ph >> row) & 1u, 2);
-                if (!ok) return;
-                taken_ph ^= rbit;
-                pending &= ~rbit;
-                tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the row
-            }
-            const uint64_t b_desc =
-                smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
-            const uint32_t d = tmem + row * C::kRowCols;
-            const uint32_t acc0 = (started & rbit) ? 1u : 0u;
-            const uint32_t w_bar = w_empty(ws), a_bar = a_empty(as), p_bar = p_ready(row);
-            const long long ti = tracing ? clock64() : 0;
-            if (elect_one()) {
+                const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
+                const uint32_t row = ((row_b0 >> i) & 1u) | (((row_b1 >> i) & 1u) << 1) | (((row_b2 >> i) & 1u) << 2);
+                const uint32_t rbit = 1u << row;
+                const bool wlast = ((wlasts >> i) & 1u) != 0, drain = ((drains >> i) & 1u) != 0;
+                // the warp that issues a slab's last block also arrives for the warps that have none in it
+                const uint32_t idle = ((lasts >> i) & 1u) * (((idle_b0 >> i) & 1u) | (((idle_b1 >> i) & 1u) << 1));
+                wait(w_full(ws), (seq / kWRing) & 1u, 1);
+                ++seq;
+                if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
+                    wait(p_taken(row), (taken_ph >> row) & 1u, 2);
+                    taken_ph ^= rbit;
+                    pending &= ~rbit;
+                    tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the row
+                }
+                const uint64_t b_desc =
+                    smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
+                const uint32_t a_hi = tmem + C::kAccCols + as * C::kAStageCols;
+                const uint32_t d = tmem + row * C::kRowCols;
+                const uint32_t acc0 = (started & rbit) ? 1u : 0u;
+                const uint32_t w_bar = w_empty(ws), a_bar = a_empty(as), p_bar = p_ready(row);
+                const long long ti = tracing ? clock64() : 0;
+                if (elect_one() && !bad) {
 #pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    // k-step s: 8 columns further in the slab's tensor-memory copy, 2 KiB further in the image
-                    const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
-                    const uint32_t acc = s == 0 ? acc0 : 1u;
-                    if (kPasses == 3) {
-                        mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, acc);               // x_hi x [w_hi ; w_lo]
-                        mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // x_lo x w_hi
-                    } else {
-                        mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, acc);
+                    for (int s = 0; s < 4; ++s) {
+                        // k-step s: 8 columns further in the slab's tensor-memory copy, 2 KiB further in the image
+                        const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
+                        const uint32_t acc = s == 0 ? acc0 : 1u;
+                        if (kPasses == 3) {
+                            mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, acc);               // x_hi x [w_hi ; w_lo]
+                            mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // x_lo x w_hi
+                        } else {
+                            mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, acc);
+                        }
                     }
+                    mma_commit(w_bar);
+                    if (wlast) mma_commit(a_bar);
+                    if (idle != 0) mbar_arrive_n(a_bar, idle);
+                    if (drain) mma_commit(p_bar);
                 }
-                mma_commit(w_bar);
-                if (last) mma_commit(a_bar);
-                if (drain) mma_commit(p_bar);
+                if (tracing) tr[3] += clock64() - ti;
+                started |= rbit;
+                if (drain) { pending |= rbit; started &= ~rbit; }
             }
-            if (tracing) tr[3] += clock64() - ti;
-            started |= rbit;
-            if (++ws == kWStages) { ws = 0; wph ^= 1u; }
-            if (drain) { pending |= rbit; started &= ~rbit; }
-        };
-        int4 q0 = fetch(e0), q1 = fetch(e0 + 1), q2 = fetch(e0 + 2), q3 = fetch(e0 + 3);
-        for (int e = e0; e < e1 && ok; e += 4) {
-            issue(q0); q0 = fetch(e + 4);
-            if (e + 1 < e1 && ok) { issue(q1); q1 = fetch(e + 5); }
-            if (e + 2 < e1 && ok) { issue(q2); q2 = fetch(e + 6); }
-            if (e + 3 < e1 && ok) { issue(q3); q3 = fetch(e + 7); }
+            slab_base += __popc(firsts & valid);
         }
         if (tracing && lane == 0 && mw == 0) {
             p.trace[kTrMmaAFull] = tr[0];
@@ -283,7 +337,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
             p.trace[kTrMmaTotal] = clock64() - t_role0;
             p.trace[kTrMmaIssue] = tr[3];
         }
-    } else if (warp < 7) {
+    } else if (warp < kFirstDrainWarp) {
         // ------------------------------------------------------------------ transform
         const int quarter = warp & 3;           // tensor-memory lane quarter this warp may access
         const int row = quarter * 32 + lane;    // token inside the tile = tensor-memory lane
@@ -291,7 +345,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         int xs = 0, as = 0;
         uint32_t xph = 0, aph = 0;
         for (int s = 0; s < nslabs; ++s) {
-            if (!__all_sync(0xffffffffu, wait(x_full(xs), xph, 0))) break;
+            wait(x_full(xs), xph, 0);
             uint32_t hi[32], lo[32];
             {
                 const uint8_t* xrow = smem_gen + C::kOffX + xs * kSlabBytes + row * 128;
@@ -310,17 +364,27 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
             }
             mbar_arrive(x_empty(xs));
             if (++xs == XS) { xs = 0; xph ^= 1u; }
-            if (!__all_sync(0xffffffffu, wait(a_empty(as), aph ^ 1u, 1))) break;
+            wait(a_empty(as), aph ^ 1u, 1);
             tc_fence_after();
             const uint32_t a_hi = tmem_lane + C::kAccCols + as * C::kAStageCols;
             tmem_st32(a_hi, hi);
             if (kPasses == 3) tmem_st32(a_hi + 32, lo);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(a_full(as));
+            // barrier of the four split warps (the whole slab is stored) that also tells whether any of their
+            // threads gave up on a wait; only here, together, may they leave the loop
+            uint32_t any_bad;
+            asm volatile(
+                "{\n\t.reg .pred q, r;\n\t"
+                "setp.ne.u32 q, %1, 0;\n\t"
+                "bar.red.or.pred r, 1, 128, q;\n\t"
+                "selp.u32 %0, 1, 0, r;\n\t}"
+                : "=r"(any_bad) : "r"(bad) : "memory");
+            if (any_bad) break;
+            if (warp == kFirstSplitWarp && lane == 0) smem_add_release(a_count, 1u);
             if (++as == AS) { as = 0; aph ^= 1u; }
         }
-        if (tracing && warp == 3 && lane == 0) {
+        if (tracing && warp == kFirstSplitWarp && lane == 0) {
             p.trace[kTrXfXFull] = tr[0];
             p.trace[kTrXfAEmpty] = tr[1];
             p.trace[kTrXfTotal] = clock64() - t_role0;
@@ -362,14 +426,17 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         uint32_t ready_ph = 0;  // bit r: parity of the next p_ready[r] phase
         uint32_t seen = 0;      // bit r: the row has been written once
         bool ok = true;
+        int4 ahead = fetch(e0 + lane);  // 32 entries per warp-wide load, one chunk ahead
         for (int base = e0; base < e1 && ok; base += 32) {
-            const int4 mine = fetch(base + lane);  // 32 entries per warp-wide load
-            const int count = min(32, e1 - base);
-            for (int i = 0; i < count; ++i) {
-                const int flags = __shfl_sync(0xffffffffu, mine.w, i);
-                if (!(flags & kPlanDrain)) continue;
+            const int4 mine = ahead;
+            ahead = fetch(base + 32 + lane);
+            uint32_t drains = __ballot_sync(0xffffffffu, (mine.w & kPlanDrain) != 0);
+            while (drains != 0) {
+                const int i = __ffs(drains) - 1;
+                drains &= drains - 1;
                 const int r = __shfl_sync(0xffffffffu, mine.z, i);
-                ok = __all_sync(0xffffffffu, wait(p_ready(r), (ready_ph >> r) & 1u, 0));
+                wait(p_ready(r), (ready_ph >> r) & 1u, 0);
+                ok = !__any_sync(0xffffffffu, bad != 0);
                 if (!ok) break;
                 ready_ph ^= 1u << r;
                 tc_fence_after();
@@ -401,7 +468,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
             for (int r = 0; r < nrows; ++r)
                 if (!((seen >> r) & 1u)) emit(r, z, true);
         }
-        if (tracing && warp == 7 && lane == 0) {
+        if (tracing && warp == kFirstDrainWarp && lane == 0) {
             p.trace[kTrDrainPReady] = tr[0];
             p.trace[kTrDrainTotal] = clock64() - t_role0;
         }
@@ -411,7 +478,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag != 0) atomicOr(p.status, 1u);
-    if (warp == 1) {
+    if (warp == kFirstMmaWarp) {
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);

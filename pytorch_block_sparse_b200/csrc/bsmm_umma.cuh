@@ -12,11 +12,17 @@ struct __align__(16) PlanEntry {
     int32_t inner;    // block index along the contraction axis (selects the activation slab)
     int32_t slot;     // position of the block in `data` / the packed images
     int32_t row;      // output block-row inside the group, 0..group-1
-    int32_t flags;    // kPlanFirst | kPlanLast | kPlanDrain
+    int32_t flags;    // kPlanFirst | kPlanLast | kPlanDrain | kPlanWarpLast | idle warps << kPlanIdleShift
 };
-constexpr int32_t kPlanFirst = 1;  // first entry of its activation slab
-constexpr int32_t kPlanLast = 2;   // last entry of its activation slab
-constexpr int32_t kPlanDrain = 4;  // after this entry the row's tensor-memory partial sum is promoted
+// The dsd kernel issues its MMAs from kDsdMmaWarps warps; output row r of a group belongs to warp
+// r mod kDsdMmaWarps.  A slab's tensor-memory stage is released by kDsdMmaWarps arrivals: one from every warp
+// with a block in the slab (after its last one), the rest from the warp that issues the slab's last block.
+constexpr int kDsdMmaWarps = 4;
+constexpr int32_t kPlanFirst = 1;     // first entry of its activation slab
+constexpr int32_t kPlanLast = 2;      // last entry of its activation slab
+constexpr int32_t kPlanDrain = 4;     // after this entry the row's tensor-memory partial sum is promoted
+constexpr int32_t kPlanWarpLast = 8;  // last entry of its slab among the rows of the same MMA warp
+constexpr int kPlanIdleShift = 4;     // on the slab's last entry, 2 bits: MMA warps without a block in the slab
 // Blocks of one output row accumulated in tensor memory between two promotions.  The tensor core
 // adds into its fp32 accumulator with a systematic rounding error of about 2e-8 (relative) per
 // accumulation.  The kernel keeps the main term (hi*hi: 4 accumulations per block) apart from the
@@ -57,8 +63,9 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
 // device resolves the symbol).
 cudaError_t sddmm_static_scratch(void** ptr, size_t* bytes);
 
-// Diagnostics: the following dsd launches record, for CTA `block`, the cycles each warp role spent in
-// each kind of wait into `device_buffer` (32 int64, see TraceSlot in bsmm_umma.cu); null switches it off.
+// Diagnostics, effective only in a library built with -DBSMM_TRACE: the following dsd launches record, for CTA
+// `block`, the cycles each warp role spent in each kind of wait into `device_buffer` (32 int64, see TraceSlot
+// in bsmm_umma.cu); null switches it off.
 void set_dsd_trace(long long* device_buffer, int block);
 
 // 2-D tiled tensor map over a row-major [outer, inner] array.

@@ -248,7 +248,13 @@ def test_plan_is_the_group_merge_of_the_csr(group):
             seen[r] = seen.get(r, 0) + 1
             row_len = ptr[g * group + r + 1] - ptr[g * group + r]
             drain = seen[r] % 32 == 0 or seen[r] == row_len  # promotion every 32 blocks of a row and at its end
-            assert flags == (1 if first else 0) | (2 if last else 0) | (4 if drain else 0)
+            # MMA warp of a row: row mod 4.  Bit 3: last block of its slab for its warp; on the slab's last
+            # block, bits 4-5: warps without a block in the slab
+            slab = [int(q[2]) for q in got if q[0] == c]
+            warp_last = not any(q > r and q % 4 == r % 4 for q in slab)
+            idle = 4 - len({q % 4 for q in slab})
+            assert flags == ((1 if first else 0) | (2 if last else 0) | (4 if drain else 0) | (8 if warp_last else 0)
+                             | ((idle << 4) if last else 0))
 
 
 @pytest.mark.parametrize("group", ["4", "6", "8"])
