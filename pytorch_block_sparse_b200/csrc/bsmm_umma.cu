@@ -46,11 +46,14 @@ constexpr uint32_t kSlabBytes = kTileTokens * 32 * 4;  // 16 KiB: [128 tokens][3
 constexpr uint32_t kWStageBytes = kImage32Bytes;       // 8 KiB: hi and lo parts interleaved
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMmaWarps = kDsdMmaWarps;
-constexpr int kFirstMmaWarp = 2;                  // warp 0 loads weight blocks, warp 1 activation slabs
+constexpr int kWProducers = 2;                    // warps 0..1 load weight blocks (alternate entries)
+constexpr int kXProducerWarp = kWProducers;       // this warp loads activation slabs
+constexpr int kFirstMmaWarp = kXProducerWarp + 1;
 constexpr int kFirstSplitWarp = kFirstMmaWarp + kMmaWarps;
-constexpr int kFirstDrainWarp = kFirstSplitWarp + 4;
+constexpr int kSplitWarps = 8;                    // two groups of four, taking alternate slabs
+constexpr int kFirstDrainWarp = kFirstSplitWarp + kSplitWarps;
 constexpr int kThreads = 32 * (kFirstDrainWarp + 4);
-constexpr int kXStages = 5;
+constexpr int kXStages = 4;  // even: a stage always belongs to the same split-warp group
 constexpr int kWRing = 4;                     // weight stages per MMA warp (a ring of its own, a power of two)
 constexpr int kWStages = kMmaWarps * kWRing;
 
@@ -66,7 +69,7 @@ struct Cfg {
     static constexpr uint32_t kOffBar = kOffW + kWStages * kWStageBytes;
     static constexpr int kNumBars = 2 * kXStages + 2 * kWStages + kAStages + 2 * G;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
-    static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;  // + slack to align the base to 1 KiB
+    static constexpr uint32_t kSmemBytes = kOffMisc + 64 + 1024;  // + slack to align the base to 1 KiB
     static_assert(kAStages >= 2, "tensor memory over-subscribed");
     static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
 };
@@ -115,9 +118,9 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
     auto p_ready = [&](int r) { return bar0 + 8u * (2 * XS + 2 * kWStages + AS + r); };
     auto p_taken = [&](int r) { return bar0 + 8u * (2 * XS + 2 * kWStages + AS + G + r); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kOffMisc);
-    // misc[0]: tensor-memory base address, misc[1]: abort flag, misc[2]: number of slabs whose tensor-memory
-    // copy is complete -- slab s may be read once it exceeds s
-    const uint32_t a_count = smem_base + C::kOffMisc + 8;
+    // misc[0]: tensor-memory base address, misc[1]: abort flag, misc[2 + stage]: how many split warps have
+    // completed a copy into that tensor-memory stage so far -- its u-th slab may be read at 4 * (u + 1)
+    auto a_count = [&](int s) { return smem_base + C::kOffMisc + 8u + 4u * s; };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -134,7 +137,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         for (int s = 0; s < kWStages; ++s) { mbar_init(w_full(s), 1); mbar_init(w_empty(s), 1); }
         for (int r = 0; r < G; ++r) { mbar_init(p_ready(r), 1); mbar_init(p_taken(r), 128); }
         misc[1] = 0;
-        misc[2] = 0;
+        for (int s = 0; s < AS; ++s) misc[2 + s] = 0;
         fence_mbar_init();
     }
     if (warp == kFirstMmaWarp) {
@@ -185,8 +188,8 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
     // entry base + i) one chunk ahead of use; the flag bits and row numbers of a chunk become warp-uniform
     // bit masks (ballots) and the per-entry decisions are bit tests; ring stages follow from entry and slab
     // numbers, so a warp visits only the entries it has work for; the lane that holds an entry issues its loads.
-    if (warp == 0) {
-        // ------------------------------------------------------------------ weight producer
+    if (warp < kWProducers) {
+        // ------------------------------------------------------------------ weight producers
         // every MMA warp has a ring of kWRing stages of its own, filled in the order of that warp's blocks: a
         // ring with one producer and one consumer, each seeing every phase, which a phase-parity barrier needs
         uint32_t issued[kMmaWarps];  // blocks already loaded per MMA warp
@@ -206,7 +209,12 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                 issued[w] += __popc(same);
             }
             const uint32_t stage_use = (owner * kWRing + (seq & (kWRing - 1))) | (((seq / kWRing) & 1u) << 8);
-            for (int i = 0; i < count; ++i) {
+            // a stage is always filled by the same producer warp (stage number mod kWProducers), which thus
+            // sees every phase of the stage's barriers
+            uint32_t todo = __ballot_sync(0xffffffffu, lane < count && (seq & (kWProducers - 1)) == (uint32_t)warp);
+            while (todo != 0) {
+                const int i = __ffs(todo) - 1;
+                todo &= todo - 1;
                 const uint32_t su = __shfl_sync(0xffffffffu, stage_use, i);
                 const int slot = __shfl_sync(0xffffffffu, mine.y, i);
                 const int ws = (int)(su & 0xffu);
@@ -218,11 +226,11 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                 }
             }
         }
-        if (tracing && lane == 0) {
+        if (tracing && lane == 0 && warp == 0) {
             p.trace[kTrProdWEmpty] = tr[1];
             p.trace[kTrProdTotal] = clock64() - t_role0;
         }
-    } else if (warp == 1) {
+    } else if (warp == kXProducerWarp) {
         // ------------------------------------------------------------------ activation producer
         int xs = 0;
         uint32_t xph = 0;
@@ -280,19 +288,19 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                 todo &= todo - 1;
                 const int slab = slab_base + __popc(firsts & (0xffffffffu >> (31 - i)));
                 const int as = slab & (AS - 1);
+                const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
+                wait(w_full(ws), (seq / kWRing) & 1u, 1);
+                ++seq;
                 if (slab != cur_slab) {
-                    wait_count(a_count, (uint32_t)(slab + 1));
+                    wait_count(a_count(as), 4u * (uint32_t)(slab / AS + 1));
                     tc_fence_after();  // the transform warps' tcgen05.st precede the MMAs that read the slab
                     cur_slab = slab;
                 }
-                const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
                 const uint32_t row = ((row_b0 >> i) & 1u) | (((row_b1 >> i) & 1u) << 1) | (((row_b2 >> i) & 1u) << 2);
                 const uint32_t rbit = 1u << row;
                 const bool wlast = ((wlasts >> i) & 1u) != 0, drain = ((drains >> i) & 1u) != 0;
                 // the warp that issues a slab's last block also arrives for the warps that have none in it
                 const uint32_t idle = ((lasts >> i) & 1u) * (((idle_b0 >> i) & 1u) | (((idle_b1 >> i) & 1u) << 1));
-                wait(w_full(ws), (seq / kWRing) & 1u, 1);
-                ++seq;
                 if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
                     wait(p_taken(row), (taken_ph >> row) & 1u, 2);
                     taken_ph ^= rbit;
@@ -339,13 +347,17 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         }
     } else if (warp < kFirstDrainWarp) {
         // ------------------------------------------------------------------ transform
+        // Two groups of four warps take alternate slabs, so that one slab's trip through registers (shared
+        // memory -> split -> tensor memory, a few hundred cycles of latency) overlaps the next one's.  Ring
+        // stages follow from the slab number; the stage counts are even, so a stage stays with one group.
         const int quarter = warp & 3;           // tensor-memory lane quarter this warp may access
+        const int group = (warp - kFirstSplitWarp) >> 2;
         const int row = quarter * 32 + lane;    // token inside the tile = tensor-memory lane
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
-        int xs = 0, as = 0;
-        uint32_t xph = 0, aph = 0;
-        for (int s = 0; s < nslabs; ++s) {
-            wait(x_full(xs), xph, 0);
+        static_assert(XS % 2 == 0 && AS % 2 == 0, "a ring stage must stay with one split-warp group");
+        for (int s = group; s < nslabs; s += 2) {
+            const int xs = s % XS, as = s & (AS - 1);
+            wait(x_full(xs), (uint32_t)(s / XS) & 1u, 0);
             uint32_t hi[32], lo[32];
             {
                 const uint8_t* xrow = smem_gen + C::kOffX + xs * kSlabBytes + row * 128;
@@ -363,26 +375,15 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                 }
             }
             mbar_arrive(x_empty(xs));
-            if (++xs == XS) { xs = 0; xph ^= 1u; }
-            wait(a_empty(as), aph ^ 1u, 1);
+            wait(a_empty(as), ((uint32_t)(s / AS) & 1u) ^ 1u, 1);
             tc_fence_after();
             const uint32_t a_hi = tmem_lane + C::kAccCols + as * C::kAStageCols;
             tmem_st32(a_hi, hi);
             if (kPasses == 3) tmem_st32(a_hi + 32, lo);
             tmem_wait_st();
             tc_fence_before();
-            // barrier of the four split warps (the whole slab is stored) that also tells whether any of their
-            // threads gave up on a wait; only here, together, may they leave the loop
-            uint32_t any_bad;
-            asm volatile(
-                "{\n\t.reg .pred q, r;\n\t"
-                "setp.ne.u32 q, %1, 0;\n\t"
-                "bar.red.or.pred r, 1, 128, q;\n\t"
-                "selp.u32 %0, 1, 0, r;\n\t}"
-                : "=r"(any_bad) : "r"(bad) : "memory");
-            if (any_bad) break;
-            if (warp == kFirstSplitWarp && lane == 0) smem_add_release(a_count, 1u);
-            if (++as == AS) { as = 0; aph ^= 1u; }
+            if (__any_sync(0xffffffffu, bad != 0)) break;  // nothing is published once a wait has given up
+            if (lane == 0) smem_add_release(a_count(as), 1u);
         }
         if (tracing && warp == kFirstSplitWarp && lane == 0) {
             p.trace[kTrXfXFull] = tr[0];
