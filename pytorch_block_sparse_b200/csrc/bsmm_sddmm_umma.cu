@@ -7,20 +7,27 @@
 // A CTA owns one "item": up to 16 blocks of ONE block-row R (a CSR row segment) and one range of
 // tokens.  Four blocks of the row form a chunk and fill the 128 rows of one MMA:
 //   D[128 = 4 blocks x 32 c, 32 = r] += A[128 x K] * B[32 x K]^T,   K = tokens, 8 per instruction.
-// Both operands are token-major in memory, i.e. MN-major for the MMA: a TMA box of 32 tokens x 32
-// features with the 128-byte / 32-byte-atom swizzle IS the canonical MN-major tf32 operand tile (one 128-byte row per
-// token), so the slabs are consumed where TMA put them, without transposition:
-//   A = the four X slabs of the chunk (atoms 4 KiB apart), B = the dY slab of row R.
-// D is already the block's storage layout (row c holds 32 consecutive r).
+// D is already the block's storage layout (row c holds 32 consecutive r).  A "unit" is one chunk times one
+// 32-token step: 8 MMAs.
 //
-//   warp 0    producer : TMA tensor loads: one dY slab per 32-token step, four X slabs per chunk
-//   warps 3-6 split    : lo = v - trunc_tf32(v) of every slab into a second tile of the same layout
-//                        (the tensor core reads only the tf32 bits of an operand, so the raw slab is hi)
-//   warps 1-2 MMA      : (chunks by parity) per chunk and k-step (8 tokens)  x x [dy ; dy_lo] (N = 64) and x_lo x dy (N = 32),
-//                        tcgen05.mma kind::tf32, M = 128: main | correction columns of the chunk
-//   warps 7-10 drain   : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
-//                        (fp32, round to nearest) to the chunk's master tile in shared memory; final
-//                        store of the master tiles to global
+// B = the dY slab of row R, token-major in memory, i.e. MN-major for the MMA: a TMA box of 32 tokens x 32
+// features with the 128-byte / 32-byte-atom swizzle IS the canonical MN-major tf32 operand tile, read from
+// shared memory where TMA put it.  A = the chunk's four X slabs, which the split warps carry through
+// registers into tensor memory, transposed (lane = feature, column = token) and split into hi | lo: reading
+// A from shared memory as well made the kernel shared-memory-bandwidth bound (92 KB per unit).
+//
+//   warps 0-1   X producers : TMA, four X slabs per unit (units by parity)
+//   warp 2      dY producer : TMA, one dY slab per step
+//   warp 3      dY split    : lo = v - trunc_tf32(v) of the dY slab into a second tile of the same layout
+//                             (the tensor core reads only the tf32 bits of an operand, so the raw slab is hi)
+//   warps 4-7   MMA         : warp c owns chunk c: per unit and k-step (8 tokens)
+//                             x x [dy ; dy_lo] (N = 64) and x_lo x dy (N = 32), tcgen05.mma kind::tf32, M = 128,
+//                             into the main | correction columns of the chunk
+//   warps 8-15  X split     : two groups of four (units by parity): shared memory -> registers (transposing
+//                             reads, conflict-free under the 128-byte swizzle) -> hi, lo -> tensor memory
+//   warps 16-19 drain       : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
+//                             (fp32, round to nearest) to the chunk's master tile in shared memory; final
+//                             store of the master tiles to global
 //
 // The promotion bounds the tensor core's systematic accumulate error (about 2e-8 relative per MMA).
 // Token ranges (grid.y > 1) write partial results to the workspace; a second kernel sums them in a
@@ -39,24 +46,30 @@ constexpr int kStepTokens = 32;
 constexpr int kDrainSteps = 32;            // promote every 1024 tokens: 128 accumulations of the main term
 constexpr uint32_t kSlabBytes = 32 * 32 * 4;            // 4 KiB: [32 tokens][32 features], 128-byte rows
 constexpr uint32_t kKStepBytes = 8 * 128;               // one MMA k-step = 8 token rows
-constexpr uint32_t kXHalfBytes = 4 * kSlabBytes;        // one chunk's four X slabs
-constexpr uint32_t kXStageBytes = 2 * kXHalfBytes;      // raw slabs | their lo parts
+constexpr uint32_t kXStageBytes = 4 * kSlabBytes;       // one unit's four X slabs
 constexpr uint32_t kDyStageBytes = 2 * kSlabBytes;      // raw slab | its lo part
 constexpr uint32_t kMasterBytes = 128 * 32 * 4;         // 16 KiB per chunk
-constexpr int kXStages = 4, kDyStages = 3;
-constexpr uint32_t kTmemCols = 256;
+constexpr int kStages = 4;                              // X stages in shared memory = A stages in tensor memory
+constexpr int kDyStages = 4;
+constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kChunkCols = 64;                     // main | correction
-constexpr int kThreads = 352;  // producer, two MMA issuers, four split warps, four drain warps
+constexpr uint32_t kAccCols = kChunks * kChunkCols;     // 256
+constexpr uint32_t kAStageCols = 64;                    // x_hi | x_lo, 32 tokens each
+constexpr int kXProducers = 2, kDyProducerWarp = 2, kDySplitWarp = 3, kFirstMmaWarp = 4;
+constexpr int kFirstSplitWarp = kFirstMmaWarp + kChunks, kSplitWarps = 8;
+constexpr int kFirstDrainWarp = kFirstSplitWarp + kSplitWarps;
+constexpr int kThreads = 32 * (kFirstDrainWarp + 4);
 
 constexpr uint32_t kOffMaster = 0;
 constexpr uint32_t kOffX = kOffMaster + kChunks * kMasterBytes;
-constexpr uint32_t kOffDy = kOffX + kXStages * kXStageBytes;
+constexpr uint32_t kOffDy = kOffX + kStages * kXStageBytes;
 constexpr uint32_t kOffBar = kOffDy + kDyStages * kDyStageBytes;
-constexpr int kNumBars = 3 * kXStages + 3 * kDyStages + 2 * kChunks;
+constexpr int kNumBars = 3 * kStages + 3 * kDyStages + 2 * kChunks;
 constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
-constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+constexpr uint32_t kSmemBytes = kOffMisc + 32 + 1024;
 static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
-static_assert(kChunks * kChunkCols <= kTmemCols, "tensor memory over-subscribed");
+static_assert(kAccCols + kStages * kAStageCols <= kTmemCols, "tensor memory over-subscribed");
+static_assert(kStages % 2 == 0, "a stage must stay with one producer warp and one split-warp group");
 
 // Item table: [0] = item count; item i at int32 offsets 4 + 4*i: {block-row, first CSR entry, blocks, 0}
 struct SddmmParams {
@@ -88,32 +101,37 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     const int64_t t_begin = (int64_t)blockIdx.y * p.tokens_per_split;
     const int64_t t_end = min(p.tokens, t_begin + p.tokens_per_split);
     const int nsteps = (int)((t_end - t_begin + kStepTokens - 1) / kStepTokens);
+    const int nunits = nsteps * nchunks;  // unit u = step * nchunks + chunk uses stage u mod kStages
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar0 = smem_base + kOffBar;
-    auto x_full = [&](int s) { return bar0 + 8u * s; };                       // TMA delivered the chunk's slabs
-    auto xlo_full = [&](int s) { return bar0 + 8u * (kXStages + s); };        // split warps wrote their lo parts
-    auto x_empty = [&](int s) { return bar0 + 8u * (2 * kXStages + s); };     // the MMAs reading the stage completed
-    auto dy_full = [&](int s) { return bar0 + 8u * (3 * kXStages + s); };
-    auto dylo_full = [&](int s) { return bar0 + 8u * (3 * kXStages + kDyStages + s); };
-    auto dy_empty = [&](int s) { return bar0 + 8u * (3 * kXStages + 2 * kDyStages + s); };
-    auto p_ready = [&](int c) { return bar0 + 8u * (3 * kXStages + 3 * kDyStages + c); };
-    auto p_taken = [&](int c) { return bar0 + 8u * (3 * kXStages + 3 * kDyStages + kChunks + c); };
+    auto x_full = [&](int s) { return bar0 + 8u * s; };                      // TMA delivered the unit's slabs
+    auto x_empty = [&](int s) { return bar0 + 8u * (kStages + s); };         // the split warps have read them
+    auto a_empty = [&](int s) { return bar0 + 8u * (2 * kStages + s); };     // the MMAs reading the tensor-memory stage completed
+    auto dy_full = [&](int s) { return bar0 + 8u * (3 * kStages + s); };
+    auto dylo_full = [&](int s) { return bar0 + 8u * (3 * kStages + kDyStages + s); };
+    auto dy_empty = [&](int s) { return bar0 + 8u * (3 * kStages + 2 * kDyStages + s); };
+    auto p_ready = [&](int c) { return bar0 + 8u * (3 * kStages + 3 * kDyStages + c); };
+    auto p_taken = [&](int c) { return bar0 + 8u * (3 * kStages + 3 * kDyStages + kChunks + c); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + kOffMisc);
+    // misc[0]: tensor-memory base address, misc[1]: abort flag, misc[2 + stage]: how many split warps have
+    // completed a copy into that tensor-memory stage so far -- its u-th unit may be read at 4 * (u + 1)
+    auto a_count = [&](int s) { return smem_base + kOffMisc + 8u + 4u * s; };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kXStages; ++s) { mbar_init(x_full(s), 1); mbar_init(xlo_full(s), 128); mbar_init(x_empty(s), 1); }
-        for (int s = 0; s < kDyStages; ++s) { mbar_init(dy_full(s), 1); mbar_init(dylo_full(s), 128); mbar_init(dy_empty(s), 2); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); mbar_init(a_empty(s), 1); }
+        for (int s = 0; s < kDyStages; ++s) { mbar_init(dy_full(s), 1); mbar_init(dylo_full(s), 32); mbar_init(dy_empty(s), nchunks); }
         for (int c = 0; c < kChunks; ++c) { mbar_init(p_ready(c), 1); mbar_init(p_taken(c), 128); }
         misc[1] = 0;
+        for (int s = 0; s < kStages; ++s) misc[2 + s] = 0;
         fence_mbar_init();
     }
-    if (warp == 1) {
+    if (warp == kFirstMmaWarp) {
         tmem_alloc(smem_base + kOffMisc, kTmemCols);
         tmem_relinquish();
     }
@@ -123,138 +141,165 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     const uint32_t tmem = misc[0];
     volatile uint32_t* abort_flag = &misc[1];
 
+    // Waits do not branch on their result in the common case (a conditional branch costs a lone warp ~40
+    // cycles).  A wait that gives up (bounded, see mbar_wait) sets `bad`; the issuing instructions are
+    // predicated on it and the role loops test it once per iteration.
+    uint32_t bad = 0;
+    auto wait = [&](uint32_t bar, uint32_t parity) {
+        if (!mbar_try_wait(bar, parity) && !mbar_wait(bar, parity, abort_flag)) bad = 1;
+    };
+    auto wait_count = [&](uint32_t addr, uint32_t target) {  // bounded like mbar_wait
+        if ((int32_t)(smem_load_acquire(addr) - target) < 0) {
+            const long long t0 = clock64();
+            for (;;) {
+                if ((int32_t)(smem_load_acquire(addr) - target) >= 0) break;
+                if (*abort_flag != 0) { bad = 1; break; }
+                if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; bad = 1; break; }
+            }
+        }
+    };
+
     // the item's CSR entries, one per lane (at most 16), handed out by shuffle
     const int2 my_ent = lane < nblk ? __ldg(p.idx + ent0 + lane) : make_int2(0, 0);
 
     // a step is a promotion point when it closes a 1024-token segment or the token range
     auto drain_step = [&](int step) { return ((step + 1) % kDrainSteps) == 0 || step + 1 == nsteps; };
 
-    // The producer and MMA warps run their loops with all 32 lanes in lock-step and elect one lane only
-    // for the single-thread instructions, which keeps those instructions' operands in uniform registers.
-    if (warp == 0) {
-        // ------------------------------------------------------------------ producer
-        int xs = 0, ds = 0;
-        uint32_t xph = 0, dph = 0;
-        bool ok = true;
-        for (int step = 0; step < nsteps && ok; ++step) {
+    if (warp < kXProducers) {
+        // ------------------------------------------------------------------ X producers
+        int step = 0, ch = warp;
+        while (ch >= nchunks) { ch -= nchunks; ++step; }
+        for (int u = warp; u < nunits && !bad; u += kXProducers) {
+            const int xs = u & (kStages - 1);
+            const int nb = min(4, nblk - ch * 4);
             const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
-            ok = mbar_wait(dy_empty(ds), dph ^ 1u, abort_flag);
-            if (!ok) break;
-            if (elect_one()) {
+            int bcol[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) bcol[j] = __shfl_sync(0xffffffffu, my_ent.x, ch * 4 + j);
+            wait(x_empty(xs), ((uint32_t)(u / kStages) & 1u) ^ 1u);
+            const uint32_t dst = smem_base + kOffX + xs * kXStageBytes;
+            if (elect_one() && !bad) {
+                mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (j < nb) tma_load_2d(dst + j * kSlabBytes, &tmap_x, bcol[j] * 32, tok, x_full(xs));
+            }
+            ch += kXProducers;
+            while (ch >= nchunks) { ch -= nchunks; ++step; }
+        }
+    } else if (warp == kDyProducerWarp) {
+        // ------------------------------------------------------------------ dY producer
+        for (int step = 0; step < nsteps && !bad; ++step) {
+            const int ds = step & (kDyStages - 1);
+            const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
+            wait(dy_empty(ds), ((uint32_t)(step / kDyStages) & 1u) ^ 1u);
+            if (elect_one() && !bad) {
                 mbar_arrive_expect_tx(dy_full(ds), kSlabBytes);
                 tma_load_2d(smem_base + kOffDy + ds * kDyStageBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
             }
-            if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
-            for (int ch = 0; ch < nchunks; ++ch) {
-                const int nb = min(4, nblk - ch * 4);
-                int bcol[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) bcol[j] = __shfl_sync(0xffffffffu, my_ent.x, ch * 4 + j);
-                ok = mbar_wait(x_empty(xs), xph ^ 1u, abort_flag);
-                if (!ok) break;
-                const uint32_t dst = smem_base + kOffX + xs * kXStageBytes;
-                if (elect_one()) {
-                    mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (j < nb) tma_load_2d(dst + j * kSlabBytes, &tmap_x, bcol[j] * 32, tok, x_full(xs));
-                }
-                if (++xs == kXStages) { xs = 0; xph ^= 1u; }
-            }
         }
-    } else if (warp <= 2) {
-        // ------------------------------------------------------------------ MMA issuers
-        // two warps share the chunks by parity; both walk every chunk so that their stage counters agree
-        const int mw = warp - 1;
-        constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, true, true);
-        constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, true, true);
-        int xs = 0, ds = 0;
-        uint32_t xph = 0, dph = 0;
-        uint32_t pending = 0, taken_ph = 0;
-        bool ok = true;
-        for (int step = 0; step < nsteps && ok; ++step) {
-            ok = mbar_wait(dylo_full(ds), dph, abort_flag);
-            if (!ok) break;
-            // B: atom 0 = the raw dY slab, atom 1 (N = 64 only) = its lo part, one slab further
-            const uint64_t b_desc = smem_desc_mnmajor_sw128(smem_base + kOffDy + ds * kDyStageBytes, kSlabBytes);
-            const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
-            const bool drain = drain_step(step);
-            for (int ch = 0; ch < nchunks; ++ch) {
-                if ((ch & 1) != mw) {
-                    if (++xs == kXStages) { xs = 0; xph ^= 1u; }
-                    continue;
-                }
-                ok = mbar_wait(xlo_full(xs), xph, abort_flag);
-                if (!ok) break;
-                if (fresh && ((pending >> ch) & 1u)) {
-                    ok = mbar_wait(p_taken(ch), (taken_ph >> ch) & 1u, abort_flag);
-                    if (!ok) break;
-                    taken_ph ^= 1u << ch;
-                    pending &= ~(1u << ch);
-                    tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the columns
-                }
-                // A: four atoms (the chunk's slabs) one slab apart; the lo parts follow kXHalfBytes further
-                const uint64_t a_desc = smem_desc_mnmajor_sw128(smem_base + kOffX + xs * kXStageBytes, kSlabBytes);
-                const uint32_t d = tmem + ch * kChunkCols;
-                const uint32_t acc0 = fresh ? 0u : 1u;
-                const uint32_t x_bar = x_empty(xs), p_bar = p_ready(ch);
-                if (elect_one()) {
+    } else if (warp == kDySplitWarp) {
+        // ------------------------------------------------------------------ dY split
+        // lo = v - trunc_tf32(v), elementwise at the same offset of the stage's second half: the swizzle
+        // needs no decoding; consecutive lanes take consecutive 16-byte chunks
+        for (int step = 0; step < nsteps; ++step) {
+            const int ds = step & (kDyStages - 1);
+            wait(dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
+            if (__any_sync(0xffffffffu, bad != 0)) break;
+            uint8_t* base = smem_gen + kOffDy + ds * kDyStageBytes;
 #pragma unroll
-                    for (int s = 0; s < 4; ++s) {
-                        const uint64_t a = a_desc + (uint64_t)(s * (kKStepBytes >> 4));
-                        const uint64_t b = b_desc + (uint64_t)(s * (kKStepBytes >> 4));
-                        mma_ss_tf32(d, a, b, idesc_wide, s == 0 ? acc0 : 1u);                          // x x [dy ; dy_lo]
-                        mma_ss_tf32(d + 32, a + (uint64_t)(kXHalfBytes >> 4), b, idesc_narrow, 1u);    // x_lo x dy
-                    }
-                    mma_commit(x_bar);
-                    if (drain) mma_commit(p_bar);
-                }
-                if (++xs == kXStages) { xs = 0; xph ^= 1u; }
-                if (drain) pending |= 1u << ch;
-            }
-            if (!ok) break;
-            const uint32_t dy_bar = dy_empty(ds);
-            if (elect_one()) mma_commit(dy_bar);
-            if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
-        }
-    } else if (warp < 7) {
-        // ------------------------------------------------------------------ split
-        const int tt = (warp - 3) * 32 + lane;  // 0..127 over the four split warps
-        int xs = 0, ds = 0;
-        uint32_t xph = 0, dph = 0;
-        bool ok = true;
-        // lo = v - trunc_tf32(v), elementwise at the same offset of the stage's second half: the 128-byte
-        // swizzle needs no decoding; consecutive threads take consecutive 16-byte chunks
-        auto split16 = [](const uint8_t* src, uint8_t* dst) {
-            const float4 v = *reinterpret_cast<const float4*>(src);
-            float4 l;
-            l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
-            l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
-            l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
-            l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-            *reinterpret_cast<float4*>(dst) = l;
-        };
-        for (int step = 0; step < nsteps && ok; ++step) {
-            ok = __all_sync(0xffffffffu, mbar_wait(dy_full(ds), dph, abort_flag));
-            if (!ok) break;
-            {
-                uint8_t* base = smem_gen + kOffDy + ds * kDyStageBytes;
-#pragma unroll
-                for (int i = 0; i < 2; ++i) split16(base + (tt + 128 * i) * 16, base + kSlabBytes + (tt + 128 * i) * 16);
+            for (int i = 0; i < 8; ++i) {
+                const float4 v = *reinterpret_cast<const float4*>(base + (lane + 32 * i) * 16);
+                float4 l;
+                l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+                l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+                l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+                l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+                *reinterpret_cast<float4*>(base + kSlabBytes + (lane + 32 * i) * 16) = l;
             }
             fence_proxy_async_smem();  // generic-proxy writes, read by the MMA through the async proxy
             mbar_arrive(dylo_full(ds));
-            if (++ds == kDyStages) { ds = 0; dph ^= 1u; }
-            for (int ch = 0; ch < nchunks; ++ch) {
-                const int nb = min(4, nblk - ch * 4);
-                ok = __all_sync(0xffffffffu, mbar_wait(x_full(xs), xph, abort_flag));
-                if (!ok) break;
-                uint8_t* base = smem_gen + kOffX + xs * kXStageBytes;
-                for (int i = 0; i < 2 * nb; ++i) split16(base + (tt + 128 * i) * 16, base + kXHalfBytes + (tt + 128 * i) * 16);
-                fence_proxy_async_smem();
-                mbar_arrive(xlo_full(xs));
-                if (++xs == kXStages) { xs = 0; xph ^= 1u; }
+        }
+    } else if (warp < kFirstSplitWarp) {
+        // ------------------------------------------------------------------ MMA issuers
+        const int ch = warp - kFirstMmaWarp;  // accumulations into one chunk stay in one thread's program order
+        constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, true);
+        constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, true);
+        bool pending = false;   // a promotion of the chunk was requested and not yet seen taken
+        uint32_t taken_ph = 0;
+        for (int step = 0; step < nsteps && !bad && ch < nchunks; ++step) {
+            const int u = step * nchunks + ch;
+            const int as = u & (kStages - 1);
+            const int ds = step & (kDyStages - 1);
+            const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
+            const bool drain = drain_step(step);
+            wait(dylo_full(ds), (uint32_t)(step / kDyStages) & 1u);
+            wait_count(a_count(as), 4u * (uint32_t)(u / kStages + 1));
+            tc_fence_after();  // the split warps' tcgen05.st precede the MMAs that read the stage
+            if (fresh && pending) {
+                wait(p_taken(ch), taken_ph);
+                taken_ph ^= 1u;
+                pending = false;
+                tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the columns
             }
+            // B: atom 0 = the raw dY slab, atom 1 (N = 64 only) = its lo part, one slab further
+            const uint64_t b_desc = smem_desc_mnmajor_sw128(smem_base + kOffDy + ds * kDyStageBytes, kSlabBytes);
+            const uint32_t a_tm = tmem + kAccCols + as * kAStageCols;
+            const uint32_t d = tmem + ch * kChunkCols;
+            const uint32_t acc0 = fresh ? 0u : 1u;
+            const uint32_t a_bar = a_empty(as), dy_bar = dy_empty(ds), p_bar = p_ready(ch);
+            if (elect_one() && !bad) {
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const uint64_t b = b_desc + (uint64_t)(s * (kKStepBytes >> 4));
+                    mma_ts_tf32(d, a_tm + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);     // x x [dy ; dy_lo]
+                    mma_ts_tf32(d + 32, a_tm + 32 + s * 8, b, idesc_narrow, 1u);         // x_lo x dy
+                }
+                mma_commit(a_bar);
+                mma_commit(dy_bar);
+                if (drain) mma_commit(p_bar);
+            }
+            if (drain) pending = true;
+        }
+    } else if (warp < kFirstDrainWarp) {
+        // ------------------------------------------------------------------ X split
+        // Thread (quarter j, lane c) owns feature c of the unit's block j = tensor-memory lane 32 j + c and
+        // reads that feature of the slab's 32 tokens: with the 128-byte swizzle (16-byte chunk index XOR
+        // token mod 8) the 32 lanes of a warp hit 32 different banks.
+        const int quarter = warp & 3;
+        const int group = (warp - kFirstSplitWarp) >> 2;
+        const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        int ch = group;
+        while (ch >= nchunks) ch -= nchunks;
+        for (int u = group; u < nunits; u += 2) {
+            const int xs = u & (kStages - 1);
+            const int nb = min(4, nblk - ch * 4);
+            wait(x_full(xs), (uint32_t)(u / kStages) & 1u);
+            uint32_t hi[32], lo[32];
+            if (quarter < nb) {
+                const uint8_t* col = smem_gen + kOffX + xs * kXStageBytes + quarter * kSlabBytes + ((lane & 3) << 2);
+#pragma unroll
+                for (int t = 0; t < 32; ++t) {
+                    const uint32_t v = *reinterpret_cast<const uint32_t*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
+                    hi[t] = v;
+                    lo[t] = __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xffffe000u));
+                }
+            } else {  // no block there: the rows are never stored, keep them finite
+#pragma unroll
+                for (int t = 0; t < 32; ++t) { hi[t] = 0u; lo[t] = 0u; }
+            }
+            mbar_arrive(x_empty(xs));
+            wait(a_empty(xs), ((uint32_t)(u / kStages) & 1u) ^ 1u);
+            tc_fence_after();
+            const uint32_t a_tm = tmem_lane + kAccCols + xs * kAStageCols;
+            tmem_st32(a_tm, hi);
+            tmem_st32(a_tm + 32, lo);
+            tmem_wait_st();
+            tc_fence_before();
+            if (__any_sync(0xffffffffu, bad != 0)) break;  // nothing is published once a wait has given up
+            if (lane == 0) smem_add_release(a_count(xs), 1u);
+            ch += 2;
+            while (ch >= nchunks) ch -= nchunks;
         }
     } else {
         // ------------------------------------------------------------------ drain + epilogue
@@ -274,7 +319,8 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         for (int step = 0; step < nsteps && ok; ++step) {
             if (!drain_step(step)) continue;
             for (int ch = 0; ch < nchunks; ++ch) {
-                ok = __all_sync(0xffffffffu, mbar_wait(p_ready(ch), (ready_ph >> ch) & 1u, abort_flag));
+                wait(p_ready(ch), (ready_ph >> ch) & 1u);
+                ok = !__any_sync(0xffffffffu, bad != 0);
                 if (!ok) break;
                 ready_ph ^= 1u << ch;
                 tc_fence_after();
@@ -324,7 +370,7 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag != 0) atomicOr(p.status, 1u);
-    if (warp == 1) {
+    if (warp == kFirstMmaWarp) {
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
@@ -481,7 +527,7 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     if (err != cudaSuccess) return err;
     CUtensorMap tmap_x, tmap_dy;
     err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)cols, (uint64_t)tokens, 32,
-                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess) return err;
     err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)rows, (uint64_t)tokens, 32,
                        kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
