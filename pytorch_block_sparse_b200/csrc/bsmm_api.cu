@@ -68,8 +68,11 @@ int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz, uint32_t preci
     const bool wide_ok = (precision & BSMM_PREC_MASK) != BSMM_PREC_TF32X3;  // 3xTF32 rows take 64 columns
     if (m <= 0 || n_out_blocks <= 0) return wide_ok ? 8 : 6;
     // The widest tile re-uses each activation slab most; narrower tiles are only worth it when the
-    // wide one would leave most of the 148 SMs without a CTA.
+    // wide one would leave most of the 148 SMs without a CTA.  3xTF32 at 6 rows has room for only two
+    // activation stages in tensor memory, which serialises the split warps and the MMAs: with several waves
+    // of CTAs the 4-row tile (four stages) is faster at every density measured.
     const int64_t tiles = (m + 127) / 128;
+    if (!wide_ok && tiles * ((n_out_blocks + 5) / 6) >= 4 * 148) return 4;
     for (int g : {8, 6}) {
         if (g == 8 && !wide_ok) continue;
         if (tiles * ((n_out_blocks + g - 1) / g) >= 148) return g;
@@ -142,7 +145,7 @@ int bsmm_build_sddmm_plan(const int32_t* ptr, int64_t n_block_rows, int64_t nnz,
 int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t flags) {
     if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0) return -1;
     const uint32_t precision = flags & BSMM_PREC_MASK;
-    if (precision != BSMM_PREC_TF32X3) return 0;
+    if (!bsmm::is_tf32_precision(precision)) return 0;
     if ((flags & (BSMM_SDDMM_A_COLMAJOR | BSMM_SDDMM_B_COLMAJOR)) != 0) return 0;
     return bsmm::sddmm_umma_workspace_bytes(rows, cols, tokens, nnz, precision);
 }
@@ -162,9 +165,9 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
         !aligned(plan, 16) || !aligned(workspace, 16))
         return BSMM_ERR_INVALID_ARGUMENT;
     if (nnz > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
-    if (precision != BSMM_PREC_FP32_SIMT && precision != BSMM_PREC_TF32X3) return BSMM_ERR_UNSUPPORTED;
+    if (precision != BSMM_PREC_FP32_SIMT && !bsmm::is_tf32_precision(precision)) return BSMM_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (precision == BSMM_PREC_TF32X3 && !a_col && !b_col) {
+    if (bsmm::is_tf32_precision(precision) && !a_col && !b_col) {
         const cudaError_t err = bsmm::launch_sddmm_umma(a, b, rows, cols, tokens, sparse_c, csr_idx, plan, nnz,
                                                         block_sumsq, workspace, precision, s);
         if (err != cudaErrorNotSupported) return cuda_status(err);

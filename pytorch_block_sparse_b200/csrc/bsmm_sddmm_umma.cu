@@ -90,8 +90,10 @@ __device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint3
     return smem_desc_sw128_base32(addr, atom_stride, 512);
 }
 
+// kPasses = 3: 3xTF32 as described above; kPasses = 1: single-pass TF32 (no lo parts, no correction columns)
+template <int kPasses>
 __global__ void __launch_bounds__(kThreads, 1)
-sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
+sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
                          const SddmmParams p) {
     const int n_items = p.items[0];
     if ((int)blockIdx.x >= n_items) return;
@@ -202,7 +204,7 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
         // ------------------------------------------------------------------ dY split
         // lo = v - trunc_tf32(v), elementwise at the same offset of the stage's second half: the swizzle
         // needs no decoding; consecutive lanes take consecutive 16-byte chunks
-        for (int step = 0; step < nsteps; ++step) {
+        for (int step = 0; step < nsteps && kPasses == 3; ++step) {
             const int ds = step & (kDyStages - 1);
             wait(dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
             if (__any_sync(0xffffffffu, bad != 0)) break;
@@ -233,7 +235,7 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
             const int ds = step & (kDyStages - 1);
             const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
             const bool drain = drain_step(step);
-            wait(dylo_full(ds), (uint32_t)(step / kDyStages) & 1u);
+            wait(kPasses == 3 ? dylo_full(ds) : dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
             wait_count(a_count(as), 4u * (uint32_t)(u / kStages + 1));
             tc_fence_after();  // the split warps' tcgen05.st precede the MMAs that read the stage
             if (fresh && pending) {
@@ -252,8 +254,12 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
 #pragma unroll
                 for (int s = 0; s < 4; ++s) {
                     const uint64_t b = b_desc + (uint64_t)(s * (kKStepBytes >> 4));
-                    mma_ts_tf32(d, a_tm + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);     // x x [dy ; dy_lo]
-                    mma_ts_tf32(d + 32, a_tm + 32 + s * 8, b, idesc_narrow, 1u);         // x_lo x dy
+                    if (kPasses == 3) {
+                        mma_ts_tf32(d, a_tm + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);     // x x [dy ; dy_lo]
+                        mma_ts_tf32(d + 32, a_tm + 32 + s * 8, b, idesc_narrow, 1u);         // x_lo x dy
+                    } else {
+                        mma_ts_tf32(d, a_tm + s * 8, b, idesc_narrow, s == 0 ? acc0 : 1u);
+                    }
                 }
                 mma_commit(a_bar);
                 mma_commit(dy_bar);
@@ -282,7 +288,7 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                 for (int t = 0; t < 32; ++t) {
                     const uint32_t v = *reinterpret_cast<const uint32_t*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
                     hi[t] = v;
-                    lo[t] = __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xffffe000u));
+                    if (kPasses == 3) lo[t] = __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xffffe000u));
                 }
             } else {  // no block there: the rows are never stored, keep them finite
 #pragma unroll
@@ -293,7 +299,7 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
             tc_fence_after();
             const uint32_t a_tm = tmem_lane + kAccCols + xs * kAStageCols;
             tmem_st32(a_tm, hi);
-            tmem_st32(a_tm + 32, lo);
+            if (kPasses == 3) tmem_st32(a_tm + 32, lo);
             tmem_wait_st();
             tc_fence_before();
             if (__any_sync(0xffffffffu, bad != 0)) break;  // nothing is published once a wait has given up
@@ -326,8 +332,12 @@ sddmm_umma_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_x, const __gri
                 tc_fence_after();
                 uint32_t acc[32], corr[32];
                 tmem_ld32(tmem_lane + ch * kChunkCols, acc);
-                tmem_ld32(tmem_lane + ch * kChunkCols + 32, corr);
+                if (kPasses == 3) tmem_ld32(tmem_lane + ch * kChunkCols + 32, corr);
                 tmem_wait_ld();
+                if (kPasses != 3) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) corr[j] = 0u;
+                }
                 tc_fence_before();
                 mbar_arrive(p_taken(ch));
 #pragma unroll
@@ -504,7 +514,7 @@ cudaError_t launch_build_sddmm_plan(const int32_t* ptr, int64_t n_rows, int64_t 
 }
 
 int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t precision) {
-    if (precision != BSMM_PREC_TF32X3 || tokens < kStepTokens || nnz == 0) return 0;
+    if (!is_tf32_precision(precision) || tokens < kStepTokens || nnz == 0) return 0;
     int64_t splits, per;
     choose_splits(rows / 32, cols, nnz, tokens, &splits, &per);
     return splits > 1 ? splits * nnz * (int64_t)kBlockElems * 4 : 0;
@@ -513,7 +523,7 @@ int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, i
 cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens,
                               float* sparse_c, const int32_t* csr_idx, const void* plan, int64_t nnz,
                               float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream) {
-    if (precision != BSMM_PREC_TF32X3 || plan == nullptr || csr_idx == nullptr) return cudaErrorNotSupported;
+    if (!is_tf32_precision(precision) || plan == nullptr || csr_idx == nullptr) return cudaErrorNotSupported;
     if (tokens < kStepTokens) return cudaErrorNotSupported;  // a box may not exceed its tensor
     if (tokens > 0x7fffffffll) return cudaErrorInvalidValue;
     const int64_t n_rows = rows / 32;
@@ -522,8 +532,9 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     if (splits > 1 && workspace == nullptr) return cudaErrorInvalidValue;
     if (splits > 65535) return cudaErrorInvalidValue;
 
-    cudaError_t err = cudaFuncSetAttribute(sddmm_umma_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)kSmemBytes);
+    const bool x3 = precision == BSMM_PREC_TF32X3;
+    cudaError_t err = cudaFuncSetAttribute(x3 ? sddmm_umma_tf32_kernel<3> : sddmm_umma_tf32_kernel<1>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (err != cudaSuccess) return err;
     CUtensorMap tmap_x, tmap_dy;
     err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)cols, (uint64_t)tokens, 32,
@@ -544,7 +555,8 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     p.tokens_per_split = per;
     p.split_stride = nnz * (int64_t)kBlockElems;
     dim3 grid((unsigned)max_items(n_rows, nnz), (unsigned)splits);
-    sddmm_umma_tf32x3_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
+    if (x3) sddmm_umma_tf32_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
+    else sddmm_umma_tf32_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     if (splits > 1) {

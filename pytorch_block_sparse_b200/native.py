@@ -294,8 +294,8 @@ def sddmm(a, a_rowmajor, b, b_rowmajor, blocks, out, precision=None, block_sumsq
     _need_cuda(a, "dense_a")
     lib = load()
     prec = resolve_precision(precision) if not isinstance(precision, int) else precision
-    if prec in (PREC_TF32, PREC_BF16):
-        prec = PREC_TF32X3  # the weight gradient is always accumulated in the fp32-class mode
+    if prec == PREC_BF16:
+        prec = PREC_TF32X3  # no bf16 weight-gradient kernel: use the fp32-class mode
     tokens, rows = a.shape
     cols = b.shape[1]
     nnz = blocks.shape[0] // 2

@@ -44,7 +44,8 @@ def test_size_queries():
     assert lib.bsmm_plan_bytes(16, 100, 4) == 48 + 100 * 16
     assert lib.bsmm_plan_bytes(16, 100, 5) == -1
     assert lib.bsmm_plan_group(16384, 128, 4096, native.PREC_TF32) == 8
-    assert lib.bsmm_plan_group(16384, 128, 4096, native.PREC_TF32X3) == 6
+    assert lib.bsmm_plan_group(16384, 128, 4096, native.PREC_TF32X3) == 4  # many waves: four activation stages
+    assert lib.bsmm_plan_group(4096, 96, 2304, native.PREC_TF32X3) == 6
     assert lib.bsmm_plan_group(128, 24, 288, native.PREC_TF32X3) == 4
     assert lib.bsmm_packed_bytes(10, native.PREC_TF32) == 2 * 10 * 8192
     assert lib.bsmm_sddmm_plan_bytes(8, 100) == 16 + 16 * (100 // 16 + 8)

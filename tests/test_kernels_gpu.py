@@ -257,6 +257,19 @@ def test_plan_is_the_group_merge_of_the_csr(group):
                              | ((idle << 4) if last else 0))
 
 
+def test_single_pass_tf32_wgrad():
+    """Opt-in 'tf32' precision of the weight gradient: bound 2e-3 relative Frobenius; 2100 tokens cross two
+    promotion points and leave a ragged last step."""
+    m = make_matrix((256, 384), n_blocks=40, seed=31)
+    dy, x = randn((2100, 256), seed=32), randn((2100, 384), seed=33)
+    got = m.matmul_with_output_sparse_support(dy.cuda(), x.cuda(), precision="tf32")
+    torch.cuda.synchronize()
+    want = orc.wgrad(dy.numpy(), x.numpy(), tuple(m.shape), m.blocks.cpu().numpy())
+    check(got, want, "tf32", "wgrad")
+    assert orc.rel_fro(got.float().cpu().numpy().reshape(want.shape), want) > 1e-6  # really the single pass
+    assert_device_healthy()
+
+
 @pytest.mark.parametrize("group", ["4", "6", "8"])
 def test_dsd_every_tile_width(group, monkeypatch):
     monkeypatch.setenv("BSMM_PLAN_GROUP", group)
