@@ -84,6 +84,7 @@ struct DsdParams {
     unsigned int* status;       // device status word
     int64_t m, n;
     int32_t n_out_blocks, groups;
+    int32_t n_tiles;            // groups x token tiles; CTA b works on tiles b, b + gridDim.x, ...
     int32_t out_colmajor;
     uint32_t x_bytes;           // bytes one activation-slab load delivers: min(128, m) rows of 128 B
     long long* trace;           // diagnostics: 32 wait-cycle counters of CTA `trace_block`, or null
@@ -124,12 +125,6 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-
-    const int g = blockIdx.x % p.groups;
-    const int64_t tok0 = (int64_t)(blockIdx.x / p.groups) * kTileTokens;
-    const int e0 = p.group_off[g], e1 = p.group_off[g + 1];
-    const int nslabs = p.group_slabs[g];
-    const int nrows = min(G, p.n_out_blocks - g * G);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < XS; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); }
@@ -179,15 +174,33 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         }
         if (tracing) tr[0] += clock64() - t;
     };
+    // The kernel is persistent: CTA b works on tiles b, b + gridDim.x, ...  (tile = group of G output
+    // block-rows x 128 tokens), so the barrier and tensor-memory set-up is paid once and one tile's epilogue
+    // overlaps the next tile's loads.  Every role walks the same tile sequence; ring positions (entry, slab
+    // and promotion counts) run on across tiles.
     const int4* ents = reinterpret_cast<const int4*>(p.entries);
-    auto fetch = [&](int i) { return i < e1 ? __ldg(ents + i) : make_int4(0, 0, 0, 0); };  // x inner, y slot, z row, w flags
+    const int n_tiles = p.n_tiles, tile_step = (int)gridDim.x;
+    auto fetch = [&](int i, int end) { return i < end ? __ldg(ents + i) : make_int4(0, 0, 0, 0); };  // x inner, y slot, z row, w flags
+    // The plan is read 32 entries per load (lane i holds entry base + i), one chunk ahead of use -- across
+    // tile boundaries too: `ahead` is the chunk after (tile, base).
+    auto prefetch = [&](int tile, int base, int e1) {
+        if (base + 32 < e1) return fetch(base + 32 + lane, e1);
+        const int nt = tile + tile_step;
+        if (nt >= n_tiles) return make_int4(0, 0, 0, 0);
+        const int ng = nt % p.groups;
+        return fetch(__ldg(p.group_off + ng) + lane, __ldg(p.group_off + ng + 1));
+    };
+    auto first_chunk = [&]() {
+        if ((int)blockIdx.x >= n_tiles) return make_int4(0, 0, 0, 0);
+        const int g0 = (int)blockIdx.x % p.groups;
+        return fetch(__ldg(p.group_off + g0) + lane, __ldg(p.group_off + g0 + 1));
+    };
 
     // Control warps are latency machines: one warp executing dependent scalar code retires an instruction
-    // every few cycles, a successful barrier wait costs ~85 cycles and a global load ~1000, while the tensor
-    // core needs only ~250 cycles for a block.  Hence: the plan is read 32 entries per load (lane i holds
-    // entry base + i) one chunk ahead of use; the flag bits and row numbers of a chunk become warp-uniform
-    // bit masks (ballots) and the per-entry decisions are bit tests; ring stages follow from entry and slab
-    // numbers, so a warp visits only the entries it has work for; the lane that holds an entry issues its loads.
+    // every few cycles, a conditional branch costs ~40 cycles, a successful barrier wait ~85 and a global load
+    // ~1000, while the tensor core needs only ~200 cycles for a block.  Hence: the flag bits and row numbers
+    // of a chunk become warp-uniform bit masks (ballots) and the per-entry decisions are bit tests; ring
+    // stages follow from entry and slab counts, so a warp visits only the entries it has work for.
     if (warp < kWProducers) {
         // ------------------------------------------------------------------ weight producers
         // every MMA warp has a ring of kWRing stages of its own, filled in the order of that warp's blocks: a
@@ -195,34 +208,38 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         uint32_t issued[kMmaWarps];  // blocks already loaded per MMA warp
 #pragma unroll
         for (int w = 0; w < kMmaWarps; ++w) issued[w] = 0;
-        int4 ahead = fetch(e0 + lane);
-        for (int base = e0; base < e1 && !bad; base += 32) {
-            const int4 mine = ahead;
-            ahead = fetch(base + 32 + lane);
-            const int count = min(32, e1 - base);
-            const uint32_t owner = (uint32_t)mine.z & (kMmaWarps - 1);
-            uint32_t seq = 0;  // this lane's block is the seq-th of its MMA warp
+        int4 ahead = first_chunk();
+        for (int tile = blockIdx.x; tile < n_tiles && !bad; tile += tile_step) {
+            const int g = tile % p.groups;
+            const int e0 = __ldg(p.group_off + g), e1 = __ldg(p.group_off + g + 1);
+            for (int base = e0; base < e1 && !bad; base += 32) {
+                const int4 mine = ahead;
+                ahead = prefetch(tile, base, e1);
+                const int count = min(32, e1 - base);
+                const uint32_t owner = (uint32_t)mine.z & (kMmaWarps - 1);
+                uint32_t seq = 0;  // this lane's block is the seq-th of its MMA warp
 #pragma unroll
-            for (int w = 0; w < kMmaWarps; ++w) {
-                const uint32_t same = __ballot_sync(0xffffffffu, owner == (uint32_t)w && lane < count);
-                if (owner == (uint32_t)w) seq = issued[w] + __popc(same & ((1u << lane) - 1u));
-                issued[w] += __popc(same);
-            }
-            const uint32_t stage_use = (owner * kWRing + (seq & (kWRing - 1))) | (((seq / kWRing) & 1u) << 8);
-            // a stage is always filled by the same producer warp (stage number mod kWProducers), which thus
-            // sees every phase of the stage's barriers
-            uint32_t todo = __ballot_sync(0xffffffffu, lane < count && (seq & (kWProducers - 1)) == (uint32_t)warp);
-            while (todo != 0) {
-                const int i = __ffs(todo) - 1;
-                todo &= todo - 1;
-                const uint32_t su = __shfl_sync(0xffffffffu, stage_use, i);
-                const int slot = __shfl_sync(0xffffffffu, mine.y, i);
-                const int ws = (int)(su & 0xffu);
-                wait(w_empty(ws), (su >> 8) ^ 1u, 1);
-                const uint8_t* src = p.packed + (int64_t)slot * kWStageBytes;
-                if (elect_one() && !bad) {
-                    mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
-                    bulk_load(smem_base + C::kOffW + ws * kWStageBytes, src, kWStageBytes, w_full(ws));
+                for (int w = 0; w < kMmaWarps; ++w) {
+                    const uint32_t same = __ballot_sync(0xffffffffu, owner == (uint32_t)w && lane < count);
+                    if (owner == (uint32_t)w) seq = issued[w] + __popc(same & ((1u << lane) - 1u));
+                    issued[w] += __popc(same);
+                }
+                const uint32_t stage_use = (owner * kWRing + (seq & (kWRing - 1))) | (((seq / kWRing) & 1u) << 8);
+                // a stage is always filled by the same producer warp (stage number mod kWProducers), which thus
+                // sees every phase of the stage's barriers
+                uint32_t todo = __ballot_sync(0xffffffffu, lane < count && (seq & (kWProducers - 1)) == (uint32_t)warp);
+                while (todo != 0) {
+                    const int i = __ffs(todo) - 1;
+                    todo &= todo - 1;
+                    const uint32_t su = __shfl_sync(0xffffffffu, stage_use, i);
+                    const int slot = __shfl_sync(0xffffffffu, mine.y, i);
+                    const int ws = (int)(su & 0xffu);
+                    wait(w_empty(ws), (su >> 8) ^ 1u, 1);
+                    const uint8_t* src = p.packed + (int64_t)slot * kWStageBytes;
+                    if (elect_one() && !bad) {
+                        mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
+                        bulk_load(smem_base + C::kOffW + ws * kWStageBytes, src, kWStageBytes, w_full(ws));
+                    }
                 }
             }
         }
@@ -234,21 +251,26 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         // ------------------------------------------------------------------ activation producer
         int xs = 0;
         uint32_t xph = 0;
-        int4 ahead = fetch(e0 + lane);
-        for (int base = e0; base < e1 && !bad; base += 32) {
-            const int4 mine = ahead;
-            ahead = fetch(base + 32 + lane);
-            uint32_t firsts = __ballot_sync(0xffffffffu, (mine.w & kPlanFirst) != 0);
-            while (firsts != 0) {
-                const int i = __ffs(firsts) - 1;
-                firsts &= firsts - 1;
-                wait(x_empty(xs), xph ^ 1u, 0);
-                const int inner = __shfl_sync(0xffffffffu, mine.x, i);
-                if (elect_one() && !bad) {
-                    mbar_arrive_expect_tx(x_full(xs), p.x_bytes);
-                    tma_load_2d(smem_base + C::kOffX + xs * kSlabBytes, &tmap_a, inner * 32, (int32_t)tok0, x_full(xs));
+        int4 ahead = first_chunk();
+        for (int tile = blockIdx.x; tile < n_tiles && !bad; tile += tile_step) {
+            const int g = tile % p.groups;
+            const int32_t tok0 = (tile / p.groups) * kTileTokens;
+            const int e0 = __ldg(p.group_off + g), e1 = __ldg(p.group_off + g + 1);
+            for (int base = e0; base < e1 && !bad; base += 32) {
+                const int4 mine = ahead;
+                ahead = prefetch(tile, base, e1);
+                uint32_t firsts = __ballot_sync(0xffffffffu, (mine.w & kPlanFirst) != 0);
+                while (firsts != 0) {
+                    const int i = __ffs(firsts) - 1;
+                    firsts &= firsts - 1;
+                    wait(x_empty(xs), xph ^ 1u, 0);
+                    const int inner = __shfl_sync(0xffffffffu, mine.x, i);
+                    if (elect_one() && !bad) {
+                        mbar_arrive_expect_tx(x_full(xs), p.x_bytes);
+                        tma_load_2d(smem_base + C::kOffX + xs * kSlabBytes, &tmap_a, inner * 32, tok0, x_full(xs));
+                    }
+                    if (++xs == XS) { xs = 0; xph ^= 1u; }
                 }
-                if (++xs == XS) { xs = 0; xph ^= 1u; }
             }
         }
         if (tracing && lane == 0) p.trace[kTrProdXEmpty] = tr[0];
@@ -256,87 +278,91 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         // ------------------------------------------------------------------ MMA issuers
         // The warps share the issue work by output row (row mod kMmaWarps): accumulations into one row stay
         // in one thread's program order, and while one warp is between blocks the others keep the tensor pipe
-        // fed.  Each warp visits only its own blocks (ring stages follow from the entry and slab numbers); a
-        // slab's stage is released by one commit from every warp that read it plus, from the warp issuing the
-        // slab's last block, plain arrivals on behalf of the warps that had nothing in it.
+        // fed.  Each warp visits only its own blocks; a slab's stage is released by one commit from every
+        // warp that read it plus, from the warp issuing the slab's last block, plain arrivals on behalf of the
+        // warps that had nothing in it.
         const uint32_t mw = (uint32_t)(warp - kFirstMmaWarp);
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
         uint32_t started = 0;   // bit r: the row's columns hold a partial sum of the current segment
         uint32_t pending = 0;   // bit r: a promotion of the row was requested and not yet seen taken
         uint32_t taken_ph = 0;  // bit r: parity of the next p_taken[r] phase to wait for
-        int slab_base = -1;     // number of the last slab opened before this chunk
+        int slab_base = -1;     // number (over all tiles of this CTA) of the last slab opened before this chunk
         int cur_slab = -1;      // slab this warp has waited for
         uint32_t seq = 0;       // this warp's blocks so far: position in its weight ring
-        int4 ahead = fetch(e0 + lane);
-        for (int base = e0; base < e1 && !bad; base += 32) {
-            const int4 mine4 = ahead;
-            ahead = fetch(base + 32 + lane);
-            const uint32_t valid = __ballot_sync(0xffffffffu, base + lane < e1);
-            const uint32_t firsts = __ballot_sync(0xffffffffu, (mine4.w & kPlanFirst) != 0);
-            const uint32_t lasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanLast) != 0);
-            const uint32_t wlasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanWarpLast) != 0);
-            const uint32_t drains = __ballot_sync(0xffffffffu, (mine4.w & kPlanDrain) != 0);
-            const uint32_t idle_b0 = __ballot_sync(0xffffffffu, (mine4.w & (1 << kPlanIdleShift)) != 0);
-            const uint32_t idle_b1 = __ballot_sync(0xffffffffu, (mine4.w & (2 << kPlanIdleShift)) != 0);
-            const uint32_t row_b0 = __ballot_sync(0xffffffffu, (mine4.z & 1) != 0);
-            const uint32_t row_b1 = __ballot_sync(0xffffffffu, (mine4.z & 2) != 0);
-            const uint32_t row_b2 = __ballot_sync(0xffffffffu, (mine4.z & 4) != 0);
-            uint32_t todo = __ballot_sync(0xffffffffu, (uint32_t)(mine4.z & (kMmaWarps - 1)) == mw) & valid;
-            while (todo != 0) {
-                const int i = __ffs(todo) - 1;
-                todo &= todo - 1;
-                const int slab = slab_base + __popc(firsts & (0xffffffffu >> (31 - i)));
-                const int as = slab & (AS - 1);
-                const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
-                wait(w_full(ws), (seq / kWRing) & 1u, 1);
-                ++seq;
-                if (slab != cur_slab) {
-                    wait_count(a_count(as), 4u * (uint32_t)(slab / AS + 1));
-                    tc_fence_after();  // the transform warps' tcgen05.st precede the MMAs that read the slab
-                    cur_slab = slab;
-                }
-                const uint32_t row = ((row_b0 >> i) & 1u) | (((row_b1 >> i) & 1u) << 1) | (((row_b2 >> i) & 1u) << 2);
-                const uint32_t rbit = 1u << row;
-                const bool wlast = ((wlasts >> i) & 1u) != 0, drain = ((drains >> i) & 1u) != 0;
-                // the warp that issues a slab's last block also arrives for the warps that have none in it
-                const uint32_t idle = ((lasts >> i) & 1u) * (((idle_b0 >> i) & 1u) | (((idle_b1 >> i) & 1u) << 1));
-                if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
-                    wait(p_taken(row), (taken_ph >> row) & 1u, 2);
-                    taken_ph ^= rbit;
-                    pending &= ~rbit;
-                    tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the row
-                }
-                const uint64_t b_desc =
-                    smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
-                const uint32_t a_hi = tmem + C::kAccCols + as * C::kAStageCols;
-                const uint32_t d = tmem + row * C::kRowCols;
-                const uint32_t acc0 = (started & rbit) ? 1u : 0u;
-                const uint32_t w_bar = w_empty(ws), a_bar = a_empty(as), p_bar = p_ready(row);
-                const long long ti = tracing ? clock64() : 0;
-                if (elect_one() && !bad) {
-#pragma unroll
-                    for (int s = 0; s < 4; ++s) {
-                        // k-step s: 8 columns further in the slab's tensor-memory copy, 2 KiB further in the image
-                        const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
-                        const uint32_t acc = s == 0 ? acc0 : 1u;
-                        if (kPasses == 3) {
-                            mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, acc);               // x_hi x [w_hi ; w_lo]
-                            mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // x_lo x w_hi
-                        } else {
-                            mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, acc);
-                        }
+        int4 ahead = first_chunk();
+        for (int tile = blockIdx.x; tile < n_tiles && !bad; tile += tile_step) {
+            const int g = tile % p.groups;
+            const int e0 = __ldg(p.group_off + g), e1 = __ldg(p.group_off + g + 1);
+            for (int base = e0; base < e1 && !bad; base += 32) {
+                const int4 mine4 = ahead;
+                ahead = prefetch(tile, base, e1);
+                const uint32_t valid = __ballot_sync(0xffffffffu, base + lane < e1);
+                const uint32_t firsts = __ballot_sync(0xffffffffu, (mine4.w & kPlanFirst) != 0);
+                const uint32_t lasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanLast) != 0);
+                const uint32_t wlasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanWarpLast) != 0);
+                const uint32_t drains = __ballot_sync(0xffffffffu, (mine4.w & kPlanDrain) != 0);
+                const uint32_t idle_b0 = __ballot_sync(0xffffffffu, (mine4.w & (1 << kPlanIdleShift)) != 0);
+                const uint32_t idle_b1 = __ballot_sync(0xffffffffu, (mine4.w & (2 << kPlanIdleShift)) != 0);
+                const uint32_t row_b0 = __ballot_sync(0xffffffffu, (mine4.z & 1) != 0);
+                const uint32_t row_b1 = __ballot_sync(0xffffffffu, (mine4.z & 2) != 0);
+                const uint32_t row_b2 = __ballot_sync(0xffffffffu, (mine4.z & 4) != 0);
+                uint32_t todo = __ballot_sync(0xffffffffu, (uint32_t)(mine4.z & (kMmaWarps - 1)) == mw) & valid;
+                while (todo != 0) {
+                    const int i = __ffs(todo) - 1;
+                    todo &= todo - 1;
+                    const int slab = slab_base + __popc(firsts & (0xffffffffu >> (31 - i)));
+                    const int as = slab & (AS - 1);
+                    const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
+                    wait(w_full(ws), (seq / kWRing) & 1u, 1);
+                    ++seq;
+                    if (slab != cur_slab) {
+                        wait_count(a_count(as), 4u * (uint32_t)(slab / AS + 1));
+                        tc_fence_after();  // the split warps' tcgen05.st precede the MMAs that read the slab
+                        cur_slab = slab;
                     }
-                    mma_commit(w_bar);
-                    if (wlast) mma_commit(a_bar);
-                    if (idle != 0) mbar_arrive_n(a_bar, idle);
-                    if (drain) mma_commit(p_bar);
+                    const uint32_t row = ((row_b0 >> i) & 1u) | (((row_b1 >> i) & 1u) << 1) | (((row_b2 >> i) & 1u) << 2);
+                    const uint32_t rbit = 1u << row;
+                    const bool wlast = ((wlasts >> i) & 1u) != 0, drain = ((drains >> i) & 1u) != 0;
+                    // the warp that issues a slab's last block also arrives for the warps that have none in it
+                    const uint32_t idle = ((lasts >> i) & 1u) * (((idle_b0 >> i) & 1u) | (((idle_b1 >> i) & 1u) << 1));
+                    if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
+                        wait(p_taken(row), (taken_ph >> row) & 1u, 2);
+                        taken_ph ^= rbit;
+                        pending &= ~rbit;
+                        tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the row
+                    }
+                    const uint64_t b_desc =
+                        smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
+                    const uint32_t a_hi = tmem + C::kAccCols + as * C::kAStageCols;
+                    const uint32_t d = tmem + row * C::kRowCols;
+                    const uint32_t acc0 = (started & rbit) ? 1u : 0u;
+                    const uint32_t w_bar = w_empty(ws), a_bar = a_empty(as), p_bar = p_ready(row);
+                    const long long ti = tracing ? clock64() : 0;
+                    if (elect_one() && !bad) {
+#pragma unroll
+                        for (int s = 0; s < 4; ++s) {
+                            // k-step s: 8 columns further in the slab's tensor-memory copy, 2 KiB further in the image
+                            const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
+                            const uint32_t acc = s == 0 ? acc0 : 1u;
+                            if (kPasses == 3) {
+                                mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, acc);               // x_hi x [w_hi ; w_lo]
+                                mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // x_lo x w_hi
+                            } else {
+                                mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, acc);
+                            }
+                        }
+                        mma_commit(w_bar);
+                        if (wlast) mma_commit(a_bar);
+                        if (idle != 0) mbar_arrive_n(a_bar, idle);
+                        if (drain) mma_commit(p_bar);
+                    }
+                    if (tracing) tr[3] += clock64() - ti;
+                    started |= rbit;
+                    if (drain) { pending |= rbit; started &= ~rbit; }
                 }
-                if (tracing) tr[3] += clock64() - ti;
-                started |= rbit;
-                if (drain) { pending |= rbit; started &= ~rbit; }
+                slab_base += __popc(firsts & valid);
             }
-            slab_base += __popc(firsts & valid);
         }
         if (tracing && lane == 0 && mw == 0) {
             p.trace[kTrMmaAFull] = tr[0];
@@ -346,7 +372,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
             p.trace[kTrMmaIssue] = tr[3];
         }
     } else if (warp < kFirstDrainWarp) {
-        // ------------------------------------------------------------------ transform
+        // ------------------------------------------------------------------ split
         // Two groups of four warps take alternate slabs, so that one slab's trip through registers (shared
         // memory -> split -> tensor memory, a few hundred cycles of latency) overlaps the next one's.  Ring
         // stages follow from the slab number; the stage counts are even, so a stage stays with one group.
@@ -355,35 +381,41 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         const int row = quarter * 32 + lane;    // token inside the tile = tensor-memory lane
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         static_assert(XS % 2 == 0 && AS % 2 == 0, "a ring stage must stay with one split-warp group");
-        for (int s = group; s < nslabs; s += 2) {
-            const int xs = s % XS, as = s & (AS - 1);
-            wait(x_full(xs), (uint32_t)(s / XS) & 1u, 0);
-            uint32_t hi[32], lo[32];
-            {
-                const uint8_t* xrow = smem_gen + C::kOffX + xs * kSlabBytes + row * 128;
+        int slab0 = 0;  // slabs of this CTA's earlier tiles
+        bool go = true;
+        for (int tile = blockIdx.x; tile < n_tiles && go; tile += tile_step) {
+            const int nslabs = __ldg(p.group_slabs + tile % p.groups);
+            for (int s = slab0 + ((group ^ slab0) & 1); s < slab0 + nslabs; s += 2) {
+                const int xs = s % XS, as = s & (AS - 1);
+                wait(x_full(xs), (uint32_t)(s / XS) & 1u, 0);
+                uint32_t hi[32], lo[32];
+                {
+                    const uint8_t* xrow = smem_gen + C::kOffX + xs * kSlabBytes + row * 128;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    // 128-byte swizzle: the 16-byte chunk index is XORed with (row mod 8)
-                    const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((j ^ (row & 7)) << 4));
-                    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+                    for (int j = 0; j < 8; ++j) {
+                        // 128-byte swizzle: the 16-byte chunk index is XORed with (row mod 8)
+                        const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((j ^ (row & 7)) << 4));
+                        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        hi[j * 4 + q] = u[q];
-                        if (kPasses == 3)
-                            lo[j * 4 + q] = __float_as_uint(__uint_as_float(u[q]) - __uint_as_float(u[q] & 0xffffe000u));
+                        for (int q = 0; q < 4; ++q) {
+                            hi[j * 4 + q] = u[q];
+                            if (kPasses == 3)
+                                lo[j * 4 + q] = __float_as_uint(__uint_as_float(u[q]) - __uint_as_float(u[q] & 0xffffe000u));
+                        }
                     }
                 }
+                mbar_arrive(x_empty(xs));
+                wait(a_empty(as), ((uint32_t)(s / AS) & 1u) ^ 1u, 1);
+                tc_fence_after();
+                const uint32_t a_hi = tmem_lane + C::kAccCols + as * C::kAStageCols;
+                tmem_st32(a_hi, hi);
+                if (kPasses == 3) tmem_st32(a_hi + 32, lo);
+                tmem_wait_st();
+                tc_fence_before();
+                if (__any_sync(0xffffffffu, bad != 0)) { go = false; break; }  // nothing is published once a wait has given up
+                if (lane == 0) smem_add_release(a_count(as), 1u);
             }
-            mbar_arrive(x_empty(xs));
-            wait(a_empty(as), ((uint32_t)(s / AS) & 1u) ^ 1u, 1);
-            tc_fence_after();
-            const uint32_t a_hi = tmem_lane + C::kAccCols + as * C::kAStageCols;
-            tmem_st32(a_hi, hi);
-            if (kPasses == 3) tmem_st32(a_hi + 32, lo);
-            tmem_wait_st();
-            tc_fence_before();
-            if (__any_sync(0xffffffffu, bad != 0)) break;  // nothing is published once a wait has given up
-            if (lane == 0) smem_add_release(a_count(as), 1u);
+            slab0 += nslabs;
         }
         if (tracing && warp == kFirstSplitWarp && lane == 0) {
             p.trace[kTrXfXFull] = tr[0];
@@ -395,79 +427,84 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         const int quarter = warp & 3;          // tensor-memory lane quarter this warp may access
         const int row = quarter * 32 + lane;   // token inside the tile = tensor-memory lane
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
-        const int64_t tok = tok0 + row;
-        const bool live = tok < p.m;
-
-        // v (+ bias on a row's first promotion, + previous output afterwards) -> out[tok, col0 .. col0+31]
-        auto emit = [&](int r, const float (&v)[32], bool first) {
-            if (!live) return;
-            const int64_t col0 = ((int64_t)g * G + r) * 32;
-            if (!p.out_colmajor) {
-                float4* dst = reinterpret_cast<float4*>(p.out + tok * p.n + col0);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (!first) add = dst[j];
-                    else if (p.bias != nullptr) add = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
-                    dst[j] = make_float4(v[j * 4 + 0] + add.x, v[j * 4 + 1] + add.y, v[j * 4 + 2] + add.z,
-                                         v[j * 4 + 3] + add.w);
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float* dst = p.out + (col0 + j) * p.m + tok;
-                    float add = 0.f;
-                    if (!first) add = *dst;
-                    else if (p.bias != nullptr) add = __ldg(p.bias + col0 + j);
-                    *dst = v[j] + add;
-                }
-            }
-        };
-
         uint32_t ready_ph = 0;  // bit r: parity of the next p_ready[r] phase
-        uint32_t seen = 0;      // bit r: the row has been written once
         bool ok = true;
-        int4 ahead = fetch(e0 + lane);  // 32 entries per warp-wide load, one chunk ahead
-        for (int base = e0; base < e1 && ok; base += 32) {
-            const int4 mine = ahead;
-            ahead = fetch(base + 32 + lane);
-            uint32_t drains = __ballot_sync(0xffffffffu, (mine.w & kPlanDrain) != 0);
-            while (drains != 0) {
-                const int i = __ffs(drains) - 1;
-                drains &= drains - 1;
-                const int r = __shfl_sync(0xffffffffu, mine.z, i);
-                wait(p_ready(r), (ready_ph >> r) & 1u, 0);
-                ok = !__any_sync(0xffffffffu, bad != 0);
-                if (!ok) break;
-                ready_ph ^= 1u << r;
-                tc_fence_after();
-                uint32_t main_[32];
-                float v[32];
-                tmem_ld32(tmem_lane + r * C::kRowCols, main_);
-                if (kPasses == 3) {
-                    uint32_t corr[32];
-                    tmem_ld32(tmem_lane + r * C::kRowCols + 32, corr);
-                    tmem_wait_ld();
+        int4 ahead = first_chunk();
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += tile_step) {
+            const int g = tile % p.groups;
+            const int e0 = __ldg(p.group_off + g), e1 = __ldg(p.group_off + g + 1);
+            const int nrows = min(G, p.n_out_blocks - g * G);
+            const int64_t tok = (int64_t)(tile / p.groups) * kTileTokens + row;
+            const bool live = tok < p.m;
+
+            // v (+ bias on a row's first promotion, + previous output afterwards) -> out[tok, col0 .. col0+31]
+            auto emit = [&](int r, const float (&v)[32], bool first) {
+                if (!live) return;
+                const int64_t col0 = ((int64_t)g * G + r) * 32;
+                if (!p.out_colmajor) {
+                    float4* dst = reinterpret_cast<float4*>(p.out + tok * p.n + col0);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]) + __uint_as_float(corr[j]);
+                    for (int j = 0; j < 8; ++j) {
+                        float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (!first) add = dst[j];
+                        else if (p.bias != nullptr) add = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+                        dst[j] = make_float4(v[j * 4 + 0] + add.x, v[j * 4 + 1] + add.y, v[j * 4 + 2] + add.z,
+                                             v[j * 4 + 3] + add.w);
+                    }
                 } else {
-                    tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]);
+                    for (int j = 0; j < 32; ++j) {
+                        float* dst = p.out + (col0 + j) * p.m + tok;
+                        float add = 0.f;
+                        if (!first) add = *dst;
+                        else if (p.bias != nullptr) add = __ldg(p.bias + col0 + j);
+                        *dst = v[j] + add;
+                    }
                 }
-                tc_fence_before();
-                mbar_arrive(p_taken(r));
-                emit(r, v, !((seen >> r) & 1u));
-                seen |= 1u << r;
-            }
-        }
-        if (ok) {
-            // block-rows without any block: bias (or zero)
-            float z[32];
+            };
+
+            uint32_t seen = 0;      // bit r: the row has been written once in this tile
+            for (int base = e0; base < e1 && ok; base += 32) {
+                const int4 mine = ahead;
+                ahead = prefetch(tile, base, e1);
+                uint32_t drains = __ballot_sync(0xffffffffu, (mine.w & kPlanDrain) != 0);
+                while (drains != 0) {
+                    const int i = __ffs(drains) - 1;
+                    drains &= drains - 1;
+                    const int r = __shfl_sync(0xffffffffu, mine.z, i);
+                    wait(p_ready(r), (ready_ph >> r) & 1u, 0);
+                    ok = !__any_sync(0xffffffffu, bad != 0);
+                    if (!ok) break;
+                    ready_ph ^= 1u << r;
+                    tc_fence_after();
+                    uint32_t main_[32];
+                    float v[32];
+                    tmem_ld32(tmem_lane + r * C::kRowCols, main_);
+                    if (kPasses == 3) {
+                        uint32_t corr[32];
+                        tmem_ld32(tmem_lane + r * C::kRowCols + 32, corr);
+                        tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) z[j] = 0.f;
-            for (int r = 0; r < nrows; ++r)
-                if (!((seen >> r) & 1u)) emit(r, z, true);
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]) + __uint_as_float(corr[j]);
+                    } else {
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(main_[j]);
+                    }
+                    tc_fence_before();
+                    mbar_arrive(p_taken(r));
+                    emit(r, v, !((seen >> r) & 1u));
+                    seen |= 1u << r;
+                }
+            }
+            if (ok) {
+                // block-rows without any block: bias (or zero)
+                float z[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) z[j] = 0.f;
+                for (int r = 0; r < nrows; ++r)
+                    if (!((seen >> r) & 1u)) emit(r, z, true);
+            }
         }
         if (tracing && warp == kFirstDrainWarp && lane == 0) {
             p.trace[kTrDrainPReady] = tr[0];
@@ -510,8 +547,14 @@ cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const DsdParams& p, int64_t 
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)Cfg<G, kPasses>::kSmemBytes);
     if (err != cudaSuccess) return err;
-    dsd_umma_tf32_kernel<G, kPasses>
-        <<<(unsigned)(p.groups * tiles), kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, p);
+    int dev = 0, sms = 0;
+    err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return err;
+    const int64_t n_tiles = (int64_t)p.groups * tiles;
+    const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);  // persistent: one CTA per SM
+    dsd_umma_tf32_kernel<G, kPasses><<<grid, kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, p);
     return cudaGetLastError();
 }
 
@@ -591,6 +634,7 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     p.n = n;
     p.n_out_blocks = (int32_t)n_out_blocks;
     p.groups = (int32_t)groups;
+    p.n_tiles = (int32_t)(groups * tiles);
     p.out_colmajor = out_colmajor ? 1 : 0;
     p.x_bytes = box_rows * 128u;
     p.trace = g_trace_buffer;
