@@ -40,8 +40,8 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kChunks = 4;                 // chunks (of 4 blocks) per item
-constexpr int kItemBlocks = 4 * kChunks;   // 16
+constexpr int kChunks = 2;                 // chunks (of 4 blocks) per item
+constexpr int kItemBlocks = 4 * kChunks;   // 8
 constexpr int kStepTokens = 32;
 constexpr int kDrainSteps = 32;            // promote every 1024 tokens: 128 accumulations of the main term
 constexpr uint32_t kSlabBytes = 32 * 32 * 4;            // 4 KiB: [32 tokens][32 features], 128-byte rows
@@ -49,14 +49,16 @@ constexpr uint32_t kKStepBytes = 8 * 128;               // one MMA k-step = 8 to
 constexpr uint32_t kXStageBytes = 4 * kSlabBytes;       // one unit's four X slabs
 constexpr uint32_t kDyStageBytes = 2 * kSlabBytes;      // raw slab | its lo part
 constexpr uint32_t kMasterBytes = 128 * 32 * 4;         // 16 KiB per chunk
-constexpr int kStages = 4;                              // X stages in shared memory = A stages in tensor memory
+constexpr int kStages = 6;                              // X stages in shared memory = A stages in tensor memory:
+                                                        // three per chunk, so a chunk's copy runs ahead of its MMAs
 constexpr int kDyStages = 4;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kChunkCols = 64;                     // main | correction
-constexpr uint32_t kAccCols = kChunks * kChunkCols;     // 256
+constexpr uint32_t kAccCols = kChunks * kChunkCols;     // 128
 constexpr uint32_t kAStageCols = 64;                    // x_hi | x_lo, 32 tokens each
 constexpr int kXProducers = 2, kDyProducerWarp = 2, kDySplitWarp = 3, kFirstMmaWarp = 4;
-constexpr int kFirstSplitWarp = kFirstMmaWarp + kChunks, kSplitWarps = 8;
+constexpr int kSplitGroups = 3;  // groups of four split warps; unit u goes to group u mod kSplitGroups
+constexpr int kFirstSplitWarp = kFirstMmaWarp + kChunks, kSplitWarps = 4 * kSplitGroups;
 constexpr int kFirstDrainWarp = kFirstSplitWarp + kSplitWarps;
 constexpr int kThreads = 32 * (kFirstDrainWarp + 4);
 
@@ -69,7 +71,8 @@ constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
 constexpr uint32_t kSmemBytes = kOffMisc + 32 + 1024;
 static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
 static_assert(kAccCols + kStages * kAStageCols <= kTmemCols, "tensor memory over-subscribed");
-static_assert(kStages % 2 == 0, "a stage must stay with one producer warp and one split-warp group");
+static_assert(kStages % kXProducers == 0 && kStages % kSplitGroups == 0,
+              "a stage must stay with one producer warp and one split-warp group");
 
 // Item table: [0] = item count; item i at int32 offsets 4 + 4*i: {block-row, first CSR entry, blocks, 0}
 struct SddmmParams {
@@ -172,7 +175,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         int step = 0, ch = warp;
         while (ch >= nchunks) { ch -= nchunks; ++step; }
         for (int u = warp; u < nunits && !bad; u += kXProducers) {
-            const int xs = u & (kStages - 1);
+            const int xs = u % kStages;
             const int nb = min(4, nblk - ch * 4);
             const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
             int bcol[4];
@@ -231,7 +234,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         uint32_t taken_ph = 0;
         for (int step = 0; step < nsteps && !bad && ch < nchunks; ++step) {
             const int u = step * nchunks + ch;
-            const int as = u & (kStages - 1);
+            const int as = u % kStages;
             const int ds = step & (kDyStages - 1);
             const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
             const bool drain = drain_step(step);
@@ -277,8 +280,8 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         int ch = group;
         while (ch >= nchunks) ch -= nchunks;
-        for (int u = group; u < nunits; u += 2) {
-            const int xs = u & (kStages - 1);
+        for (int u = group; u < nunits; u += kSplitGroups) {
+            const int xs = u % kStages;
             const int nb = min(4, nblk - ch * 4);
             wait(x_full(xs), (uint32_t)(u / kStages) & 1u);
             uint32_t hi[32], lo[32];
@@ -304,7 +307,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             tc_fence_before();
             if (__any_sync(0xffffffffu, bad != 0)) break;  // nothing is published once a wait has given up
             if (lane == 0) smem_add_release(a_count(xs), 1u);
-            ch += 2;
+            ch += kSplitGroups;
             while (ch >= nchunks) ch -= nchunks;
         }
     } else {
