@@ -283,7 +283,13 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         for (int u = group; u < nunits; u += kSplitGroups) {
             const int xs = u % kStages;
             const int nb = min(4, nblk - ch * 4);
-            wait(x_full(xs), (uint32_t)(u / kStages) & 1u);
+            // one wait instruction for both barriers (a successful wait costs ~85 cycles whatever it tests): the
+            // lower half-warp polls the slabs' arrival, the upper half the tensor-memory stage's release
+            {
+                const bool upper = lane >= 16;
+                wait(upper ? a_empty(xs) : x_full(xs), ((uint32_t)(u / kStages) & 1u) ^ (upper ? 1u : 0u));
+                __syncwarp();
+            }
             uint32_t hi[32], lo[32];
             if (quarter < nb) {
                 const uint8_t* col = smem_gen + kOffX + xs * kXStageBytes + quarter * kSlabBytes + ((lane & 3) << 2);
@@ -298,7 +304,6 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 for (int t = 0; t < 32; ++t) { hi[t] = 0u; lo[t] = 0u; }
             }
             mbar_arrive(x_empty(xs));
-            wait(a_empty(xs), ((uint32_t)(u / kStages) & 1u) ^ 1u);
             tc_fence_after();
             const uint32_t a_tm = tmem_lane + kAccCols + xs * kAStageCols;
             tmem_st32(a_tm, hi);
