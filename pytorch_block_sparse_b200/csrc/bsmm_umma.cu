@@ -46,7 +46,7 @@ constexpr uint32_t kSlabBytes = kTileTokens * 32 * 4;  // 16 KiB: [128 tokens][3
 constexpr uint32_t kWStageBytes = kImage32Bytes;       // 8 KiB: hi and lo parts interleaved
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMmaWarps = kDsdMmaWarps;
-constexpr int kWProducers = 2;                    // warps 0..1 load weight blocks (alternate entries)
+constexpr int kWProducers = kMmaWarps;            // warp w loads the weight blocks of MMA warp w
 constexpr int kXProducerWarp = kWProducers;       // this warp loads activation slabs
 constexpr int kFirstMmaWarp = kXProducerWarp + 1;
 constexpr int kFirstSplitWarp = kFirstMmaWarp + kMmaWarps;
@@ -203,11 +203,10 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
     // stages follow from entry and slab counts, so a warp visits only the entries it has work for.
     if (warp < kWProducers) {
         // ------------------------------------------------------------------ weight producers
-        // every MMA warp has a ring of kWRing stages of its own, filled in the order of that warp's blocks: a
-        // ring with one producer and one consumer, each seeing every phase, which a phase-parity barrier needs
-        uint32_t issued[kMmaWarps];  // blocks already loaded per MMA warp
-#pragma unroll
-        for (int w = 0; w < kMmaWarps; ++w) issued[w] = 0;
+        // Every MMA warp has a ring of kWRing stages of its own, filled by a producer warp of its own in the
+        // order of that warp's blocks: one producer and one consumer per ring, each seeing every phase (which a
+        // phase-parity barrier needs), and a full ring stalls nobody else's loads.
+        uint32_t seq = 0;  // blocks of this warp's MMA warp loaded so far
         int4 ahead = first_chunk();
         for (int tile = blockIdx.x; tile < n_tiles && !bad; tile += tile_step) {
             const int g = tile % p.groups;
@@ -215,26 +214,14 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
             for (int base = e0; base < e1 && !bad; base += 32) {
                 const int4 mine = ahead;
                 ahead = prefetch(tile, base, e1);
-                const int count = min(32, e1 - base);
-                const uint32_t owner = (uint32_t)mine.z & (kMmaWarps - 1);
-                uint32_t seq = 0;  // this lane's block is the seq-th of its MMA warp
-#pragma unroll
-                for (int w = 0; w < kMmaWarps; ++w) {
-                    const uint32_t same = __ballot_sync(0xffffffffu, owner == (uint32_t)w && lane < count);
-                    if (owner == (uint32_t)w) seq = issued[w] + __popc(same & ((1u << lane) - 1u));
-                    issued[w] += __popc(same);
-                }
-                const uint32_t stage_use = (owner * kWRing + (seq & (kWRing - 1))) | (((seq / kWRing) & 1u) << 8);
-                // a stage is always filled by the same producer warp (stage number mod kWProducers), which thus
-                // sees every phase of the stage's barriers
-                uint32_t todo = __ballot_sync(0xffffffffu, lane < count && (seq & (kWProducers - 1)) == (uint32_t)warp);
+                uint32_t todo = __ballot_sync(0xffffffffu, base + lane < e1 && ((uint32_t)mine.z & (kMmaWarps - 1)) == (uint32_t)warp);
                 while (todo != 0) {
                     const int i = __ffs(todo) - 1;
                     todo &= todo - 1;
-                    const uint32_t su = __shfl_sync(0xffffffffu, stage_use, i);
                     const int slot = __shfl_sync(0xffffffffu, mine.y, i);
-                    const int ws = (int)(su & 0xffu);
-                    wait(w_empty(ws), (su >> 8) ^ 1u, 1);
+                    const int ws = (int)(warp * kWRing + (seq & (kWRing - 1)));
+                    wait(w_empty(ws), ((seq / kWRing) & 1u) ^ 1u, 1);
+                    ++seq;
                     const uint8_t* src = p.packed + (int64_t)slot * kWStageBytes;
                     if (elect_one() && !bad) {
                         mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
@@ -311,33 +298,36 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                 while (todo != 0) {
                     const int i = __ffs(todo) - 1;
                     todo &= todo - 1;
+                    // everything that does not depend on the operands' arrival first: the time from a slab's
+                    // publication to this warp's commit is part of the stage's recycle time
                     const int slab = slab_base + __popc(firsts & (0xffffffffu >> (31 - i)));
                     const int as = slab & (AS - 1);
                     const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
-                    wait(w_full(ws), (seq / kWRing) & 1u, 1);
+                    const uint32_t w_parity = (seq / kWRing) & 1u;
                     ++seq;
-                    if (slab != cur_slab) {
-                        wait_count(a_count(as), 4u * (uint32_t)(slab / AS + 1));
-                        tc_fence_after();  // the split warps' tcgen05.st precede the MMAs that read the slab
-                        cur_slab = slab;
-                    }
                     const uint32_t row = ((row_b0 >> i) & 1u) | (((row_b1 >> i) & 1u) << 1) | (((row_b2 >> i) & 1u) << 2);
                     const uint32_t rbit = 1u << row;
                     const bool wlast = ((wlasts >> i) & 1u) != 0, drain = ((drains >> i) & 1u) != 0;
                     // the warp that issues a slab's last block also arrives for the warps that have none in it
                     const uint32_t idle = ((lasts >> i) & 1u) * (((idle_b0 >> i) & 1u) | (((idle_b1 >> i) & 1u) << 1));
-                    if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
-                        wait(p_taken(row), (taken_ph >> row) & 1u, 2);
-                        taken_ph ^= rbit;
-                        pending &= ~rbit;
-                        tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the row
-                    }
                     const uint64_t b_desc =
                         smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
                     const uint32_t a_hi = tmem + C::kAccCols + as * C::kAStageCols;
                     const uint32_t d = tmem + row * C::kRowCols;
                     const uint32_t acc0 = (started & rbit) ? 1u : 0u;
                     const uint32_t w_bar = w_empty(ws), a_bar = a_empty(as), p_bar = p_ready(row);
+                    if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
+                        wait(p_taken(row), (taken_ph >> row) & 1u, 2);
+                        taken_ph ^= rbit;
+                        pending &= ~rbit;
+                    }
+                    wait(w_full(ws), w_parity, 1);
+                    if (slab != cur_slab) {
+                        wait_count(a_count(as), 4u * (uint32_t)(slab / AS + 1));
+                        cur_slab = slab;
+                    }
+                    // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the row) precede the MMAs
+                    tc_fence_after();
                     const long long ti = tracing ? clock64() : 0;
                     if (elect_one() && !bad) {
 #pragma unroll
