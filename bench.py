@@ -400,9 +400,15 @@ def run_gpu_arm(args, cfg):
     # tcgen05 kind::tf32 runs at half the bf16 rate; the measured dense bf16 peak (sustained, the
     # kernel is timed inside a long loop) halved is the single-pass TF32 ceiling used here
     peak = peaks["bf16_tflops_sustained"] / 2.0 if prec_name != "bf16" else peaks["bf16_tflops_sustained"]
+    # DRAM bytes (read + write) of one launch of that kernel from an ncu capture of this workload; null
+    # where no capture was taken (the summaries with the commands are under profiles/)
+    ncu_traffic = {
+        ("c3_d0.25", "tf32x3", "wgrad_ms"): (667.8e6, "profiles/sddmm_umma_tf32x3_c3_d0.25.md"),
+        ("c3_d0.25", "tf32x3", "fwd_ms"): (648.5e6, "profiles/dsd_umma_tf32x3_c3_d0.25.md"),
+    }.get((args.workload, prec_name, dom), (None, None))
     roofline = {
         "kernel": op_names[dom], "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": achieved / peak, "traffic": None,
+        "frac": achieved / peak, "traffic": ncu_traffic[0], "traffic_source": ncu_traffic[1],
         "peak_source": "%s bf16 sustained %.1f TFLOP/s %s" % (peaks["source"], peaks["bf16_tflops_sustained"], "/ 2 (tf32)" if prec_name != "bf16" else ""),
         "algorithmic_flops_per_launch": f_op,
     }

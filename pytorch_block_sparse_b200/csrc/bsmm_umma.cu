@@ -2,34 +2,33 @@
 // block-sparse Linear; replaces the reference's cutlass::gemm::kernel<block_task>,
 // cutlass/gemm/dispatch.h:185-218 and block_task.h:647-715).
 //
-// Tile: 128 tokens x G output block-rows (G*32 columns) per CTA, accumulated in tensor memory.  The
+// Tile: 128 tokens x G output block-rows (G*32 columns), accumulated in tensor memory.  The
 // contraction axis is walked one 32-wide activation slab at a time, visiting only slabs for which
-// the group has at least one block (the plan lists them, bsmm_plan.cu).
+// the group has at least one block (the plan lists them, bsmm_plan.cu).  The kernel is persistent:
+// one CTA per SM walks its tiles, and every ring position runs on across tiles.
 //
-//   warp 0     producer : TMA tensor load of the [128 x 32] fp32 activation slab (128-byte swizzle)
-//                         and one 8 KiB linear bulk copy per block of its packed weight image
-//   warps 3-6  transform: slab smem -> registers -> tensor memory (lane = token, column = k) with
-//                         tcgen05.st, which makes it the MMA's A operand; for 3xTF32 also
-//                         lo = x - trunc_tf32(x) (the tensor core reads only the tf32 bits of an
-//                         operand, so the raw slab is x_hi)
-//   warps 1-2  MMA      : tcgen05.mma kind::tf32, M = 128, A from tensor memory, B from smem; the
-//                         two warps take the blocks of even and odd output rows.
-//                         3xTF32, per k-step (8 values of k) two instructions:
-//                           x_hi x [w_hi ; w_lo]  (N = 64) -> main | correction columns of the row
-//                           x_lo x  w_hi          (N = 32) -> correction columns
-//                         single-pass TF32: one N = 32 instruction per k-step.
-//   warps 7-10 drain    : after every kDrainEvery-th block of a row and after its last one,
-//                         tcgen05.ld the row's columns, main + correction (+ bias, or + the output
-//                         written by the row's previous promotion), 128-byte row stores to global
+//   warps 0-3   weight producers : warp w feeds MMA warp w's own ring of kWRing stages, one 8 KiB
+//                                  linear bulk copy per block of its packed weight image
+//   warp 4      activation producer : TMA tensor load of the [128 x 32] fp32 slab (128-byte swizzle)
+//   warps 5-8   MMA : tcgen05.mma kind::tf32, M = 128, A from tensor memory, B from smem; output row r
+//                     of the group belongs to warp r mod 4.
+//                     3xTF32, per k-step (8 values of k) two instructions:
+//                       x_hi x [w_hi ; w_lo]  (N = 64) -> main | correction columns of the row
+//                       x_lo x  w_hi          (N = 32) -> correction columns
+//                     single-pass TF32: one N = 32 instruction per k-step.
+//   warps 9-16  split : two groups of four, alternate slabs: slab smem -> registers -> tensor memory
+//                       (lane = token, column = k) with tcgen05.st, which makes it the MMA's A operand;
+//                       for 3xTF32 also lo = x - trunc_tf32(x) (the tensor core reads only the tf32
+//                       bits of an operand, so the raw slab is x_hi)
+//   warps 17-20 drain : after every kDrainEvery-th block of a row and after its last one,
+//                       tcgen05.ld the row's columns, main + correction (+ bias, or + the output
+//                       written by the row's previous promotion), 128-byte row stores to global
 //
 // Measured on an idle SM, one block costs the tensor pipe 255 clk (3xTF32) or 165 clk (single pass)
 // in this form, against 422 / 232 clk with A read from shared memory (4 KiB per instruction).
 // Keeping the main term apart from the corrections and promoting it every 32 blocks bounds the
 // tensor core's systematic fp32-accumulate error (about 2e-8 relative per accumulation).
-// The producer and MMA warps run warp-uniform loops and elect one lane only for the instruction
-// itself, so the operands of TMA / tcgen05.mma stay in uniform registers; plan entries are read
-// four blocks ahead.  Every mbarrier wait is bounded; on expiry the CTA raises the device status
-// word and drains.
+// Every wait is bounded; on expiry the CTA raises the device status word, stops issuing and drains.
 #include "bsmm_ptx.cuh"
 #include "bsmm_umma.cuh"
 
