@@ -4,7 +4,7 @@
 //
 //   out[slot][c][r] = sum over tokens t of X[t, C*32 + c] * dY[t, R*32 + r]
 //
-// A CTA owns one "item": up to 16 blocks of ONE block-row R (a CSR row segment) and one range of
+// A CTA owns one "item": up to 8 blocks of ONE block-row R (a CSR row segment) and one range of
 // tokens.  Four blocks of the row form a chunk and fill the 128 rows of one MMA:
 //   D[128 = 4 blocks x 32 c, 32 = r] += A[128 x K] * B[32 x K]^T,   K = tokens, 8 per instruction.
 // D is already the block's storage layout (row c holds 32 consecutive r).  A "unit" is one chunk times one
@@ -20,12 +20,13 @@
 //   warp 2      dY producer : TMA, one dY slab per step
 //   warp 3      dY split    : lo = v - trunc_tf32(v) of the dY slab into a second tile of the same layout
 //                             (the tensor core reads only the tf32 bits of an operand, so the raw slab is hi)
-//   warps 4-7   MMA         : warp c owns chunk c: per unit and k-step (8 tokens)
+//   warps 4-5   MMA         : warp c owns chunk c (two chunks per item): per unit and k-step (8 tokens)
 //                             x x [dy ; dy_lo] (N = 64) and x_lo x dy (N = 32), tcgen05.mma kind::tf32, M = 128,
 //                             into the main | correction columns of the chunk
-//   warps 8-15  X split     : two groups of four (units by parity): shared memory -> registers (transposing
-//                             reads, conflict-free under the 128-byte swizzle) -> hi, lo -> tensor memory
-//   warps 16-19 drain       : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
+//   warps 6-17  X split     : three groups of four (unit mod 3): shared memory -> registers (transposing
+//                             reads, conflict-free under the 128-byte swizzle) -> hi, lo -> tensor memory;
+//                             six stages, so a chunk's copies run up to three steps ahead of its MMAs
+//   warps 18-21 drain       : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
 //                             (fp32, round to nearest) to the chunk's master tile in shared memory; final
 //                             store of the master tiles to global
 //

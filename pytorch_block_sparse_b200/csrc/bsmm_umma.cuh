@@ -50,7 +50,7 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
                             bool out_colmajor, cudaStream_t stream);
 
-// SDDMM: item table built from the CSR offsets (one item = up to 16 blocks of one block-row)
+// SDDMM: item table built from the CSR offsets (one item = up to 8 blocks of one block-row)
 int64_t sddmm_plan_bytes(int64_t n_rows, int64_t nnz);
 cudaError_t launch_build_sddmm_plan(const int32_t* ptr, int64_t n_rows, int64_t nnz, void* plan, cudaStream_t stream);
 int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t precision);

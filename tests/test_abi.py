@@ -48,7 +48,7 @@ def test_size_queries():
     assert lib.bsmm_plan_group(4096, 96, 2304, native.PREC_TF32X3) == 6
     assert lib.bsmm_plan_group(128, 24, 288, native.PREC_TF32X3) == 4
     assert lib.bsmm_packed_bytes(10, native.PREC_TF32) == 2 * 10 * 8192
-    assert lib.bsmm_sddmm_plan_bytes(8, 100) == 16 + 16 * (100 // 16 + 8)
+    assert lib.bsmm_sddmm_plan_bytes(8, 100) == 16 + 16 * (100 // 8 + 8)  # items of at most 8 blocks
     assert lib.bsmm_sddmm_workspace_bytes(64, 64, 100, 2, native.PREC_FP32_SIMT) == 0
 
 
