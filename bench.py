@@ -413,7 +413,11 @@ def run_gpu_arm(args, cfg):
         "algorithmic_flops_per_launch": f_op,
     }
 
-    cpu_value, cpu_m, cpu_t = time_cpu_reference(cfg, target_seconds=args.cpu_seconds, reps=3)
+    if world == 1:
+        cpu_value, cpu_m, cpu_t = time_cpu_reference(cfg, target_seconds=args.cpu_seconds, reps=3)
+        cpu_sample = "first %d of %d tokens, median of 3; numpy to_dense + fp32 matmul" % (cpu_m, m)
+    else:  # the host cores are timed in the single-GPU run only
+        cpu_value, cpu_sample = None, "not timed when n_gpus > 1"
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -425,7 +429,7 @@ def run_gpu_arm(args, cfg):
                         % (m * k * 4 >> 20, m * n * 4 >> 20)), **cfg),
         "roofline": roofline,
         "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-                         "sample": "first %d of %d tokens, median of 3; numpy to_dense + fp32 matmul" % (cpu_m, m)},
+                         "sample": cpu_sample},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
