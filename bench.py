@@ -475,7 +475,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3_d0.25", choices=sorted(WORKLOADS))
-    ap.add_argument("--precision", default="tf32x3", choices=["tf32x3", "tf32", "fp32"])
+    ap.add_argument("--precision", default="tf32x3", choices=["tf32x3", "tf32", "bf16", "fp32"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-comparators", action="store_true")
     args = ap.parse_args()

@@ -35,7 +35,7 @@ extern "C" {
 /* arithmetic of a contraction (bits 0..3 of `flags`) */
 #define BSMM_PREC_FP32_SIMT 0u /* exact fp32 FMA on CUDA cores (the reference's arithmetic) */
 #define BSMM_PREC_TF32X3 1u    /* tcgen05 kind::tf32, 3-pass hi/lo split, fp32-class accuracy  */
-#define BSMM_PREC_BF16 2u      /* tcgen05 kind::f16 on bf16 operands, fp32 accumulate        */
+#define BSMM_PREC_BF16 2u      /* tcgen05 kind::f16: operands rounded to bf16 in the kernel, fp32 accumulate; tensors stay fp32 */
 #define BSMM_PREC_TF32 3u      /* tcgen05 kind::tf32, single pass (cuBLAS allow_tf32 accuracy class) */
 #define BSMM_PREC_MASK 0xFu
 
@@ -100,7 +100,7 @@ int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks
  * (reference native/block_sparse_native.cpp:6-16, native/block_sparse_cutlass_kernel.cu:113-150):
  *   fwd   (flags without BSMM_DSD_DGRAD): out[m, n] = a[m, k] * W^T (+ bias[n]),  W is [n, k], ptr/idx = CSR
  *   dgrad (BSMM_DSD_DGRAD)              : out[m, n] = a[m, k] * W,               W is [k, n], ptr/idx = CSC
- * a: [m, k] row-major (fp32, or bf16 with BSMM_PREC_BF16); out: same element type; m is free,
+ * a: [m, k] row-major fp32; out: fp32; m is free,
  * n and k are multiples of 32.  Every output element is written (empty block-rows give zeros),
  * so `out` needs no pre-zeroing.  `data` is always required; `packed`/`plan` (and the plan's group size
  * in the flags, BSMM_DSD_GROUP) are required by the tensor-core precisions and ignored by FP32_SIMT.

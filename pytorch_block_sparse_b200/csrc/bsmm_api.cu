@@ -145,7 +145,7 @@ int bsmm_build_sddmm_plan(const int32_t* ptr, int64_t n_block_rows, int64_t nnz,
 int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t flags) {
     if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0) return -1;
     const uint32_t precision = flags & BSMM_PREC_MASK;
-    if (!bsmm::is_tf32_precision(precision)) return 0;
+    if (!bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return 0;
     if ((flags & (BSMM_SDDMM_A_COLMAJOR | BSMM_SDDMM_B_COLMAJOR)) != 0) return 0;
     return bsmm::sddmm_umma_workspace_bytes(rows, cols, tokens, nnz, precision);
 }
@@ -165,9 +165,10 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
         !aligned(plan, 16) || !aligned(workspace, 16))
         return BSMM_ERR_INVALID_ARGUMENT;
     if (nnz > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
-    if (precision != BSMM_PREC_FP32_SIMT && !bsmm::is_tf32_precision(precision)) return BSMM_ERR_UNSUPPORTED;
+    if (precision != BSMM_PREC_FP32_SIMT && !bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16)
+        return BSMM_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (bsmm::is_tf32_precision(precision) && !a_col && !b_col) {
+    if (precision != BSMM_PREC_FP32_SIMT && !a_col && !b_col) {
         const cudaError_t err = bsmm::launch_sddmm_umma(a, b, rows, cols, tokens, sparse_c, csr_idx, plan, nnz,
                                                         block_sumsq, workspace, precision, s);
         if (err != cudaErrorNotSupported) return cuda_status(err);

@@ -29,6 +29,9 @@ __host__ __device__ constexpr uint32_t image16_offset(uint32_t mn, uint32_t k) {
     return (k >> 3) * 512u + (mn >> 3) * 128u + (mn & 7u) * 16u + (k & 7u) * 2u;
 }
 constexpr uint32_t kImage16Bytes = 2048;
+constexpr uint32_t kImage16Lbo = 512;
+constexpr uint32_t kImage16Sbo = 128;
+constexpr uint32_t kImage16StepBytes = 1024;   // one MMA k-step = 16 values of k = two k-chunks
 
 // tensor-core arithmetic that reads the tf32 images
 __host__ __device__ constexpr bool is_tf32_precision(uint32_t precision) {

@@ -18,21 +18,23 @@
 //
 //   warps 0-1   X producers : TMA, four X slabs per unit (units by parity)
 //   warp 2      dY producer : TMA, one dY slab per step
-//   warp 3      dY split    : lo = v - trunc_tf32(v) of the dY slab into a second tile of the same layout
+//   warps 3-4   dY split    : lo = v - trunc_tf32(v) of the dY slab (half each) into a second tile of the same layout
 //                             (the tensor core reads only the tf32 bits of an operand, so the raw slab is hi)
-//   warps 4-5   MMA         : warp c owns chunk c (two chunks per item): per unit and k-step (8 tokens)
+//   warps 5-6   MMA         : warp c owns chunk c (two chunks per item): per unit and k-step (8 tokens)
 //                             x x [dy ; dy_lo] (N = 64) and x_lo x dy (N = 32), tcgen05.mma kind::tf32, M = 128,
 //                             into the main | correction columns of the chunk
-//   warps 6-17  X split     : three groups of four (unit mod 3): shared memory -> registers (transposing
+//   warps 7-18  X split     : three groups of four (unit mod 3): shared memory -> registers (transposing
 //                             reads, conflict-free under the 128-byte swizzle) -> hi, lo -> tensor memory;
 //                             six stages, so a chunk's copies run up to three steps ahead of its MMAs
-//   warps 18-21 drain       : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
+//   warps 19-22 drain       : every 1024 tokens tcgen05.ld each chunk's columns and add main + correction
 //                             (fp32, round to nearest) to the chunk's master tile in shared memory; final
 //                             store of the master tiles to global
 //
 // The promotion bounds the tensor core's systematic accumulate error (about 2e-8 relative per MMA).
 // Token ranges (grid.y > 1) write partial results to the workspace; a second kernel sums them in a
 // fixed order (deterministic, no atomics) and produces the per-slot sum of squares.
+#include <cuda_bf16.h>
+
 #include "bsmm_ptx.cuh"
 #include "bsmm_umma.cuh"
 
@@ -57,7 +59,8 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kChunkCols = 64;                     // main | correction
 constexpr uint32_t kAccCols = kChunks * kChunkCols;     // 128
 constexpr uint32_t kAStageCols = 64;                    // x_hi | x_lo, 32 tokens each
-constexpr int kXProducers = 2, kDyProducerWarp = 2, kDySplitWarp = 3, kFirstMmaWarp = 4;
+constexpr int kXProducers = 2, kDyProducerWarp = 2, kDySplitWarp = 3, kDySplitWarps = 2;  // halves of the slab
+constexpr int kFirstMmaWarp = kDySplitWarp + kDySplitWarps;
 constexpr int kSplitGroups = 3;  // groups of four split warps; unit u goes to group u mod kSplitGroups
 constexpr int kFirstSplitWarp = kFirstMmaWarp + kChunks, kSplitWarps = 4 * kSplitGroups;
 constexpr int kFirstDrainWarp = kFirstSplitWarp + kSplitWarps;
@@ -94,7 +97,9 @@ __device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint3
     return smem_desc_sw128_base32(addr, atom_stride, 512);
 }
 
-// kPasses = 3: 3xTF32 as described above; kPasses = 1: single-pass TF32 (no lo parts, no correction columns)
+// kPasses = 3: 3xTF32 as described above; kPasses = 1: single-pass TF32 (no lo parts, no correction columns);
+// kPasses = 0: bf16 operands (kind::f16, K = 16 per instruction): the dY split warp writes the slab transposed
+// and rounded as a K-major bf16 tile (the layout of the bf16 weight images), the X split warps pack token pairs
 template <int kPasses>
 __global__ void __launch_bounds__(kThreads, 1)
 sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
@@ -131,7 +136,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 128); mbar_init(a_empty(s), 1); }
-        for (int s = 0; s < kDyStages; ++s) { mbar_init(dy_full(s), 1); mbar_init(dylo_full(s), 32); mbar_init(dy_empty(s), nchunks); }
+        for (int s = 0; s < kDyStages; ++s) { mbar_init(dy_full(s), 1); mbar_init(dylo_full(s), 32 * kDySplitWarps); mbar_init(dy_empty(s), nchunks); }
         for (int c = 0; c < kChunks; ++c) { mbar_init(p_ready(c), 1); mbar_init(p_taken(c), 128); }
         misc[1] = 0;
         for (int s = 0; s < kStages; ++s) misc[2 + s] = 0;
@@ -204,24 +209,38 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 tma_load_2d(smem_base + kOffDy + ds * kDyStageBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
             }
         }
-    } else if (warp == kDySplitWarp) {
+    } else if (warp < kFirstMmaWarp) {
         // ------------------------------------------------------------------ dY split
         // lo = v - trunc_tf32(v), elementwise at the same offset of the stage's second half: the swizzle
         // needs no decoding; consecutive lanes take consecutive 16-byte chunks
-        for (int step = 0; step < nsteps && kPasses == 3; ++step) {
+        const int half = warp - kDySplitWarp;  // which half of the slab this warp converts
+        for (int step = 0; step < nsteps && kPasses != 1; ++step) {
             const int ds = step & (kDyStages - 1);
             wait(dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
             if (__any_sync(0xffffffffu, bad != 0)) break;
             uint8_t* base = smem_gen + kOffDy + ds * kDyStageBytes;
+            if (kPasses == 3) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 v = *reinterpret_cast<const float4*>(base + (lane + 32 * i) * 16);
-                float4 l;
-                l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
-                l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
-                l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
-                l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-                *reinterpret_cast<float4*>(base + kSlabBytes + (lane + 32 * i) * 16) = l;
+                for (int i = 4 * half; i < 4 * half + 4; ++i) {
+                    const float4 v = *reinterpret_cast<const float4*>(base + (lane + 32 * i) * 16);
+                    float4 l;
+                    l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+                    l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+                    l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+                    l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+                    *reinterpret_cast<float4*>(base + kSlabBytes + (lane + 32 * i) * 16) = l;
+                }
+            } else {
+                // lane = feature r; the slab (plain 128-byte swizzle in this mode) is read along the tokens
+                const uint8_t* col = base + ((lane & 3) << 2);
+#pragma unroll
+                for (int t = 16 * half; t < 16 * half + 16; t += 2) {
+                    const float v0 = *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
+                    const float v1 = *reinterpret_cast<const float*>(col + (t + 1) * 128 + (((lane >> 2) ^ ((t + 1) & 7)) << 4));
+                    const __nv_bfloat162 pr = __floats2bfloat162_rn(v0, v1);  // k = t low half, k = t + 1 high half
+                    *reinterpret_cast<uint32_t*>(base + kSlabBytes + image16_offset((uint32_t)lane, (uint32_t)t)) =
+                        *reinterpret_cast<const uint32_t*>(&pr);
+                }
             }
             fence_proxy_async_smem();  // generic-proxy writes, read by the MMA through the async proxy
             mbar_arrive(dylo_full(ds));
@@ -231,6 +250,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const int ch = warp - kFirstMmaWarp;  // accumulations into one chunk stay in one thread's program order
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, true);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, true);
+        constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, false);
         bool pending = false;   // a promotion of the chunk was requested and not yet seen taken
         uint32_t taken_ph = 0;
         for (int step = 0; step < nsteps && !bad && ch < nchunks; ++step) {
@@ -239,7 +259,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             const int ds = step & (kDyStages - 1);
             const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
             const bool drain = drain_step(step);
-            wait(kPasses == 3 ? dylo_full(ds) : dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
+            wait(kPasses != 1 ? dylo_full(ds) : dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
             wait_count(a_count(as), 4u * (uint32_t)(u / kStages + 1));
             tc_fence_after();  // the split warps' tcgen05.st precede the MMAs that read the stage
             if (fresh && pending) {
@@ -255,14 +275,23 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             const uint32_t acc0 = fresh ? 0u : 1u;
             const uint32_t a_bar = a_empty(as), dy_bar = dy_empty(ds), p_bar = p_ready(ch);
             if (elect_one() && !bad) {
+                if (kPasses == 0) {
+                    const uint64_t b16 =
+                        smem_desc_noswizzle(smem_base + kOffDy + ds * kDyStageBytes + kSlabBytes, kImage16Lbo, kImage16Sbo);
 #pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    const uint64_t b = b_desc + (uint64_t)(s * (kKStepBytes >> 4));
-                    if (kPasses == 3) {
-                        mma_ts_tf32(d, a_tm + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);     // x x [dy ; dy_lo]
-                        mma_ts_tf32(d + 32, a_tm + 32 + s * 8, b, idesc_narrow, 1u);         // x_lo x dy
-                    } else {
-                        mma_ts_tf32(d, a_tm + s * 8, b, idesc_narrow, s == 0 ? acc0 : 1u);
+                    for (int s = 0; s < 2; ++s)  // 16 tokens per instruction: 8 columns of token pairs, two k-chunks
+                        mma_ts_f16(d, a_tm + s * 8, b16 + (uint64_t)(s * (kImage16StepBytes >> 4)), idesc_bf16,
+                                   s == 0 ? acc0 : 1u);
+                } else {
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        const uint64_t b = b_desc + (uint64_t)(s * (kKStepBytes >> 4));
+                        if (kPasses == 3) {
+                            mma_ts_tf32(d, a_tm + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);     // x x [dy ; dy_lo]
+                            mma_ts_tf32(d + 32, a_tm + 32 + s * 8, b, idesc_narrow, 1u);         // x_lo x dy
+                        } else {
+                            mma_ts_tf32(d, a_tm + s * 8, b, idesc_narrow, s == 0 ? acc0 : 1u);
+                        }
                     }
                 }
                 mma_commit(a_bar);
@@ -307,8 +336,18 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             mbar_arrive(x_empty(xs));
             tc_fence_after();
             const uint32_t a_tm = tmem_lane + kAccCols + xs * kAStageCols;
-            tmem_st32(a_tm, hi);
-            if (kPasses == 3) tmem_st32(a_tm + 32, lo);
+            if (kPasses == 0) {
+                uint32_t packed[16];  // column j: token 2j in the low half, token 2j + 1 in the high half
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(hi[2 * j]), __uint_as_float(hi[2 * j + 1]));
+                    packed[j] = *reinterpret_cast<const uint32_t*>(&pr);
+                }
+                tmem_st16(a_tm, packed);
+            } else {
+                tmem_st32(a_tm, hi);
+                if (kPasses == 3) tmem_st32(a_tm + 32, lo);
+            }
             tmem_wait_st();
             tc_fence_before();
             if (__any_sync(0xffffffffu, bad != 0)) break;  // nothing is published once a wait has given up
@@ -523,7 +562,7 @@ cudaError_t launch_build_sddmm_plan(const int32_t* ptr, int64_t n_rows, int64_t 
 }
 
 int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t precision) {
-    if (!is_tf32_precision(precision) || tokens < kStepTokens || nnz == 0) return 0;
+    if ((!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) || tokens < kStepTokens || nnz == 0) return 0;
     int64_t splits, per;
     choose_splits(rows / 32, cols, nnz, tokens, &splits, &per);
     return splits > 1 ? splits * nnz * (int64_t)kBlockElems * 4 : 0;
@@ -532,7 +571,8 @@ int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, i
 cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens,
                               float* sparse_c, const int32_t* csr_idx, const void* plan, int64_t nnz,
                               float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream) {
-    if (!is_tf32_precision(precision) || plan == nullptr || csr_idx == nullptr) return cudaErrorNotSupported;
+    if ((!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) || plan == nullptr || csr_idx == nullptr)
+        return cudaErrorNotSupported;
     if (tokens < kStepTokens) return cudaErrorNotSupported;  // a box may not exceed its tensor
     if (tokens > 0x7fffffffll) return cudaErrorInvalidValue;
     const int64_t n_rows = rows / 32;
@@ -541,16 +581,17 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     if (splits > 1 && workspace == nullptr) return cudaErrorInvalidValue;
     if (splits > 65535) return cudaErrorInvalidValue;
 
-    const bool x3 = precision == BSMM_PREC_TF32X3;
-    cudaError_t err = cudaFuncSetAttribute(x3 ? sddmm_umma_tf32_kernel<3> : sddmm_umma_tf32_kernel<1>,
+    const bool x3 = precision == BSMM_PREC_TF32X3, bf16 = precision == BSMM_PREC_BF16;
+    cudaError_t err = cudaFuncSetAttribute(x3 ? sddmm_umma_tf32_kernel<3> : bf16 ? sddmm_umma_tf32_kernel<0> : sddmm_umma_tf32_kernel<1>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (err != cudaSuccess) return err;
     CUtensorMap tmap_x, tmap_dy;
     err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)cols, (uint64_t)tokens, 32,
                        kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess) return err;
+    // dY is the MMA's operand as loaded in the tf32 modes (32-byte-atom swizzle); in bf16 mode a warp reads it
     err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)rows, (uint64_t)tokens, 32,
-                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+                       kStepTokens, bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (err != cudaSuccess) return err;
 
     SddmmParams p;
@@ -565,6 +606,7 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     p.split_stride = nnz * (int64_t)kBlockElems;
     dim3 grid((unsigned)max_items(n_rows, nnz), (unsigned)splits);
     if (x3) sddmm_umma_tf32_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
+    else if (bf16) sddmm_umma_tf32_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
     else sddmm_umma_tf32_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;

@@ -29,6 +29,8 @@
 // Keeping the main term apart from the corrections and promoting it every 32 blocks bounds the
 // tensor core's systematic fp32-accumulate error (about 2e-8 relative per accumulation).
 // Every wait is bounded; on expiry the CTA raises the device status word, stops issuing and drains.
+#include <cuda_bf16.h>
+
 #include "bsmm_ptx.cuh"
 #include "bsmm_umma.cuh"
 
@@ -52,14 +54,22 @@ constexpr int kFirstSplitWarp = kFirstMmaWarp + kMmaWarps;
 constexpr int kSplitWarps = 8;                    // two groups of four, taking alternate slabs
 constexpr int kFirstDrainWarp = kFirstSplitWarp + kSplitWarps;
 constexpr int kThreads = 32 * (kFirstDrainWarp + 4);
-constexpr int kXStages = 4;  // even: a stage always belongs to the same split-warp group
-constexpr int kWRing = 4;                     // weight stages per MMA warp (a ring of its own, a power of two)
+#ifndef BSMM_X_STAGES
+#define BSMM_X_STAGES 4
+#endif
+constexpr int kXStages = BSMM_X_STAGES;  // even: a stage always belongs to the same split-warp group
+#ifndef BSMM_W_RING
+#define BSMM_W_RING 4
+#endif
+constexpr int kWRing = BSMM_W_RING;           // weight stages per MMA warp (a ring of its own, a power of two)
 constexpr int kWStages = kMmaWarps * kWRing;
 
 template <int G, int kPasses>
 struct Cfg {
+    // kPasses: 3 = 3xTF32, 1 = single-pass TF32, 0 = bf16 operands (kind::f16), fp32 accumulation throughout
     static constexpr uint32_t kRowCols = kPasses == 3 ? 64 : 32;     // main | correction
-    static constexpr uint32_t kAStageCols = kPasses == 3 ? 64 : 32;  // x_hi | x_lo
+    static constexpr uint32_t kAStageCols = kPasses == 3 ? 64 : kPasses == 1 ? 32 : 16;  // x_hi | x_lo; bf16 pairs
+    static constexpr uint32_t kWBytes = kPasses == 0 ? kImage16Bytes : kImage32Bytes;    // one block's image
     static constexpr uint32_t kAccCols = G * kRowCols;
     static constexpr int kAStagesMax = (int)((kTmemCols - kAccCols) / kAStageCols);
     static constexpr int kAStages = kAStagesMax >= 8 ? 8 : kAStagesMax >= 4 ? 4 : 2;  // a power of two
@@ -221,10 +231,10 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                     const int ws = (int)(warp * kWRing + (seq & (kWRing - 1)));
                     wait(w_empty(ws), ((seq / kWRing) & 1u) ^ 1u, 1);
                     ++seq;
-                    const uint8_t* src = p.packed + (int64_t)slot * kWStageBytes;
+                    const uint8_t* src = p.packed + (int64_t)slot * C::kWBytes;
                     if (elect_one() && !bad) {
-                        mbar_arrive_expect_tx(w_full(ws), kWStageBytes);
-                        bulk_load(smem_base + C::kOffW + ws * kWStageBytes, src, kWStageBytes, w_full(ws));
+                        mbar_arrive_expect_tx(w_full(ws), C::kWBytes);
+                        bulk_load(smem_base + C::kOffW + ws * kWStageBytes, src, C::kWBytes, w_full(ws));
                     }
                 }
             }
@@ -270,6 +280,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         const uint32_t mw = (uint32_t)(warp - kFirstMmaWarp);
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
+        constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, false);
         uint32_t started = 0;   // bit r: the row's columns hold a partial sum of the current segment
         uint32_t pending = 0;   // bit r: a promotion of the row was requested and not yet seen taken
         uint32_t taken_ph = 0;  // bit r: parity of the next p_taken[r] phase to wait for
@@ -310,7 +321,8 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                     // the warp that issues a slab's last block also arrives for the warps that have none in it
                     const uint32_t idle = ((lasts >> i) & 1u) * (((idle_b0 >> i) & 1u) | (((idle_b1 >> i) & 1u) << 1));
                     const uint64_t b_desc =
-                        smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
+                        kPasses == 0 ? smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage16Lbo, kImage16Sbo)
+                                     : smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
                     const uint32_t a_hi = tmem + C::kAccCols + as * C::kAStageCols;
                     const uint32_t d = tmem + row * C::kRowCols;
                     const uint32_t acc0 = (started & rbit) ? 1u : 0u;
@@ -329,16 +341,23 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                     tc_fence_after();
                     const long long ti = tracing ? clock64() : 0;
                     if (elect_one() && !bad) {
+                        if (kPasses == 0) {
 #pragma unroll
-                        for (int s = 0; s < 4; ++s) {
-                            // k-step s: 8 columns further in the slab's tensor-memory copy, 2 KiB further in the image
-                            const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
-                            const uint32_t acc = s == 0 ? acc0 : 1u;
-                            if (kPasses == 3) {
-                                mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, acc);               // x_hi x [w_hi ; w_lo]
-                                mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // x_lo x w_hi
-                            } else {
-                                mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, acc);
+                            for (int s = 0; s < 2; ++s)  // k-step of 16: 8 columns (bf16 pairs) further, two k-chunks further
+                                mma_ts_f16(d, a_hi + s * 8, b_desc + (uint64_t)(s * (kImage16StepBytes >> 4)), idesc_bf16,
+                                           s == 0 ? acc0 : 1u);
+                        } else {
+#pragma unroll
+                            for (int s = 0; s < 4; ++s) {
+                                // k-step s: 8 columns further in the slab's tensor-memory copy, 2 KiB further in the image
+                                const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
+                                const uint32_t acc = s == 0 ? acc0 : 1u;
+                                if (kPasses == 3) {
+                                    mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, acc);               // x_hi x [w_hi ; w_lo]
+                                    mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // x_lo x w_hi
+                                } else {
+                                    mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, acc);
+                                }
                             }
                         }
                         mma_commit(w_bar);
@@ -397,8 +416,18 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                 wait(a_empty(as), ((uint32_t)(s / AS) & 1u) ^ 1u, 1);
                 tc_fence_after();
                 const uint32_t a_hi = tmem_lane + C::kAccCols + as * C::kAStageCols;
-                tmem_st32(a_hi, hi);
-                if (kPasses == 3) tmem_st32(a_hi + 32, lo);
+                if (kPasses == 0) {
+                    uint32_t packed[16];  // column j: k = 2j in the low half, k = 2j + 1 in the high half
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(hi[2 * j]), __uint_as_float(hi[2 * j + 1]));
+                        packed[j] = *reinterpret_cast<const uint32_t*>(&pr);
+                    }
+                    tmem_st16(a_hi, packed);
+                } else {
+                    tmem_st32(a_hi, hi);
+                    if (kPasses == 3) tmem_st32(a_hi + 32, lo);
+                }
                 tmem_wait_st();
                 tc_fence_before();
                 if (__any_sync(0xffffffffu, bad != 0)) { go = false; break; }  // nothing is published once a wait has given up
@@ -592,7 +621,7 @@ cudaError_t device_status_address(unsigned int** addr) {
 cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
                             bool out_colmajor, cudaStream_t stream) {
-    if (!is_tf32_precision(precision)) return cudaErrorNotSupported;
+    if (!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return cudaErrorNotSupported;
     if (!plan_group_valid(group)) return cudaErrorInvalidValue;
     if (m == 0 || n == 0) return cudaSuccess;
     if (k == 0) return cudaErrorInvalidValue;  // nothing to contract over; a tensor map cannot describe it
@@ -610,7 +639,7 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     if (err != cudaSuccess) return err;
 
     DsdParams p;
-    p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * (int64_t)kImage32Bytes : 0);
+    p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * packed_slot_bytes(precision) : 0);
     p.group_off = static_cast<const int32_t*>(plan);
     p.group_slabs = p.group_off + groups + 1;
     p.entries = reinterpret_cast<const PlanEntry*>(static_cast<const uint8_t*>(plan) +
@@ -630,6 +659,13 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     p.trace_block = g_trace_block;
     const bool split = precision == BSMM_PREC_TF32X3;
     if (split && group == 8) return cudaErrorInvalidValue;  // 8 rows x 64 columns leave no tensor memory for A
+    if (precision == BSMM_PREC_BF16) {
+        switch (group) {
+            case 4: return launch_dsd_g<4, 0>(tmap_a, p, tiles, stream);
+            case 6: return launch_dsd_g<6, 0>(tmap_a, p, tiles, stream);
+            default: return launch_dsd_g<8, 0>(tmap_a, p, tiles, stream);
+        }
+    }
     switch (group) {
         case 4: return split ? launch_dsd_g<4, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, p, tiles, stream);
         case 6: return split ? launch_dsd_g<6, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, p, tiles, stream);

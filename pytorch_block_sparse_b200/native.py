@@ -118,7 +118,8 @@ def device_status(clear=True):
 
 def set_default_precision(name):
     """'tf32x3' (default; fp32-class accuracy on tensor cores), 'fp32' (CUDA-core FMA), 'tf32' (single
-    tensor-core pass, the accuracy class of cuBLAS with allow_tf32) or 'bf16'."""
+    tensor-core pass, the accuracy class of cuBLAS with allow_tf32) or 'bf16' (operands rounded to bf16 inside
+    the kernels, fp32 tensors and accumulation)."""
     global _default_precision
     if name not in PRECISIONS:
         raise ValueError("unknown precision %r, expected one of %s" % (name, sorted(PRECISIONS)))
@@ -217,7 +218,7 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
     lib = load()
     m, k = a.shape
     prec = packed.precision
-    want = torch.bfloat16 if prec == PREC_BF16 else torch.float32
+    want = torch.float32  # every mode reads and writes fp32 tensors; 'bf16' rounds the operands in the kernel
     if a.dtype != want:
         a = a.to(want)
     if out is None:
@@ -294,8 +295,6 @@ def sddmm(a, a_rowmajor, b, b_rowmajor, blocks, out, precision=None, block_sumsq
     _need_cuda(a, "dense_a")
     lib = load()
     prec = resolve_precision(precision) if not isinstance(precision, int) else precision
-    if prec == PREC_BF16:
-        prec = PREC_TF32X3  # no bf16 weight-gradient kernel: use the fp32-class mode
     tokens, rows = a.shape
     cols = b.shape[1]
     nnz = blocks.shape[0] // 2

@@ -70,7 +70,7 @@ def test_argument_validation_without_device():
     # misaligned pointer
     assert lib.bsmm_sddmm(ctypes.c_void_p(0x1004), fake, 32, 32, 8, fake, fake, 1, null, null, null, null, 0, null) == 1
     assert lib.bsmm_sddmm(fake, fake, 48, 32, 8, fake, fake, 1, null, null, null, null, 0, null) == 1
-    assert lib.bsmm_sddmm(fake, fake, 32, 32, 8, fake, fake, 1, null, null, null, null, native.PREC_BF16, null) == 2
+    assert lib.bsmm_sddmm(fake, fake, 32, 32, 8, fake, fake, 1, null, null, null, null, 7, null) == 2  # no such arithmetic
     assert lib.bsmm_build_sddmm_plan(null, 4, 4, fake, null) == 1
     assert lib.bsmm_pack_weights(null, 3, native.PREC_TF32X3, fake, null, null) == 1
     assert lib.bsmm_build_plan(null, fake, 4, 4, 6, fake, null) == 1

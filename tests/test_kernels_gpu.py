@@ -257,6 +257,23 @@ def test_plan_is_the_group_merge_of_the_csr(group):
                              | ((idle << 4) if last else 0))
 
 
+@pytest.mark.parametrize("group", ["4", "6", "8"])
+def test_bf16_mode(group, monkeypatch):
+    """Opt-in 'bf16' precision: operands rounded to bf16 inside the kernels (tensors stay fp32), fp32
+    accumulation; bound 1e-2 relative Frobenius on all three contractions."""
+    monkeypatch.setenv("BSMM_PLAN_GROUP", group)
+    m = make_matrix((416, 352), n_blocks=70, seed=41)
+    x, dy, bias = randn((2100, 352), seed=42), randn((2100, 416), seed=43), randn((416,), seed=44)
+    check(run_dsd(m, x, True, "bf16", bias), oracle_dsd(m, x, True, bias), "bf16", "fwd")
+    check(run_dsd(m, dy, False, "bf16"), oracle_dsd(m, dy, False), "bf16", "dgrad")
+    got = m.matmul_with_output_sparse_support(dy.cuda(), x.cuda(), precision="bf16")
+    torch.cuda.synchronize()
+    want = orc.wgrad(dy.numpy(), x.numpy(), tuple(m.shape), m.blocks.cpu().numpy())
+    check(got, want, "bf16", "wgrad")
+    assert orc.rel_fro(got.float().cpu().numpy().reshape(want.shape), want) > 1e-4  # really bf16 operands
+    assert_device_healthy()
+
+
 def test_single_pass_tf32_wgrad():
     """Opt-in 'tf32' precision of the weight gradient: bound 2e-3 relative Frobenius; 2100 tokens cross two
     promotion points and leave a ragged last step."""
