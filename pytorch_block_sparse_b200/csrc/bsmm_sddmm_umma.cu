@@ -253,27 +253,33 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, false);
         bool pending = false;   // a promotion of the chunk was requested and not yet seen taken
         uint32_t taken_ph = 0;
+        int as = ch;               // stage of unit u = step * nchunks + ch: u mod kStages, kept incrementally
+        uint32_t a_target = 4;     // 4 * (u / kStages + 1): the stage's copy count that means "unit u is there"
         for (int step = 0; step < nsteps && !bad && ch < nchunks; ++step) {
-            const int u = step * nchunks + ch;
-            const int as = u % kStages;
+            // everything that does not depend on the operands first; the stage counter's load travels while
+            // the dY barrier is polled
             const int ds = step & (kDyStages - 1);
             const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
             const bool drain = drain_step(step);
-            wait(kPasses != 1 ? dylo_full(ds) : dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
-            wait_count(a_count(as), 4u * (uint32_t)(u / kStages + 1));
-            tc_fence_after();  // the split warps' tcgen05.st precede the MMAs that read the stage
-            if (fresh && pending) {
-                wait(p_taken(ch), taken_ph);
-                taken_ph ^= 1u;
-                pending = false;
-                tc_fence_after();  // the drain warps' tcgen05.ld precede the MMA that overwrites the columns
-            }
             // B: atom 0 = the raw dY slab, atom 1 (N = 64 only) = its lo part, one slab further
             const uint64_t b_desc = smem_desc_mnmajor_sw128(smem_base + kOffDy + ds * kDyStageBytes, kSlabBytes);
             const uint32_t a_tm = tmem + kAccCols + as * kAStageCols;
             const uint32_t d = tmem + ch * kChunkCols;
             const uint32_t acc0 = fresh ? 0u : 1u;
             const uint32_t a_bar = a_empty(as), dy_bar = dy_empty(ds), p_bar = p_ready(ch);
+            const uint32_t a_cnt = a_count(as);
+            const uint32_t seen = smem_load_acquire(a_cnt);
+            if (fresh && pending) {
+                wait(p_taken(ch), taken_ph);
+                taken_ph ^= 1u;
+                pending = false;
+            }
+            wait(kPasses != 1 ? dylo_full(ds) : dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
+            if ((int32_t)(seen - a_target) < 0) wait_count(a_cnt, a_target);
+            // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the columns) precede the MMAs
+            tc_fence_after();
+            as += nchunks;
+            if (as >= kStages) { as -= kStages; a_target += 4; }
             if (elect_one() && !bad) {
                 if (kPasses == 0) {
                     const uint64_t b16 =

@@ -332,11 +332,12 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                         taken_ph ^= rbit;
                         pending &= ~rbit;
                     }
+                    // the stage counter's load travels while the weight barrier is polled
+                    const uint32_t a_cnt = a_count(as), a_target = 4u * (uint32_t)(slab / AS + 1);
+                    const uint32_t seen = slab != cur_slab ? smem_load_acquire(a_cnt) : a_target;
                     wait(w_full(ws), w_parity, 1);
-                    if (slab != cur_slab) {
-                        wait_count(a_count(as), 4u * (uint32_t)(slab / AS + 1));
-                        cur_slab = slab;
-                    }
+                    if ((int32_t)(seen - a_target) < 0) wait_count(a_cnt, a_target);
+                    cur_slab = slab;
                     // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the row) precede the MMAs
                     tc_fence_after();
                     const long long ti = tracing ? clock64() : 0;
