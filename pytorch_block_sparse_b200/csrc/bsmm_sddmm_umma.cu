@@ -178,25 +178,31 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
 
     if (warp < kXProducers) {
         // ------------------------------------------------------------------ X producers
-        int step = 0, ch = warp;
-        while (ch >= nchunks) { ch -= nchunks; ++step; }
-        for (int u = warp; u < nunits && !bad; u += kXProducers) {
-            const int xs = u % kStages;
-            const int nb = min(4, nblk - ch * 4);
-            const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
-            int bcol[4];
+        // Warp w loads the units of parity w.  With two chunks that is chunk w of every step, with one chunk
+        // every other step; either way the unit number grows by two per iteration.  The block columns of both
+        // chunks are fetched from the lanes once, so the loop has no shuffles and no index loops.
+        static_assert(kChunks == 2 && kXProducers == 2, "unit parity = producer warp");
+        const int ch = nchunks == 2 ? warp : 0;
+        const int nb = min(4, nblk - ch * 4);
+        int bcol[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) bcol[j] = __shfl_sync(0xffffffffu, my_ent.x, ch * 4 + j);
-            wait(x_empty(xs), ((uint32_t)(u / kStages) & 1u) ^ 1u);
+        for (int j = 0; j < 4; ++j) bcol[j] = __shfl_sync(0xffffffffu, my_ent.x, ch * 4 + j) * 32;
+        int xs = warp;            // stage of unit u: u mod kStages, kept incrementally
+        uint32_t parity = 1u;     // of the stage's release barrier: (u / kStages) & 1, inverted
+        const int step_stride = nchunks == 2 ? 1 : 2;
+        for (int step = nchunks == 2 ? 0 : warp; step < nsteps; step += step_stride) {
+            const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
+            wait(x_empty(xs), parity);
             const uint32_t dst = smem_base + kOffX + xs * kXStageBytes;
-            if (elect_one() && !bad) {
+            if (elect_one() & (bad == 0)) {
                 mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    if (j < nb) tma_load_2d(dst + j * kSlabBytes, &tmap_x, bcol[j] * 32, tok, x_full(xs));
+                    if (j < nb) tma_load_2d(dst + j * kSlabBytes, &tmap_x, bcol[j], tok, x_full(xs));
             }
-            ch += kXProducers;
-            while (ch >= nchunks) { ch -= nchunks; ++step; }
+            const bool wrap = xs + 2 >= kStages;
+            xs = wrap ? xs + 2 - kStages : xs + 2;
+            parity ^= wrap ? 1u : 0u;
         }
     } else if (warp == kDyProducerWarp) {
         // ------------------------------------------------------------------ dY producer
@@ -251,60 +257,66 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, true);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, true);
         constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, false);
-        bool pending = false;   // a promotion of the chunk was requested and not yet seen taken
+        // The loop is cut into promotion segments (kDrainSteps steps) so that the per-step body has no
+        // first-step / last-step decisions: a conditional branch costs this lone warp ~40 cycles, and the
+        // body's length bounds how fast a chunk's stages turn around.
         uint32_t taken_ph = 0;
         int as = ch;               // stage of unit u = step * nchunks + ch: u mod kStages, kept incrementally
         uint32_t a_target = 4;     // 4 * (u / kStages + 1): the stage's copy count that means "unit u is there"
-        for (int step = 0; step < nsteps && !bad && ch < nchunks; ++step) {
-            // everything that does not depend on the operands first; the stage counter's load travels while
-            // the dY barrier is polled
-            const int ds = step & (kDyStages - 1);
-            const bool fresh = (step % kDrainSteps) == 0;  // first step of a segment overwrites the columns
-            const bool drain = drain_step(step);
-            // B: atom 0 = the raw dY slab, atom 1 (N = 64 only) = its lo part, one slab further
-            const uint64_t b_desc = smem_desc_mnmajor_sw128(smem_base + kOffDy + ds * kDyStageBytes, kSlabBytes);
-            const uint32_t a_tm = tmem + kAccCols + as * kAStageCols;
-            const uint32_t d = tmem + ch * kChunkCols;
-            const uint32_t acc0 = fresh ? 0u : 1u;
-            const uint32_t a_bar = a_empty(as), dy_bar = dy_empty(ds), p_bar = p_ready(ch);
-            const uint32_t a_cnt = a_count(as);
-            const uint32_t seen = smem_load_acquire(a_cnt);
-            if (fresh && pending) {
+        const uint32_t d = tmem + ch * kChunkCols;
+        const uint32_t p_bar = p_ready(ch);
+        for (int seg = 0; seg < nsteps && ch < nchunks; seg += kDrainSteps) {
+            const int seg_end = min(nsteps, seg + kDrainSteps);
+            if (seg != 0) {  // the drain warps must have read the columns before the segment's first MMA overwrites them
                 wait(p_taken(ch), taken_ph);
                 taken_ph ^= 1u;
-                pending = false;
             }
-            wait(kPasses != 1 ? dylo_full(ds) : dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
-            if ((int32_t)(seen - a_target) < 0) wait_count(a_cnt, a_target);
-            // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the columns) precede the MMAs
-            tc_fence_after();
-            as += nchunks;
-            if (as >= kStages) { as -= kStages; a_target += 4; }
-            if (elect_one() && !bad) {
-                if (kPasses == 0) {
-                    const uint64_t b16 =
-                        smem_desc_noswizzle(smem_base + kOffDy + ds * kDyStageBytes + kSlabBytes, kImage16Lbo, kImage16Sbo);
+            uint32_t acc0 = 0u;  // the segment's first MMA overwrites the columns
+            for (int step = seg; step < seg_end; ++step) {
+                // everything that does not depend on the operands first; the stage counter's load travels
+                // while the dY barrier is polled
+                const int ds = step & (kDyStages - 1);
+                // B: atom 0 = the raw dY slab, atom 1 (N = 64 only) = its lo part, one slab further
+                const uint64_t b_desc = smem_desc_mnmajor_sw128(smem_base + kOffDy + ds * kDyStageBytes, kSlabBytes);
+                const uint32_t a_tm = tmem + kAccCols + as * kAStageCols;
+                const uint32_t a_bar = a_empty(as), dy_bar = dy_empty(ds);
+                const uint32_t a_cnt = a_count(as);
+                const uint32_t seen = smem_load_acquire(a_cnt);
+                wait(kPasses != 1 ? dylo_full(ds) : dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
+                if ((int32_t)(seen - a_target) < 0) wait_count(a_cnt, a_target);
+                // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the columns) precede the MMAs
+                tc_fence_after();
+                if (elect_one() & (bad == 0)) {
+                    if (kPasses == 0) {
+                        const uint64_t b16 =
+                            smem_desc_noswizzle(smem_base + kOffDy + ds * kDyStageBytes + kSlabBytes, kImage16Lbo, kImage16Sbo);
 #pragma unroll
-                    for (int s = 0; s < 2; ++s)  // 16 tokens per instruction: 8 columns of token pairs, two k-chunks
-                        mma_ts_f16(d, a_tm + s * 8, b16 + (uint64_t)(s * (kImage16StepBytes >> 4)), idesc_bf16,
-                                   s == 0 ? acc0 : 1u);
-                } else {
+                        for (int s = 0; s < 2; ++s)  // 16 tokens per instruction: 8 columns of token pairs, two k-chunks
+                            mma_ts_f16(d, a_tm + s * 8, b16 + (uint64_t)(s * (kImage16StepBytes >> 4)), idesc_bf16,
+                                       s == 0 ? acc0 : 1u);
+                    } else {
 #pragma unroll
-                    for (int s = 0; s < 4; ++s) {
-                        const uint64_t b = b_desc + (uint64_t)(s * (kKStepBytes >> 4));
-                        if (kPasses == 3) {
-                            mma_ts_tf32(d, a_tm + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);     // x x [dy ; dy_lo]
-                            mma_ts_tf32(d + 32, a_tm + 32 + s * 8, b, idesc_narrow, 1u);         // x_lo x dy
-                        } else {
-                            mma_ts_tf32(d, a_tm + s * 8, b, idesc_narrow, s == 0 ? acc0 : 1u);
+                        for (int s = 0; s < 4; ++s) {
+                            const uint64_t b = b_desc + (uint64_t)(s * (kKStepBytes >> 4));
+                            if (kPasses == 3) {
+                                mma_ts_tf32(d, a_tm + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);     // x x [dy ; dy_lo]
+                                mma_ts_tf32(d + 32, a_tm + 32 + s * 8, b, idesc_narrow, 1u);         // x_lo x dy
+                            } else {
+                                mma_ts_tf32(d, a_tm + s * 8, b, idesc_narrow, s == 0 ? acc0 : 1u);
+                            }
                         }
                     }
+                    mma_commit(a_bar);
+                    mma_commit(dy_bar);
+                    // the segment's columns are complete once everything this thread issued has executed
+                    if (step + 1 == seg_end) mma_commit(p_bar);
                 }
-                mma_commit(a_bar);
-                mma_commit(dy_bar);
-                if (drain) mma_commit(p_bar);
+                acc0 = 1u;
+                const int next = as + nchunks;
+                const bool wrap = next >= kStages;
+                as = wrap ? next - kStages : next;
+                a_target += wrap ? 4u : 0u;
             }
-            if (drain) pending = true;
         }
     } else if (warp < kFirstDrainWarp) {
         // ------------------------------------------------------------------ X split
@@ -314,10 +326,9 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const int quarter = warp & 3;
         const int group = (warp - kFirstSplitWarp) >> 2;
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
-        int ch = group;
-        while (ch >= nchunks) ch -= nchunks;
         for (int u = group; u < nunits; u += kSplitGroups) {
             const int xs = u % kStages;
+            const int ch = nchunks == 2 ? (u & 1) : 0;
             const int nb = min(4, nblk - ch * 4);
             // one wait instruction for both barriers (a successful wait costs ~85 cycles whatever it tests): the
             // lower half-warp polls the slabs' arrival, the upper half the tensor-memory stage's release
@@ -358,8 +369,6 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             tc_fence_before();
             if (__any_sync(0xffffffffu, bad != 0)) break;  // nothing is published once a wait has given up
             if (lane == 0) smem_add_release(a_count(xs), 1u);
-            ch += kSplitGroups;
-            while (ch >= nchunks) ch -= nchunks;
         }
     } else {
         // ------------------------------------------------------------------ drain + epilogue
