@@ -326,19 +326,20 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const int quarter = warp & 3;
         const int group = (warp - kFirstSplitWarp) >> 2;
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+        int xs = group;        // stage of unit u: u mod kStages, kept incrementally (u grows by kSplitGroups)
+        uint32_t use = 0;      // u / kStages
         for (int u = group; u < nunits; u += kSplitGroups) {
-            const int xs = u % kStages;
-            const int ch = nchunks == 2 ? (u & 1) : 0;
-            const int nb = min(4, nblk - ch * 4);
             // one wait instruction for both barriers (a successful wait costs ~85 cycles whatever it tests): the
             // lower half-warp polls the slabs' arrival, the upper half the tensor-memory stage's release
             {
                 const bool upper = lane >= 16;
-                wait(upper ? a_empty(xs) : x_full(xs), ((uint32_t)(u / kStages) & 1u) ^ (upper ? 1u : 0u));
+                wait(upper ? a_empty(xs) : x_full(xs), (use & 1u) ^ (upper ? 1u : 0u));
                 __syncwarp();
             }
+            // (a quarter without a block, in an item's ragged last chunk, reads whatever the stage holds: its
+            // accumulator rows are independent of the others and never stored)
             uint32_t hi[32], lo[32];
-            if (quarter < nb) {
+            {
                 const uint8_t* col = smem_gen + kOffX + xs * kXStageBytes + quarter * kSlabBytes + ((lane & 3) << 2);
 #pragma unroll
                 for (int t = 0; t < 32; ++t) {
@@ -346,9 +347,6 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                     hi[t] = v;
                     if (kPasses == 3) lo[t] = __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xffffe000u));
                 }
-            } else {  // no block there: the rows are never stored, keep them finite
-#pragma unroll
-                for (int t = 0; t < 32; ++t) { hi[t] = 0u; lo[t] = 0u; }
             }
             mbar_arrive(x_empty(xs));
             tc_fence_after();
@@ -367,8 +365,10 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             }
             tmem_wait_st();
             tc_fence_before();
-            if (__any_sync(0xffffffffu, bad != 0)) break;  // nothing is published once a wait has given up
-            if (lane == 0) smem_add_release(a_count(xs), 1u);
+            if ((lane == 0) & (bad == 0)) smem_add_release(a_count(xs), 1u);  // nothing is published once a wait has given up
+            const bool wrap = xs + kSplitGroups >= kStages;
+            xs = wrap ? xs + kSplitGroups - kStages : xs + kSplitGroups;
+            use += wrap ? 1u : 0u;
         }
     } else {
         // ------------------------------------------------------------------ drain + epilogue

@@ -391,8 +391,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
         static_assert(XS % 2 == 0 && AS % 2 == 0, "a ring stage must stay with one split-warp group");
         int slab0 = 0;  // slabs of this CTA's earlier tiles
-        bool go = true;
-        for (int tile = blockIdx.x; tile < n_tiles && go; tile += tile_step) {
+        for (int tile = blockIdx.x; tile < n_tiles && !__any_sync(0xffffffffu, bad != 0); tile += tile_step) {
             const int nslabs = __ldg(p.group_slabs + tile % p.groups);
             for (int s = slab0 + ((group ^ slab0) & 1); s < slab0 + nslabs; s += 2) {
                 const int xs = s % XS, as = s & (AS - 1);
@@ -431,8 +430,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                 }
                 tmem_wait_st();
                 tc_fence_before();
-                if (__any_sync(0xffffffffu, bad != 0)) { go = false; break; }  // nothing is published once a wait has given up
-                if (lane == 0) smem_add_release(a_count(as), 1u);
+                if ((lane == 0) & (bad == 0)) smem_add_release(a_count(as), 1u);  // nothing is published once a wait has given up
             }
             slab0 += nslabs;
         }
