@@ -47,6 +47,7 @@ constexpr uint32_t kSlabBytes = kTileTokens * 32 * 4;  // 16 KiB: [128 tokens][3
 constexpr uint32_t kWStageBytes = kImage32Bytes;       // 8 KiB: hi and lo parts interleaved
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMmaWarps = kDsdMmaWarps;
+static_assert(kMmaWarps == 4, "a row's number is its warp's number plus 0 or 4");
 constexpr int kWProducers = kMmaWarps;            // warp w loads the weight blocks of MMA warp w
 constexpr int kXProducerWarp = kWProducers;       // this warp loads activation slabs
 constexpr int kFirstMmaWarp = kXProducerWarp + 1;
@@ -285,7 +286,6 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         uint32_t pending = 0;   // bit r: a promotion of the row was requested and not yet seen taken
         uint32_t taken_ph = 0;  // bit r: parity of the next p_taken[r] phase to wait for
         int slab_base = -1;     // number (over all tiles of this CTA) of the last slab opened before this chunk
-        int cur_slab = -1;      // slab this warp has waited for
         uint32_t seq = 0;       // this warp's blocks so far: position in its weight ring
         int4 ahead = first_chunk();
         for (int tile = blockIdx.x; tile < n_tiles && !bad; tile += tile_step) {
@@ -301,8 +301,6 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                 const uint32_t drains = __ballot_sync(0xffffffffu, (mine4.w & kPlanDrain) != 0);
                 const uint32_t idle_b0 = __ballot_sync(0xffffffffu, (mine4.w & (1 << kPlanIdleShift)) != 0);
                 const uint32_t idle_b1 = __ballot_sync(0xffffffffu, (mine4.w & (2 << kPlanIdleShift)) != 0);
-                const uint32_t row_b0 = __ballot_sync(0xffffffffu, (mine4.z & 1) != 0);
-                const uint32_t row_b1 = __ballot_sync(0xffffffffu, (mine4.z & 2) != 0);
                 const uint32_t row_b2 = __ballot_sync(0xffffffffu, (mine4.z & 4) != 0);
                 uint32_t todo = __ballot_sync(0xffffffffu, (uint32_t)(mine4.z & (kMmaWarps - 1)) == mw) & valid;
                 while (todo != 0) {
@@ -315,7 +313,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                     const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
                     const uint32_t w_parity = (seq / kWRing) & 1u;
                     ++seq;
-                    const uint32_t row = ((row_b0 >> i) & 1u) | (((row_b1 >> i) & 1u) << 1) | (((row_b2 >> i) & 1u) << 2);
+                    const uint32_t row = mw | (((row_b2 >> i) & 1u) << 2);  // this warp's rows: mw and mw + 4
                     const uint32_t rbit = 1u << row;
                     const bool wlast = ((wlasts >> i) & 1u) != 0, drain = ((drains >> i) & 1u) != 0;
                     // the warp that issues a slab's last block also arrives for the warps that have none in it
@@ -334,14 +332,13 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                     }
                     // the stage counter's load travels while the weight barrier is polled
                     const uint32_t a_cnt = a_count(as), a_target = 4u * (uint32_t)(slab / AS + 1);
-                    const uint32_t seen = slab != cur_slab ? smem_load_acquire(a_cnt) : a_target;
+                    const uint32_t seen = smem_load_acquire(a_cnt);
                     wait(w_full(ws), w_parity, 1);
                     if ((int32_t)(seen - a_target) < 0) wait_count(a_cnt, a_target);
-                    cur_slab = slab;
                     // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the row) precede the MMAs
                     tc_fence_after();
                     const long long ti = tracing ? clock64() : 0;
-                    if (elect_one() && !bad) {
+                    if (elect_one() & (bad == 0)) {
                         if (kPasses == 0) {
 #pragma unroll
                             for (int s = 0; s < 2; ++s)  // k-step of 16: 8 columns (bf16 pairs) further, two k-chunks further
