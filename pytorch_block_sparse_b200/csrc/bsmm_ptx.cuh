@@ -126,6 +126,12 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int
                  ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y)
                  : "memory");
 }
+// 2-D tiled reduction smem -> global: global += smem, element type from the tensor map.
+__device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, uint32_t src, int32_t x, int32_t y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_group_read() {

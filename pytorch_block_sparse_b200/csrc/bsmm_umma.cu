@@ -60,7 +60,7 @@ constexpr int kThreads = 32 * (kFirstDrainWarp + 4);
 #endif
 constexpr int kXStages = BSMM_X_STAGES;  // even: a stage always belongs to the same split-warp group
 #ifndef BSMM_W_RING
-#define BSMM_W_RING 4
+#define BSMM_W_RING 2
 #endif
 constexpr int kWRing = BSMM_W_RING;           // weight stages per MMA warp (a ring of its own, a power of two)
 constexpr int kWStages = kMmaWarps * kWRing;
@@ -76,7 +76,8 @@ struct Cfg {
     static constexpr int kAStages = kAStagesMax >= 8 ? 8 : kAStagesMax >= 4 ? 4 : 2;  // a power of two
     static constexpr uint32_t kOffX = 0;
     static constexpr uint32_t kOffW = kOffX + kXStages * kSlabBytes;
-    static constexpr uint32_t kOffBar = kOffW + kWStages * kWStageBytes;
+    static constexpr uint32_t kOffOut = kOffW + kWStages * kWStageBytes;   // two staging tiles of the epilogue
+    static constexpr uint32_t kOffBar = kOffOut + 2 * kSlabBytes;
     static constexpr int kNumBars = 2 * kXStages + 2 * kWStages + kAStages + 2 * G;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
     static constexpr uint32_t kSmemBytes = kOffMisc + 64 + 1024;  // + slack to align the base to 1 KiB
@@ -112,7 +113,8 @@ enum TraceSlot {
 
 template <int G, int kPasses>
 __global__ void __launch_bounds__(kThreads, 1)
-dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams p) {
+dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_out,
+                     const DsdParams p) {
     using C = Cfg<G, kPasses>;
     constexpr int XS = kXStages;
     constexpr int AS = C::kAStages;
@@ -444,37 +446,63 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
         uint32_t ready_ph = 0;  // bit r: parity of the next p_ready[r] phase
         bool ok = true;
         int4 ahead = first_chunk();
+        // Row-major output: a promotion goes through a staging tile in shared memory ([128 tokens][32 columns],
+        // 128-byte swizzle) and leaves as ONE TMA store (the row's first promotion in the tile) or TMA
+        // add-reduction (later ones) issued by one thread, instead of 16 scattered 16-byte loads and stores per
+        // thread; rows beyond m are clipped by the tensor map.  Two staging tiles alternate.
+        const bool issuer = warp == kFirstDrainWarp && lane == 0;
+        uint32_t n_out = 0;          // promotions staged so far (selects the staging tile)
+        auto stage_out = [&](const float (&v)[32], int64_t col0, int32_t tok0, bool first) {
+            const uint32_t buf = smem_base + C::kOffOut + (n_out & 1u) * kSlabBytes;
+            // the tile's previous store (two promotions ago) must have read it; a reduction additionally waits
+            // until every earlier store of this thread is complete in global memory
+            if (issuer) {
+                if (!first) bulk_wait_group<0>();
+                else bulk_wait_group_read<1>();
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            uint8_t* dst = smem_gen + C::kOffOut + (n_out & 1u) * kSlabBytes + row * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (first && p.bias != nullptr) add = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+                *reinterpret_cast<float4*>(dst + ((j ^ (row & 7)) << 4)) =
+                    make_float4(v[j * 4 + 0] + add.x, v[j * 4 + 1] + add.y, v[j * 4 + 2] + add.z, v[j * 4 + 3] + add.w);
+            }
+            fence_proxy_async_smem();  // generic-proxy writes, read by the TMA through the async proxy
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (issuer) {
+                if (first) tma_store_2d(&tmap_out, buf, (int32_t)col0, tok0);
+                else tma_reduce_add_2d(&tmap_out, buf, (int32_t)col0, tok0);
+                bulk_commit_group();
+            }
+            ++n_out;
+        };
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += tile_step) {
             const int g = tile % p.groups;
             const int e0 = __ldg(p.group_off + g), e1 = __ldg(p.group_off + g + 1);
             const int nrows = min(G, p.n_out_blocks - g * G);
-            const int64_t tok = (int64_t)(tile / p.groups) * kTileTokens + row;
+            const int32_t tok0 = (tile / p.groups) * kTileTokens;
+            const int64_t tok = (int64_t)tok0 + row;
             const bool live = tok < p.m;
 
-            // v (+ bias on a row's first promotion, + previous output afterwards) -> out[tok, col0 .. col0+31]
-            auto emit = [&](int r, const float (&v)[32], bool first) {
+            // column-major output (the reference's buffer layout): direct stores
+            // v (+ bias on a row's first promotion, + previous output afterwards) -> out[col0 .. col0+31][tok]
+            auto emit_colmajor = [&](int r, const float (&v)[32], bool first) {
                 if (!live) return;
                 const int64_t col0 = ((int64_t)g * G + r) * 32;
-                if (!p.out_colmajor) {
-                    float4* dst = reinterpret_cast<float4*>(p.out + tok * p.n + col0);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (!first) add = dst[j];
-                        else if (p.bias != nullptr) add = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
-                        dst[j] = make_float4(v[j * 4 + 0] + add.x, v[j * 4 + 1] + add.y, v[j * 4 + 2] + add.z,
-                                             v[j * 4 + 3] + add.w);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float* dst = p.out + (col0 + j) * p.m + tok;
-                        float add = 0.f;
-                        if (!first) add = *dst;
-                        else if (p.bias != nullptr) add = __ldg(p.bias + col0 + j);
-                        *dst = v[j] + add;
-                    }
+                for (int j = 0; j < 32; ++j) {
+                    float* dst = p.out + (col0 + j) * p.m + tok;
+                    float add = 0.f;
+                    if (!first) add = *dst;
+                    else if (p.bias != nullptr) add = __ldg(p.bias + col0 + j);
+                    *dst = v[j] + add;
                 }
+            };
+            auto emit = [&](int r, const float (&v)[32], bool first) {
+                if (p.out_colmajor) emit_colmajor(r, v, first);
+                else stage_out(v, ((int64_t)g * G + r) * 32, tok0, first);
             };
 
             uint32_t seen = 0;      // bit r: the row has been written once in this tile
@@ -520,6 +548,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const DsdParams
                     if (!((seen >> r) & 1u)) emit(r, z, true);
             }
         }
+        if (issuer) bulk_wait_group<0>();  // the staging tiles are read until the last store has finished
         if (tracing && warp == kFirstDrainWarp && lane == 0) {
             p.trace[kTrDrainPReady] = tr[0];
             p.trace[kTrDrainTotal] = clock64() - t_role0;
@@ -555,7 +584,8 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 template <int G, int kPasses>
-cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const DsdParams& p, int64_t tiles, cudaStream_t stream) {
+cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const CUtensorMap& tmap_out, const DsdParams& p, int64_t tiles,
+                         cudaStream_t stream) {
     // per call: the attribute is per device and the caller may switch devices
     cudaError_t err = cudaFuncSetAttribute(dsd_umma_tf32_kernel<G, kPasses>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -568,7 +598,7 @@ cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const DsdParams& p, int64_t 
     if (err != cudaSuccess) return err;
     const int64_t n_tiles = (int64_t)p.groups * tiles;
     const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);  // persistent: one CTA per SM
-    dsd_umma_tf32_kernel<G, kPasses><<<grid, kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, p);
+    dsd_umma_tf32_kernel<G, kPasses><<<grid, kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, tmap_out, p);
     return cudaGetLastError();
 }
 
@@ -633,6 +663,13 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     cudaError_t err = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)k, (uint64_t)m, 32,
                                    box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess) return err;
+    // the epilogue's stores: boxes of 32 columns x up to 128 token rows of the row-major output
+    CUtensorMap tmap_out = tmap_a;
+    if (!out_colmajor) {
+        err = make_tmap_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, (uint64_t)n, (uint64_t)m, 32, box_rows,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+        if (err != cudaSuccess) return err;
+    }
 
     DsdParams p;
     p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * packed_slot_bytes(precision) : 0);
@@ -657,15 +694,15 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     if (split && group == 8) return cudaErrorInvalidValue;  // 8 rows x 64 columns leave no tensor memory for A
     if (precision == BSMM_PREC_BF16) {
         switch (group) {
-            case 4: return launch_dsd_g<4, 0>(tmap_a, p, tiles, stream);
-            case 6: return launch_dsd_g<6, 0>(tmap_a, p, tiles, stream);
-            default: return launch_dsd_g<8, 0>(tmap_a, p, tiles, stream);
+            case 4: return launch_dsd_g<4, 0>(tmap_a, tmap_out, p, tiles, stream);
+            case 6: return launch_dsd_g<6, 0>(tmap_a, tmap_out, p, tiles, stream);
+            default: return launch_dsd_g<8, 0>(tmap_a, tmap_out, p, tiles, stream);
         }
     }
     switch (group) {
-        case 4: return split ? launch_dsd_g<4, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, p, tiles, stream);
-        case 6: return split ? launch_dsd_g<6, 3>(tmap_a, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, p, tiles, stream);
-        default: return launch_dsd_g<8, 1>(tmap_a, p, tiles, stream);
+        case 4: return split ? launch_dsd_g<4, 3>(tmap_a, tmap_out, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, tmap_out, p, tiles, stream);
+        case 6: return split ? launch_dsd_g<6, 3>(tmap_a, tmap_out, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, tmap_out, p, tiles, stream);
+        default: return launch_dsd_g<8, 1>(tmap_a, tmap_out, p, tiles, stream);
     }
 }
 
