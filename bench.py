@@ -429,8 +429,8 @@ def run_gpu_arm(args, cfg):
     # DRAM bytes (read + write) of one launch of that kernel from an ncu capture of this workload; null
     # where no capture was taken (the summaries with the commands are under profiles/)
     ncu_traffic = {
-        ("c3_d0.25", "tf32x3", "wgrad_ms"): (667.8e6, "profiles/sddmm_umma_tf32x3_c3_d0.25.md"),
-        ("c3_d0.25", "tf32x3", "fwd_ms"): (648.5e6, "profiles/dsd_umma_tf32x3_c3_d0.25.md"),
+        ("c3_d0.25", "tf32x3", "wgrad_ms"): (666.8e6, "profiles/sddmm_umma_tf32x3_c3_d0.25.md"),
+        ("c3_d0.25", "tf32x3", "fwd_ms"): (624.0e6, "profiles/dsd_umma_tf32x3_c3_d0.25.md"),
     }.get((args.workload, prec_name, dom), (None, None))
     roofline = {
         "kernel": op_names[dom], "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
