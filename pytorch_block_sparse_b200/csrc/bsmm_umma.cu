@@ -7,8 +7,8 @@
 // the group has at least one block (the plan lists them, bsmm_plan.cu).  The kernel is persistent:
 // one CTA per SM walks its tiles, and every ring position runs on across tiles.
 //
-//   warps 0-3   weight producers : warp w feeds MMA warp w's own ring of kWRing stages, one 8 KiB
-//                                  linear bulk copy per block of its packed weight image
+//   warps 0-3   weight producers : warp w feeds MMA warp w's own ring of kWRing stages, one linear bulk
+//                                  copy (8 KiB, bf16: 2 KiB) per block of its packed weight image
 //   warp 4      activation producer : TMA tensor load of the [128 x 32] fp32 slab (128-byte swizzle)
 //   warps 5-8   MMA : tcgen05.mma kind::tf32, M = 128, A from tensor memory, B from smem; output row r
 //                     of the group belongs to warp r mod 4.
@@ -21,8 +21,9 @@
 //                       for 3xTF32 also lo = x - trunc_tf32(x) (the tensor core reads only the tf32
 //                       bits of an operand, so the raw slab is x_hi)
 //   warps 17-20 drain : after every kDrainEvery-th block of a row and after its last one,
-//                       tcgen05.ld the row's columns, main + correction (+ bias, or + the output
-//                       written by the row's previous promotion), 128-byte row stores to global
+//                       tcgen05.ld the row's columns, main + correction (+ bias) into a staging tile in
+//                       shared memory, which one thread sends off with a TMA store (the row's first
+//                       promotion in the tile) or a TMA add-reduction (later ones)
 //
 // Measured on an idle SM, one block costs the tensor pipe 255 clk (3xTF32) or 165 clk (single pass)
 // in this form, against 422 / 232 clk with A read from shared memory (4 KiB per instruction).
@@ -395,6 +396,9 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             for (int s = slab0 + ((group ^ slab0) & 1); s < slab0 + nslabs; s += 2) {
                 const int xs = s % XS, as = s & (AS - 1);
                 wait(x_full(xs), (uint32_t)(s / XS) & 1u, 0);
+                // the test of the tensor-memory stage's release travels while the slab is read and split
+                const uint32_t a_parity = ((uint32_t)(s / AS) & 1u) ^ 1u;
+                const bool a_free = mbar_test_wait(a_empty(as), a_parity);
                 uint32_t hi[32], lo[32];
                 {
                     const uint8_t* xrow = smem_gen + C::kOffX + xs * kSlabBytes + row * 128;
@@ -412,7 +416,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     }
                 }
                 mbar_arrive(x_empty(xs));
-                wait(a_empty(as), ((uint32_t)(s / AS) & 1u) ^ 1u, 1);
+                if (!a_free) wait(a_empty(as), a_parity, 1);
                 tc_fence_after();
                 const uint32_t a_hi = tmem_lane + C::kAccCols + as * C::kAStageCols;
                 if (kPasses == 0) {
