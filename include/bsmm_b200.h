@@ -82,7 +82,7 @@ int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* 
 
 /*
  * Per-pattern launch plan of the tensor-core dsd kernel: for every group of `group`
- * consecutive output block-rows (group = 4, 6 or 8: the kernel's tile is 128 tokens x group*32
+ * consecutive output block-rows (group = 4, 5, 6 or 8; 5 with BSMM_PREC_TF32X3 only, 8 not with it: the kernel's tile is 128 tokens x group*32
  * columns), the group's index entries re-ordered by (inner block index, row-in-group), with the
  * points at which the kernel promotes its tensor-memory partial sums.  `plan` must hold
  * bsmm_plan_bytes(n_out_blocks, nnz, group) bytes, 16-byte aligned.  Depends only on ptr/idx

@@ -122,7 +122,8 @@ int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int3
                                                      static_cast<float*>(out), bias, dgrad, colmajor, s));
         const int group = (int)((flags >> 8) & 0xFFu);
         if (packed == nullptr || plan == nullptr || !aligned(packed, 256) || !aligned(plan, 16) ||
-            !bsmm::plan_group_valid(group) || (group == 8 && precision == BSMM_PREC_TF32X3))
+            !bsmm::plan_group_valid(group) || (group == 8 && precision == BSMM_PREC_TF32X3) ||
+            (group == 5 && precision != BSMM_PREC_TF32X3))
             return BSMM_ERR_INVALID_ARGUMENT;
         return cuda_status(bsmm::launch_dsd_umma(a, m, k, nnz, packed, plan, group, n, out, bias, precision, dgrad,
                                                  colmajor, s));

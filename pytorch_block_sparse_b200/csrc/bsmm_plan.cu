@@ -1,6 +1,6 @@
 // Launch-plan builder for the tensor-core dsd kernel.
 //
-// The kernel owns a tile of 128 tokens x `group` (4, 6 or 8) output block-rows and walks the
+// The kernel owns a tile of 128 tokens x `group` (4, 5, 6 or 8) output block-rows and walks the
 // contraction axis one 32-wide activation slab at a time, so it wants the group's blocks merged
 // across its rows and ordered by slab.  The CSR/CSC arrays of the reference
 // (block_sparse.py:85-153) list each row's blocks in ascending inner index; the merged position of

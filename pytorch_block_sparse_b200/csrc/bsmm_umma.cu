@@ -53,13 +53,7 @@ constexpr int kWProducers = kMmaWarps;            // warp w loads the weight blo
 constexpr int kXProducerWarp = kWProducers;       // this warp loads activation slabs
 constexpr int kFirstMmaWarp = kXProducerWarp + 1;
 constexpr int kFirstSplitWarp = kFirstMmaWarp + kMmaWarps;
-constexpr int kSplitWarps = 8;                    // two groups of four, taking alternate slabs
-constexpr int kFirstDrainWarp = kFirstSplitWarp + kSplitWarps;
-constexpr int kThreads = 32 * (kFirstDrainWarp + 4);
-#ifndef BSMM_X_STAGES
-#define BSMM_X_STAGES 4
-#endif
-constexpr int kXStages = BSMM_X_STAGES;  // even: a stage always belongs to the same split-warp group
+// then the split warps (Cfg::kSplitGroups groups of four) and four drain warps
 #ifndef BSMM_W_RING
 #define BSMM_W_RING 2
 #endif
@@ -74,7 +68,14 @@ struct Cfg {
     static constexpr uint32_t kWBytes = kPasses == 0 ? kImage16Bytes : kImage32Bytes;    // one block's image
     static constexpr uint32_t kAccCols = G * kRowCols;
     static constexpr int kAStagesMax = (int)((kTmemCols - kAccCols) / kAStageCols);
-    static constexpr int kAStages = kAStagesMax >= 8 ? 8 : kAStagesMax >= 4 ? 4 : 2;  // a power of two
+    static constexpr int kAStages = kAStagesMax >= 8 ? 8 : kAStagesMax >= 4 ? 4 : kAStagesMax;  // 8, 4, 3 or 2
+    // Split-warp groups take slabs round-robin; a ring stage must always meet the same group, so the stage
+    // counts are multiples of the group count.  Three stages get three groups: one stage each.
+    static constexpr int kSplitGroups = kAStages % 3 == 0 ? 3 : 2;
+    static constexpr int kXStages = 2 * kSplitGroups;
+    static constexpr int kFirstDrainWarp = kFirstSplitWarp + 4 * kSplitGroups;
+    static constexpr int kThreads = 32 * (kFirstDrainWarp + 4);
+    static_assert(kAStages % kSplitGroups == 0, "a ring stage must stay with one split-warp group");
     static constexpr uint32_t kOffX = 0;
     static constexpr uint32_t kOffW = kOffX + kXStages * kSlabBytes;
     static constexpr uint32_t kOffOut = kOffW + kWStages * kWStageBytes;   // two staging tiles of the epilogue
@@ -113,11 +114,13 @@ enum TraceSlot {
 };
 
 template <int G, int kPasses>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((Cfg<G, kPasses>::kThreads), 1)
 dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_out,
                      const DsdParams p) {
     using C = Cfg<G, kPasses>;
-    constexpr int XS = kXStages;
+    constexpr int XS = C::kXStages;
+    constexpr int kFirstDrainWarp = C::kFirstDrainWarp;
+    constexpr int kSplitGroups = C::kSplitGroups;
     constexpr int AS = C::kAStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -312,7 +315,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     // everything that does not depend on the operands' arrival first: the time from a slab's
                     // publication to this warp's commit is part of the stage's recycle time
                     const int slab = slab_base + __popc(firsts & (0xffffffffu >> (31 - i)));
-                    const int as = slab & (AS - 1);
+                    const int as = slab % AS;
                     const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
                     const uint32_t w_parity = (seq / kWRing) & 1u;
                     ++seq;
@@ -389,12 +392,13 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int group = (warp - kFirstSplitWarp) >> 2;
         const int row = quarter * 32 + lane;    // token inside the tile = tensor-memory lane
         const uint32_t tmem_lane = tmem + ((uint32_t)(quarter * 32) << 16);
-        static_assert(XS % 2 == 0 && AS % 2 == 0, "a ring stage must stay with one split-warp group");
+        static_assert(XS % kSplitGroups == 0 && AS % kSplitGroups == 0, "a ring stage must stay with one split-warp group");
         int slab0 = 0;  // slabs of this CTA's earlier tiles
         for (int tile = blockIdx.x; tile < n_tiles && !__any_sync(0xffffffffu, bad != 0); tile += tile_step) {
             const int nslabs = __ldg(p.group_slabs + tile % p.groups);
-            for (int s = slab0 + ((group ^ slab0) & 1); s < slab0 + nslabs; s += 2) {
-                const int xs = s % XS, as = s & (AS - 1);
+            // this group's slabs: s = group (mod kSplitGroups), counted over all tiles of the CTA
+            for (int s = slab0 + (group + kSplitGroups - slab0 % kSplitGroups) % kSplitGroups; s < slab0 + nslabs; s += kSplitGroups) {
+                const int xs = s % XS, as = s % AS;
                 wait(x_full(xs), (uint32_t)(s / XS) & 1u, 0);
                 // the test of the tensor-memory stage's release travels while the slab is read and split
                 const uint32_t a_parity = ((uint32_t)(s / AS) & 1u) ^ 1u;
@@ -602,7 +606,7 @@ cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const CUtensorMap& tmap_out,
     if (err != cudaSuccess) return err;
     const int64_t n_tiles = (int64_t)p.groups * tiles;
     const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);  // persistent: one CTA per SM
-    dsd_umma_tf32_kernel<G, kPasses><<<grid, kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, tmap_out, p);
+    dsd_umma_tf32_kernel<G, kPasses><<<grid, Cfg<G, kPasses>::kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, tmap_out, p);
     return cudaGetLastError();
 }
 
@@ -697,12 +701,14 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     const bool split = precision == BSMM_PREC_TF32X3;
     if (split && group == 8) return cudaErrorInvalidValue;  // 8 rows x 64 columns leave no tensor memory for A
     if (precision == BSMM_PREC_BF16) {
+        if (group == 5) return cudaErrorInvalidValue;  // the 5-row tile exists for 3xTF32 only
         switch (group) {
             case 4: return launch_dsd_g<4, 0>(tmap_a, tmap_out, p, tiles, stream);
             case 6: return launch_dsd_g<6, 0>(tmap_a, tmap_out, p, tiles, stream);
             default: return launch_dsd_g<8, 0>(tmap_a, tmap_out, p, tiles, stream);
         }
     }
+    if (group == 5) return split ? launch_dsd_g<5, 3>(tmap_a, tmap_out, p, tiles, stream) : cudaErrorInvalidValue;
     switch (group) {
         case 4: return split ? launch_dsd_g<4, 3>(tmap_a, tmap_out, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, tmap_out, p, tiles, stream);
         case 6: return split ? launch_dsd_g<6, 3>(tmap_a, tmap_out, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, tmap_out, p, tiles, stream);

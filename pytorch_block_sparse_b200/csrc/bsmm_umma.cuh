@@ -29,7 +29,7 @@ constexpr int kPlanIdleShift = 4;     // on the slab's last entry, 2 bits: MMA w
 // small correction terms, so 32 blocks cost 128 accumulations of the main term: about 3e-6.
 constexpr int kDrainEvery = 32;
 
-inline bool plan_group_valid(int group) { return group == 4 || group == 6 || group == 8; }
+inline bool plan_group_valid(int group) { return group == 4 || group == 5 || group == 6 || group == 8; }
 
 // Plan buffer: [group offsets: n_groups + 1 int32][slabs per group: n_groups int32][pad to 16 B]
 //              [entries: nnz PlanEntry]

@@ -219,7 +219,7 @@ def test_pack_statistic_matches_block_norm():
         assert np.allclose(got, want, rtol=1e-5)
 
 
-@pytest.mark.parametrize("group", [4, 6, 8])
+@pytest.mark.parametrize("group", [4, 5, 6, 8])
 def test_plan_is_the_group_merge_of_the_csr(group):
     m = make_matrix((512, 2048), n_blocks=700, seed=8)  # rows of ~44 blocks: promotions inside a row
     plan = m._plan(True)
@@ -287,7 +287,7 @@ def test_single_pass_tf32_wgrad():
     assert_device_healthy()
 
 
-@pytest.mark.parametrize("group", ["4", "6", "8"])
+@pytest.mark.parametrize("group", ["4", "5", "6", "8"])
 def test_dsd_every_tile_width(group, monkeypatch):
     monkeypatch.setenv("BSMM_PLAN_GROUP", group)
     m = make_matrix((416, 352), n_blocks=70, seed=21)  # 13 x 11 blocks: ragged last group for every width
