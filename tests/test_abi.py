@@ -42,7 +42,7 @@ def test_size_queries():
     assert lib.bsmm_packed_bytes(-1, native.PREC_TF32X3) == -1
     assert lib.bsmm_plan_bytes(16, 100, 8) == 32 + 100 * 16
     assert lib.bsmm_plan_bytes(16, 100, 4) == 48 + 100 * 16
-    assert lib.bsmm_plan_bytes(16, 100, 5) == -1
+    assert lib.bsmm_plan_bytes(16, 100, 7) == -1
     assert lib.bsmm_plan_group(16384, 128, 4096, native.PREC_TF32) == 8
     assert lib.bsmm_plan_group(16384, 128, 4096, native.PREC_TF32X3) == 4  # many waves: four activation stages
     assert lib.bsmm_plan_group(4096, 96, 2304, native.PREC_TF32X3) == 6
