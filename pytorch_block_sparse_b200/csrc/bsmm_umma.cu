@@ -460,7 +460,10 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         // thread; rows beyond m are clipped by the tensor map.  Two staging tiles alternate.
         const bool issuer = warp == kFirstDrainWarp && lane == 0;
         uint32_t n_out = 0;          // promotions staged so far (selects the staging tile)
-        auto stage_out = [&](const float (&v)[32], int64_t col0, int32_t tok0, bool first) {
+        // Returns false, to all four warps alike, when a thread of any of them has given up on a wait: the
+        // first barrier carries that vote, so that the warps leave their loops together and none is left
+        // behind at a barrier.
+        auto stage_out = [&](const float (&v)[32], int64_t col0, int32_t tok0, bool first) -> bool {
             const uint32_t buf = smem_base + C::kOffOut + (n_out & 1u) * kSlabBytes;
             // the tile's previous store (two promotions ago) must have read it; a reduction additionally waits
             // until every earlier store of this thread is complete in global memory
@@ -468,7 +471,14 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 if (!first) bulk_wait_group<0>();
                 else bulk_wait_group_read<1>();
             }
-            asm volatile("bar.sync 2, 128;" ::: "memory");
+            uint32_t any_bad;
+            asm volatile(
+                "{\n\t.reg .pred q, r;\n\t"
+                "setp.ne.u32 q, %1, 0;\n\t"
+                "bar.red.or.pred r, 2, 128, q;\n\t"
+                "selp.u32 %0, 1, 0, r;\n\t}"
+                : "=r"(any_bad) : "r"(bad) : "memory");
+            if (any_bad) return false;
             uint8_t* dst = smem_gen + C::kOffOut + (n_out & 1u) * kSlabBytes + row * 128;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -485,6 +495,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 bulk_commit_group();
             }
             ++n_out;
+            return true;
         };
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += tile_step) {
             const int g = tile % p.groups;
@@ -508,9 +519,13 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     *dst = v[j] + add;
                 }
             };
-            auto emit = [&](int r, const float (&v)[32], bool first) {
-                if (p.out_colmajor) emit_colmajor(r, v, first);
-                else stage_out(v, ((int64_t)g * G + r) * 32, tok0, first);
+            auto emit = [&](int r, const float (&v)[32], bool first) -> bool {
+                if (p.out_colmajor) {
+                    if (__any_sync(0xffffffffu, bad != 0)) return false;
+                    emit_colmajor(r, v, first);
+                    return true;
+                }
+                return stage_out(v, ((int64_t)g * G + r) * 32, tok0, first);
             };
 
             uint32_t seen = 0;      // bit r: the row has been written once in this tile
@@ -522,9 +537,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     const int i = __ffs(drains) - 1;
                     drains &= drains - 1;
                     const int r = __shfl_sync(0xffffffffu, mine.z, i);
-                    wait(p_ready(r), (ready_ph >> r) & 1u, 0);
-                    ok = !__any_sync(0xffffffffu, bad != 0);
-                    if (!ok) break;
+                    wait(p_ready(r), (ready_ph >> r) & 1u, 0);  // (a wait that gave up is noticed in emit)
                     ready_ph ^= 1u << r;
                     tc_fence_after();
                     uint32_t main_[32];
@@ -543,7 +556,8 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     }
                     tc_fence_before();
                     mbar_arrive(p_taken(r));
-                    emit(r, v, !((seen >> r) & 1u));
+                    ok = emit(r, v, !((seen >> r) & 1u));
+                    if (!ok) break;
                     seen |= 1u << r;
                 }
             }
@@ -552,8 +566,8 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 float z[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) z[j] = 0.f;
-                for (int r = 0; r < nrows; ++r)
-                    if (!((seen >> r) & 1u)) emit(r, z, true);
+                for (int r = 0; r < nrows && ok; ++r)
+                    if (!((seen >> r) & 1u)) ok = emit(r, z, true);
             }
         }
         if (issuer) bulk_wait_group<0>();  // the staging tiles are read until the last store has finished
