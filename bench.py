@@ -27,7 +27,7 @@ if ROOT not in sys.path:
 METRIC = "block_sparse_linear_fwd_bwd_effective_tflops"
 UNIT = "TFLOP/s"
 
-# BASELINE configs that are single-layer workloads (tokens M, out N, in K, density)
+# single-layer workloads of the benchmark configurations (tokens M, out N, in K, density)
 WORKLOADS = {
     "c3_d0.25": dict(m=16384, n=4096, k=4096, density=0.25),  # headline: density sweep, d = 0.25
     "c3_d0.10": dict(m=16384, n=4096, k=4096, density=0.10),

@@ -11,7 +11,7 @@ It imports ``pytorch_block_sparse`` (the reference), builds matrices with its ow
 * ``block_replace`` results                                       -> replace.npz
 * ``to_dense`` / ``from_dense`` values                             -> dense.npz
 * fwd / dgrad / wgrad of the reference's ``to_dense`` + ``torch.matmul`` path
-  (a small case in full, BASELINE config 1 as a strided sample)   -> linear.npz
+  (a small case in full, benchmark configuration 1 as a strided sample)   -> linear.npz
 
 The committed .npz files are what the tests read; the reference is not needed to run them.
 """
@@ -147,7 +147,7 @@ def gen_linear():
     out["small/dx"] = dx.detach().numpy()
     out["small/dw"] = dw.numpy()
 
-    # BASELINE config 1: inputs re-derived from the seed by the test (hash recorded), outputs sampled
+    # benchmark configuration 1: inputs re-derived from the seed by the test (hash recorded), outputs sampled
     np.random.seed(1)
     torch.manual_seed(1)
     m = BSM.zeros((256, 1024), n_blocks=128, device="cpu")

@@ -134,7 +134,7 @@ def test_golden_small_case_of_the_reference(precision, golden):
 
 
 def test_config1_sampled_golden(golden):
-    """BASELINE config 1 (X [256,1024], W 256x1024 density 0.5): inputs re-derived from the seed,
+    """Benchmark configuration 1 (X [256,1024], W 256x1024 density 0.5): inputs re-derived from the seed,
     outputs compared with the strided sample recorded from the reference."""
     import hashlib
 
@@ -357,7 +357,7 @@ def _rel_fro_gpu(got, want):
 
 @pytest.mark.parametrize("precision", ["tf32x3", "tf32", "bf16"])
 def test_full_size_config3(precision):
-    """BASELINE config 3 at density 0.25 in full (4096 x 4096, 4096 blocks, 16384 tokens): every persistent
+    """Benchmark configuration 3 at density 0.25 in full (4096 x 4096, 4096 blocks, 16384 tokens): every persistent
     CTA walks ~28 tiles.  The numpy oracle is too slow for the whole problem, so the tensor-core kernels are
     compared (a) with the exact-fp32 CUDA-core kernels on the device, which the small cases pin to the
     oracle, (b) with the oracle on a sample of 96 token rows / 8 blocks, and (c) through properties that do
