@@ -54,10 +54,7 @@ constexpr int kXProducerWarp = kWProducers;       // this warp loads activation 
 constexpr int kFirstMmaWarp = kXProducerWarp + 1;
 constexpr int kFirstSplitWarp = kFirstMmaWarp + kMmaWarps;
 // then the split warps (Cfg::kSplitGroups groups of four) and four drain warps
-#ifndef BSMM_W_RING
-#define BSMM_W_RING 2
-#endif
-constexpr int kWRing = BSMM_W_RING;           // weight stages per MMA warp (a ring of its own, a power of two)
+constexpr int kWRing = 2;  // weight stages per MMA warp (a ring of its own, a power of two); 4 measured no faster
 constexpr int kWStages = kMmaWarps * kWRing;
 
 template <int G, int kPasses>
