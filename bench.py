@@ -36,6 +36,8 @@ WORKLOADS = {
     "c2_up": dict(m=4096, n=3072, k=768, density=0.5),  # RoBERTa-base FFN 768 -> 3072
     "c2_down": dict(m=4096, n=768, k=3072, density=0.5),  # RoBERTa-base FFN 3072 -> 768
     "c1": dict(m=256, n=256, k=1024, density=0.5),  # the reference's CPU-runnable case
+    # one GPU's block-row shard of the large column-parallel layer (65536 tokens, 32768 x 8192 at density 0.1, 8 GPUs)
+    "c5_shard": dict(m=65536, n=4096, k=8192, density=0.1),
 }
 
 
