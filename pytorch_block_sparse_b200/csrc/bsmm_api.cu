@@ -14,6 +14,11 @@ int cuda_status(cudaError_t err) {
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// The launchers report cudaGetLastError() after their launches.  A non-sticky error left behind by an
+// earlier runtime call of the host program (its own probing of pointers, for instance) would be blamed on
+// them, so every entry point that launches starts from a clean error state.
+void forget_earlier_errors() { (void)cudaGetLastError(); }
+
 }  // namespace
 
 extern "C" {
@@ -99,6 +104,7 @@ int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks
 int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
              const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
              uint32_t flags, bsmm_stream_t stream) {
+    forget_earlier_errors();
     const uint32_t precision = flags & BSMM_PREC_MASK;
     const bool dgrad = (flags & BSMM_DSD_DGRAD) != 0;
     const bool colmajor = (flags & BSMM_DSD_OUT_COLMAJOR) != 0;
@@ -154,6 +160,7 @@ int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, i
 int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens, float* sparse_c,
                const int32_t* blocks, int64_t nnz, const int32_t* csr_idx, const void* plan, float* block_sumsq,
                void* workspace, uint32_t flags, bsmm_stream_t stream) {
+    forget_earlier_errors();
     const uint32_t precision = flags & BSMM_PREC_MASK;
     const bool a_col = (flags & BSMM_SDDMM_A_COLMAJOR) != 0;
     const bool b_col = (flags & BSMM_SDDMM_B_COLMAJOR) != 0;

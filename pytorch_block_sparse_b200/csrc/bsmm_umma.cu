@@ -636,6 +636,13 @@ cudaError_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t e
                          CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return cudaErrorNotSupported;
+    // The encoder is a driver entry point and wants a current context.  A thread that has made no runtime call
+    // needing one yet (autograd's backward thread when the allocator serves everything from its cache) has none:
+    // bind the runtime's context of the current device to it.
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err == cudaSuccess) err = cudaSetDevice(dev);
+    if (err != cudaSuccess) return err;
     const cuuint64_t dims[2] = {inner, outer};
     const cuuint64_t strides[1] = {inner * elem_bytes};
     const cuuint32_t box[2] = {box_inner, box_outer};

@@ -166,3 +166,43 @@ def test_nonsquare_block_shape_uses_emulator():
     y = lin(x)
     y.sum().backward()
     assert torch.allclose(y, x @ lin.weight.to_dense().t() + lin.bias, atol=1e-5)
+
+
+def test_backward_thread_without_a_cuda_context():
+    """The tensor maps are encoded by a driver entry point that needs a current context.  Autograd runs
+    backward in a thread of its own; when the caching allocator serves all of that thread's allocations
+    from memory freed earlier, the kernels' launcher is the first thing in the thread that needs the
+    context.  Needs a fresh process: the backward thread lives as long as the process."""
+    import subprocess
+    import sys
+
+    script = r'''
+import numpy as np, torch
+from pytorch_block_sparse_b200 import BlockSparseLinear
+np.random.seed(0); torch.manual_seed(0)
+lin = BlockSparseLinear(1024, 256, bias=True, density=0.5)
+x = torch.randn(256, 1024, device="cuda"); dy = torch.randn(256, 256, device="cuda")
+# the same computations in the main thread first: afterwards the allocator's cache holds every size that
+# backward will ask for, and the backward thread makes no runtime call of its own before the launcher
+w, b = lin.weight, lin.bias.detach()
+for _ in range(3):
+    y = w.reverse_matmul(x, transpose=True, bias=b)
+    dx = w.reverse_matmul(dy, transpose=False)
+    dw = w.matmul_with_output_sparse_support(dy, x)
+    db = dy.sum(0)
+    del y, dx, dw, db
+torch.cuda.synchronize()
+xd = x.detach().requires_grad_(True)
+out = lin(xd)
+out.backward(dy)
+torch.cuda.synchronize()
+assert torch.isfinite(xd.grad).all() and torch.isfinite(lin.weight.data.grad).all()
+print("backward ok")
+'''
+    import os
+
+    env = dict(os.environ)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    res = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=300)
+    assert res.returncode == 0 and "backward ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
