@@ -206,3 +206,37 @@ print("backward ok")
     env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
     res = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=300)
     assert res.returncode == 0 and "backward ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+def test_kernels_run_on_the_callers_stream():
+    """Forward and backward issued under a side stream are ordered with that stream's work (the reference
+    launches on the legacy default stream whatever the caller's stream is)."""
+    import numpy as np
+
+    from pytorch_block_sparse_b200 import BlockSparseLinear
+
+    np.random.seed(3)
+    torch.manual_seed(3)
+    lin = BlockSparseLinear(384, 256, bias=True, density=0.4)
+    x = torch.randn(700, 384, device="cuda")
+    dy = torch.randn(700, 256, device="cuda")
+    xr = x.clone().requires_grad_(True)
+    lin(xr).backward(dy)
+    want = (xr.grad.clone(), lin.weight.data.grad.clone())
+    lin.weight.data.grad = None
+    torch.cuda.synchronize()
+
+    side = torch.cuda.Stream()
+    big = torch.empty(64 << 20, device="cuda")
+    with torch.cuda.stream(side):
+        # a long fill first: the input written after it is only complete when the stream reaches our kernels
+        for _ in range(4):
+            big.normal_()
+        xs = torch.zeros_like(x)
+        xs.copy_(x)
+        xs.requires_grad_(True)
+        y = lin(xs)
+        y.backward(dy)
+    side.synchronize()
+    assert torch.equal(xs.grad, want[0])
+    assert torch.allclose(lin.weight.data.grad, want[1], rtol=1e-5, atol=1e-6)
