@@ -62,9 +62,11 @@ int bsmm_last_cuda_error(void);
  */
 int bsmm_device_status(unsigned int* status, int clear);
 /*
- * Diagnostics, no counterpart in the reference: while `device_buffer` (32 int64 on the device) is set,
- * every tensor-core bsmm_dsd launch records for its CTA number `block` how many cycles each warp role
- * (producer, MMA issuer, transform, drain) spent in each of its waits, and each role's total.
+ * Diagnostics, no counterpart in the reference.  Effective only in a library built with -DBSMM_TRACE (the
+ * shipped build compiles the tracing out of the kernels' control loops; the call then only stores the
+ * pointer): while `device_buffer` (32 int64 on the device) is set, every tensor-core bsmm_dsd launch records
+ * for its CTA number `block` how many cycles each warp role (weight / activation producers, MMA issuers,
+ * split warps, drain warps) spent in each of its waits, and each role's total.
  * NULL switches tracing off.  Process-wide, not thread-safe.
  */
 int bsmm_debug_trace_dsd(void* device_buffer, int block);
@@ -118,14 +120,14 @@ int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int3
  * rows/cols multiples of 32, tokens free.  sparse_c fp32 [nnz*32, 32] is overwritten (beta = 0).
  * `block_sumsq` (fp32 [nnz], may be NULL) receives sum(sparse_c[s]^2).
  *
- * The tensor-core kernel (BSMM_PREC_TF32X3, row-major fp32 operands, at least 32 tokens) walks the
- * matrix by block-rows and therefore also wants the CSR index array `csr_idx` (cols_a) and the
- * item table bsmm_build_sddmm_plan makes from the CSR offsets (row_start_ends_a); `plan` must hold
- * bsmm_sddmm_plan_bytes(n_block_rows, nnz) bytes, 16-byte aligned, and depends only on the pattern.
+ * The tensor-core kernel (BSMM_PREC_TF32X3, BSMM_PREC_TF32 or BSMM_PREC_BF16; row-major fp32 operands, at
+ * least 32 tokens) walks the matrix by block-rows and therefore also wants the CSR index array `csr_idx`
+ * (cols_a) and the item table bsmm_build_sddmm_plan makes from the CSR offsets (row_start_ends_a); `plan`
+ * must hold bsmm_sddmm_plan_bytes(n_block_rows, nnz) bytes, 16-byte aligned, and depends only on the pattern.
  * When the token axis is split over several CTAs the partial results go through `workspace`
  * (bsmm_sddmm_workspace_bytes(...) bytes, 16-byte aligned) and are summed in a fixed order.
- * With csr_idx or plan NULL, or for shapes that kernel does not take, the CUDA-core kernel runs
- * (same fp32-class result).
+ * With csr_idx or plan NULL, or for shapes that kernel does not take, the exact-fp32 CUDA-core kernel runs
+ * instead, whatever tensor-core precision was asked for (its result is at least as accurate).
  */
 int64_t bsmm_sddmm_plan_bytes(int64_t n_block_rows, int64_t nnz);
 int bsmm_build_sddmm_plan(const int32_t* ptr, int64_t n_block_rows, int64_t nnz, void* plan, bsmm_stream_t stream);
