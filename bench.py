@@ -1,20 +1,28 @@
 """Benchmark of the block-sparse Linear hot path (pack + fwd + dgrad + wgrad of one layer).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--precision P]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--precision P] [--legs sweep,c5,c4]
     python bench.py --impl reference ...      # the reference's CPU path (to_dense + matmul) on host cores
 
 One step = one pass of the hot path over one batch of synthetic activations:
 weight packing (the per-step replacement of the reference's transposed weight copy), forward
-y = x W^T + b, dgrad dx = dy W and the sparse-output wgrad.  With N > 1 ranks the layer runs
-token-data-parallel (every rank its own tokens, same weights) and the step ends with an NCCL
-all-reduce of the nnz-block gradient buffer.  Prints ONE JSON line on rank 0.
+y = x W^T + b, the sparse-output wgrad and dgrad dx = dy W.  With N > 1 ranks the layer runs
+token-data-parallel (every rank its own tokens, same weights): the NCCL all-reduce of the nnz-block gradient
+buffer runs on a side stream while dgrad computes.  Prints ONE JSON line on rank 0.
 
 metric = effective TFLOP/s = 3 * (2 * M * nnz * 1024) FLOP per step / time, the work of the
 non-zero blocks only (extra tensor-core passes of the 3xTF32 split and padding do not count).
+
+Extra legs in the same line (each timed after the headline region, never inside it):
+  sweep  ms per step of the other benchmark configurations and precisions on this GPU
+  c5     the large column-parallel layer (32768 x 8192, density 0.1, 65536 tokens) sharded by block-rows over the
+         N ranks, strong scaling: compute alone and with the output all-gather + input-gradient all-reduce
+  c4     RoBERTa-base (12 layers) patched by BlockSparseModelPatcher at density 0.5, MLM loss, AdamW,
+         token-data-parallel over the N ranks: training tokens/s beside the dense model
 """
 import argparse
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -39,6 +47,10 @@ WORKLOADS = {
     # one GPU's block-row shard of the large column-parallel layer (65536 tokens, 32768 x 8192 at density 0.1, 8 GPUs)
     "c5_shard": dict(m=65536, n=4096, k=8192, density=0.1),
 }
+C5 = dict(m=65536, n=32768, k=8192, density=0.1)
+# what the sweep leg times beside the headline (workload, precision)
+SWEEP = [("c3_d0.25", "tf32"), ("c3_d0.25", "bf16"), ("c3_d0.10", "tf32x3"), ("c3_d0.50", "tf32x3"),
+         ("c3_d0.75", "tf32x3"), ("c2_up", "tf32x3"), ("c2_down", "tf32x3")]
 
 
 def nnz_of(cfg):
@@ -56,6 +68,17 @@ def measured_peaks():
             p = json.load(f)
         return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], bf16_tflops_sustained=p["bf16_tflops_sustained"], source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def profile_traffic(kernel, precision, workload):
+    """DRAM read + write bytes of one launch of `kernel`, from the committed ncu summary of that kernel, precision
+    and workload (a line `traffic_bytes_per_launch: <number>`); (None, None) where no capture was taken."""
+    path = os.path.join(ROOT, "profiles", "%s_%s_%s.md" % (kernel, precision, workload))
+    if not os.path.exists(path):
+        return None, None
+    with open(path) as f:
+        m = re.search(r"traffic_bytes_per_launch\s*:\s*([0-9.eE+]+)", f.read())
+    return (float(m.group(1)), os.path.relpath(path, ROOT)) if m else (None, None)
 
 
 # --------------------------------------------------------------------------- clocks
@@ -118,16 +141,61 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU reference path
+def reference_package():
+    """The unmodified reference package when it was pip-installed into the git-ignored baseline/_ref, else None."""
+    site = os.environ.get("BSMM_REFERENCE_SITE", os.path.join(ROOT, "baseline", "_ref"))
+    if not os.path.isdir(os.path.join(site, "pytorch_block_sparse")):
+        return None
+    sys.path.insert(0, site)
+    try:
+        import pytorch_block_sparse as ref
+    except Exception:
+        return None
+    finally:
+        sys.path.remove(site)
+    return ref
+
+
 def cpu_reference_step(cfg, sample_m, seed=0):
-    """Build the seeded sample once; return a callable running fwd+dgrad+wgrad the way the reference's
-    CPU path does (to_dense + matmul in fp32), restated in numpy by the oracle."""
+    """Build the seeded sample once; return (step, kind).  `step` runs fwd + dgrad + wgrad the way the
+    reference's CPU path does: BlockSparseMatrix.to_dense() followed by fp32 matmuls, the weight gradient masked
+    to the stored blocks.  kind "reference": the reference's own classes and torch.matmul on all host cores;
+    kind "port": the numpy restatement under oracle/ (where the reference package is not installed)."""
     import numpy as np
+
+    cores = os.cpu_count() or 1
+    shape = (cfg["n"], cfg["k"])
+    ref = reference_package()
+    if ref is not None:
+        import torch
+
+        torch.set_num_threads(cores)
+        np.random.seed(seed)
+        torch.manual_seed(seed)
+        w = ref.BlockSparseMatrix.zeros(shape, n_blocks=nnz_of(cfg), device="cpu")
+        with torch.no_grad():
+            w.data.normal_(0, 0.02)
+        x = torch.randn(sample_m, cfg["k"])
+        dy = torch.randn(sample_m, cfg["n"])
+        bias = torch.randn(cfg["n"]) * 0.02
+        ones = torch.ones_like(w.data)
+
+        def step():
+            with torch.no_grad():
+                y = x @ w.to_dense().t() + bias
+                dx = dy @ w.to_dense()
+                dw = (dy.t() @ x) * w.to_dense(data_replace=ones)
+            return y, dx, dw
+
+        return step, "reference"
+
+    from threadpoolctl import threadpool_limits
 
     from oracle import block_sparse_oracle as orc
 
+    threadpool_limits(limits=cores)
     rng = np.random.RandomState(seed)
     np.random.seed(seed)
-    shape = (cfg["n"], cfg["k"])
     mask = orc.random_mask(shape, nnz_of(cfg))
     idx = orc.build_indices(mask)
     data = (rng.standard_normal((nnz_of(cfg) * 32, 32)) * 0.02).astype(np.float32)
@@ -141,21 +209,25 @@ def cpu_reference_step(cfg, sample_m, seed=0):
         dw = orc.wgrad(dy, x, shape, idx["blocks"], dtype=np.float32)
         return y, dx, dw
 
-    return step
+    return step, "port"
+
+
+def sized_cpu_sample(cfg, seconds_per_step):
+    """A token count whose CPU step takes about `seconds_per_step` (a probe on 256 tokens sets the rate)."""
+    probe_m = min(cfg["m"], 256)
+    step, _ = cpu_reference_step(cfg, probe_m)
+    step()
+    t0 = time.perf_counter()
+    step()
+    per_token = max((time.perf_counter() - t0) / probe_m, 1e-9)
+    sample_m = int(min(cfg["m"], max(probe_m, seconds_per_step / per_token)))
+    return max(32, sample_m // 32 * 32)
 
 
 def time_cpu_reference(cfg, target_seconds, reps):
     """Effective TFLOP/s of the CPU path on a bounded token sample sized for ~target_seconds."""
-    probe_m = min(cfg["m"], 256)
-    step = cpu_reference_step(cfg, probe_m)
-    step()
-    t0 = time.perf_counter()
-    step()
-    probe = time.perf_counter() - t0
-    per_token = max(probe / probe_m, 1e-9)
-    sample_m = int(min(cfg["m"], max(probe_m, target_seconds / reps / per_token)))
-    sample_m = max(32, sample_m // 32 * 32)
-    step = cpu_reference_step(cfg, sample_m)
+    sample_m = sized_cpu_sample(cfg, target_seconds / reps)
+    step, kind = cpu_reference_step(cfg, sample_m)
     step()
     times = []
     for _ in range(reps):
@@ -165,24 +237,21 @@ def time_cpu_reference(cfg, target_seconds, reps):
     times.sort()
     med = times[len(times) // 2]
     value = 3 * 2.0 * sample_m * nnz_of(cfg) * 1024 / med / 1e12
-    return value, sample_m, med
+    return value, sample_m, kind
 
 
 def run_reference_arm(args, cfg):
+    """The reference's own CPU implementation of the path on the host cores.  It has no multi-GPU form: under
+    torchrun rank 0 alone runs it (with every host core, whatever OMP_NUM_THREADS the launcher exported)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    probe_m = min(cfg["m"], 256)
-    step = cpu_reference_step(cfg, probe_m)
-    step()
-    t0 = time.perf_counter()
-    step()
-    per_token = max((time.perf_counter() - t0) / probe_m, 1e-9)
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    os.environ["MKL_NUM_THREADS"] = str(cores)
     budget = 60.0 / max(1, args.steps + args.warmup)  # whole run within about a minute of compute
-    sample_m = int(min(cfg["m"], max(probe_m, budget / per_token)))
-    sample_m = max(32, sample_m // 32 * 32)
-    step = cpu_reference_step(cfg, sample_m)
+    sample_m = sized_cpu_sample(cfg, budget)
+    step, kind = cpu_reference_step(cfg, sample_m)
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
@@ -191,27 +260,318 @@ def run_reference_arm(args, cfg):
     elapsed = time.perf_counter() - t0
     ms = elapsed / args.steps * 1e3
     value = 3 * 2.0 * sample_m * nnz_of(cfg) * 1024 / (ms / 1e3) / 1e12
-    sample = "first %d of %d tokens per step; to_dense + fp32 matmul for fwd, dgrad, wgrad" % (sample_m, cfg["m"])
+    how = ("the reference package's BlockSparseMatrix.to_dense + torch.matmul" if kind == "reference"
+           else "numpy restatement of to_dense + fp32 matmul")
+    sample = "first %d of %d tokens per step; %s for fwd, dgrad, wgrad" % (sample_m, cfg["m"], how)
     line = {
         "impl": "reference",
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-        "config": dict(workload=args.workload, nnz=nnz_of(cfg), sample_tokens=sample_m, **cfg),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": dict(workload=args.workload, nnz=nnz_of(cfg), sample_tokens=sample_m,
+                       note="CPU path: one process on the host cores whatever --gpus says", **cfg),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
-# --------------------------------------------------------------------------- GPU arm
-def run_gpu_arm(args, cfg):
+# --------------------------------------------------------------------------- GPU helpers
+def time_op(fn, reps, warm=2):
+    import torch
+
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def measure_gemm_peaks(dev):
+    """cuBLAS 8192^3 GEMMs on this GPU, best of 5 launches each: the TF32 figure is the roofline's denominator for
+    the tf32 kernels (single pass; the 3xTF32 default does three times the tensor work per useful FLOP)."""
+    import torch
+
+    n = 8192
+    a = torch.randn(n, n, device=dev)
+    b = torch.randn(n, n, device=dev)
+    c = torch.empty(n, n, device=dev)
+    out = {}
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    best = min(time_op(lambda: torch.mm(a, b, out=c), 1, warm=1) for _ in range(5))
+    out["tf32_tflops"] = 2.0 * n ** 3 / (best / 1e3) / 1e12
+    torch.backends.cuda.matmul.allow_tf32 = old
+    ab, bb = a.bfloat16(), b.bfloat16()
+    cb = torch.empty(n, n, device=dev, dtype=torch.bfloat16)
+    best = min(time_op(lambda: torch.mm(ab, bb, out=cb), 1, warm=1) for _ in range(5))
+    out["bf16_tflops"] = 2.0 * n ** 3 / (best / 1e3) / 1e12
+    return out
+
+
+class LayerCase:
+    """One BlockSparseLinear workload resident on the device: seeded pattern, weights and activations."""
+
+    def __init__(self, cfg, dev, rank=0, host_buffers=False):
+        import numpy as np
+        import torch
+
+        from pytorch_block_sparse_b200 import BlockSparseLinear
+
+        self.cfg = cfg
+        m, n, k = cfg["m"], cfg["n"], cfg["k"]
+        # same pattern and weights on every rank (token-data-parallel), different tokens per rank
+        np.random.seed(1234)
+        torch.manual_seed(1234)
+        self.lin = BlockSparseLinear(k, n, bias=True, density=cfg["density"])
+        with torch.no_grad():
+            self.lin.weight.data.copy_((torch.randn(self.lin.weight.data.shape) * 0.02).to(dev))
+            self.lin.bias.copy_((torch.randn(n) * 0.02).to(dev))
+        self.w = self.lin.weight
+        assert self.w.data.shape[0] == nnz_of(cfg) * 32
+        g = torch.Generator().manual_seed(99 + rank)
+        if host_buffers:
+            self.x_host = torch.randn(m, k, generator=g).pin_memory()
+            self.dy_host = torch.randn(m, n, generator=g).pin_memory()
+            self.x, self.dy = self.x_host.to(dev), self.dy_host.to(dev)
+        else:
+            gd = torch.Generator(device=dev).manual_seed(99 + rank)
+            self.x = torch.randn(m, k, generator=gd, device=dev)
+            self.dy = torch.randn(m, n, generator=gd, device=dev)
+        self.y = torch.empty(m, n, device=dev)
+        self.dx = torch.empty(m, k, device=dev)
+        self.dw = torch.empty_like(self.w.data)
+        self.plans = (self.w._plan(True), self.w._plan(False), self.w._sddmm_plan())
+        self.bias = self.lin.bias.detach()
+        self.data = self.w.data.detach()
+
+    def ops(self, prec):
+        """(pack, fwd, dgrad, wgrad) closures for one precision."""
+        from pytorch_block_sparse_b200 import native
+
+        n, k = self.cfg["n"], self.cfg["k"]
+        plan_f, plan_d, plan_w = self.plans
+        state = {}
+
+        def pack():
+            state["packed"] = native.pack_weights(self.data, prec)
+
+        def fwd():
+            native.dsd_matmul(self.x, plan_f, state["packed"], n, True, bias=self.bias, out=self.y)
+
+        def dgrad():
+            native.dsd_matmul(self.dy, plan_d, state["packed"], k, False, out=self.dx)
+
+        def wgrad():
+            native.sddmm(self.dy, True, self.x, True, self.w.blocks, self.dw, precision=prec, plan=plan_w)
+
+        return pack, fwd, dgrad, wgrad
+
+
+def run_sweep(dev, steps):
+    """ms per fwd+bwd step of the other benchmark configurations / precisions (one GPU, inputs resident)."""
+    import torch
+
+    from pytorch_block_sparse_b200 import native
+
+    out = {}
+    cases = {}
+    for workload, prec_name in SWEEP:
+        if workload not in cases:
+            cases.clear()  # one workload resident at a time
+            torch.cuda.empty_cache()
+            cases[workload] = LayerCase(WORKLOADS[workload], dev)
+        case = cases[workload]
+        pack, fwd, dgrad, wgrad = case.ops(native.resolve_precision(prec_name))
+
+        def step():
+            pack(); fwd(); wgrad(); dgrad()
+
+        ms = time_op(step, max(3, min(steps, 10)), warm=3)
+        out["%s/%s" % (workload, prec_name)] = {
+            "ms_per_step": ms, "effective_tflops": 3 * flops_per_op(case.cfg) / (ms / 1e3) / 1e12}
+    cases.clear()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_c5(dev, world, rank, steps, precisions):
+    """Benchmark configuration 5: one 32768 x 8192 layer at density 0.1 on 65536 tokens, its block-rows split over
+    the ranks (strong scaling: the whole layer's work is fixed).  Per step and rank: pack, forward of the shard,
+    all-gather of the output shards (side stream, overlapping what follows), local wgrad, dgrad to a partial
+    input gradient, all-reduce of that partial gradient."""
     import numpy as np
     import torch
     import torch.distributed as dist
 
-    from pytorch_block_sparse_b200 import BlockSparseLinear, BlockSparseMatrix, native
+    from pytorch_block_sparse_b200 import BlockSparseMatrix, native
+    from pytorch_block_sparse_b200.distributed import shard_block_rows
+
+    m, n, k = C5["m"], C5["n"], C5["k"]
+    nnz = nnz_of(C5)
+    np.random.seed(555)
+    torch.manual_seed(555)
+    full = BlockSparseMatrix.zeros((n, k), n_blocks=nnz, device=dev)
+    with torch.no_grad():
+        full.data.normal_(0, 0.02)
+    w = shard_block_rows(full, rank, world) if world > 1 else full
+    del full
+    n_local = w.shape[0]
+    gd = torch.Generator(device=dev).manual_seed(77)
+    x = torch.randn(m, k, generator=gd, device=dev)            # replicated input
+    dy = torch.randn(m, n_local, generator=gd, device=dev)     # this rank's slice of the output gradient
+    bias = torch.zeros(n_local, device=dev)
+    y = torch.empty(m, n_local, device=dev)
+    dx = torch.empty(m, k, device=dev)
+    dw = torch.empty_like(w.data)
+    y_all = torch.empty(world, m, n_local, device=dev) if world > 1 else None  # rank-major gather, no interleave copy
+    plan_f, plan_d, plan_w = w._plan(True), w._plan(False), w._sddmm_plan()
+    side = torch.cuda.Stream(device=dev)
+    data = w.data.detach()
+    out = {"shape": dict(C5, nnz=nnz), "block_rows_per_rank": n_local // 32, "scaling": "strong",
+           "all_gather_bytes_per_rank": (world - 1) * m * n_local * 4 if world > 1 else 0,
+           "all_reduce_bytes": m * k * 4 if world > 1 else 0}
+    f_total = 3 * 2.0 * m * nnz * 1024
+    for prec_name in precisions:
+        prec = native.resolve_precision(prec_name)
+
+        def step(collectives):
+            packed = native.pack_weights(data, prec)
+            native.dsd_matmul(x, plan_f, packed, n_local, True, bias=bias, out=y)
+            if collectives and world > 1:
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    dist.all_gather_into_tensor(y_all, y)
+            native.sddmm(dy, True, x, True, w.blocks, dw, precision=prec, plan=plan_w)
+            native.dsd_matmul(dy, plan_d, packed, k, False, out=dx)
+            if collectives and world > 1:
+                dist.all_reduce(dx)
+                torch.cuda.current_stream().wait_stream(side)
+
+        res = {}
+        for name, coll in (("compute_ms", False), ("with_collectives_ms", True)):
+            if coll and world == 1:
+                res[name] = res["compute_ms"]
+                continue
+            if world > 1:
+                dist.barrier()
+            ms = time_op(lambda: step(coll), max(2, min(steps, 5)), warm=2)
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            res[name] = ms
+        res["effective_tflops"] = f_total / (res["with_collectives_ms"] / 1e3) / 1e12
+        res["effective_tflops_compute_only"] = f_total / (res["compute_ms"] / 1e3) / 1e12
+        out[prec_name] = res
+    return out
+
+
+def run_c4(dev, world, rank, steps):
+    """Benchmark configuration 4: RoBERTa-base, three Linear kinds per layer made block-sparse at density 0.5 by
+    BlockSparseModelPatcher, batch 32 x 512 random token ids per GPU, MLM loss, AdamW; token-data-parallel
+    (gradients summed over the ranks; the sparse layers contribute only their stored blocks)."""
+    import contextlib
+    import io
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    try:
+        from transformers import RobertaConfig, RobertaForMaskedLM
+    except Exception as exc:  # pragma: no cover - the image has transformers
+        return {"unavailable": "transformers not importable: %s" % exc}
+    from pytorch_block_sparse_b200 import BlockSparseModelPatcher
+    from pytorch_block_sparse_b200.block_sparse import BlockSparseMatrixBase
+
+    batch, seq = 32, 512
+    cfg = RobertaConfig(vocab_size=50265, hidden_size=768, num_hidden_layers=12, num_attention_heads=12,
+                        intermediate_size=3072, max_position_embeddings=514, type_vocab_size=1,
+                        hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, attn_implementation="sdpa")
+    g = torch.Generator().manual_seed(4 + rank)
+    ids = torch.randint(0, 50265, (batch, seq), generator=g).to(dev)
+    labels = ids.clone()
+    labels[torch.rand(batch, seq, generator=g).to(dev) > 0.15] = -100
+
+    def build(sparse):
+        torch.manual_seed(44)
+        np.random.seed(44)
+        model = RobertaForMaskedLM(cfg).to(dev)
+        if sparse:
+            mp = BlockSparseModelPatcher()
+            for kind in ("intermediate", "output", "attention\\.output"):
+                mp.add_pattern("roberta\\.encoder\\.layer\\.[0-9]+\\.%s\\.dense" % kind, {"density": 0.5})
+            with contextlib.redirect_stdout(io.StringIO()):
+                mp.patch_model(model)
+        model.train()
+        return model
+
+    def train_ms(model, tf32):
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-4)
+        sparse_data = {id(mod.data) for mod in model.modules() if isinstance(mod, BlockSparseMatrixBase)}
+        old = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+
+        def step():
+            opt.zero_grad(set_to_none=True)
+            loss = model(input_ids=ids, labels=labels).loss
+            loss.backward()
+            if world > 1:
+                grads = [p.grad for p in model.parameters() if p.grad is not None]
+                flat = torch.cat([gr.reshape(-1) for gr in grads])
+                dist.all_reduce(flat)
+                flat /= world
+                off = 0
+                for gr in grads:
+                    gr.copy_(flat[off:off + gr.numel()].view_as(gr))
+                    off += gr.numel()
+            opt.step()
+            return loss
+
+        if world > 1:
+            dist.barrier()
+        ms = time_op(step, max(2, min(steps, 4)), warm=2)
+        torch.backends.cuda.matmul.allow_tf32 = old
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        grad_bytes = sum(p.numel() * 4 for p in model.parameters())
+        sparse_bytes = sum(p.numel() * 4 for p in model.parameters() if id(p) in sparse_data)
+        return ms, grad_bytes, sparse_bytes, float(step().item())
+
+    out = {"model": "RoBERTa-base 12 x 768/3072, vocab 50265", "tokens_per_gpu_step": batch * seq,
+           "patched": "intermediate.dense, output.dense, attention.output.dense at density 0.5"}
+    model = build(True)
+    ms, grad_bytes, sparse_bytes, loss = train_ms(model, tf32=False)
+    out["sparse"] = {"ms_per_step": ms, "tokens_per_s": world * batch * seq / (ms / 1e3), "loss": loss,
+                     "parameters": sum(p.numel() for p in model.parameters()),
+                     "grad_bytes_per_step": grad_bytes, "of_which_sparse_layers": sparse_bytes}
+    del model
+    torch.cuda.empty_cache()
+    model = build(False)
+    for name, tf32 in (("dense_tf32", True), ("dense_fp32", False)):
+        ms, grad_bytes, _, loss = train_ms(model, tf32=tf32)
+        out[name] = {"ms_per_step": ms, "tokens_per_s": world * batch * seq / (ms / 1e3), "loss": loss,
+                     "parameters": sum(p.numel() for p in model.parameters()), "grad_bytes_per_step": grad_bytes}
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_gpu_arm(args, cfg):
+    import torch
+    import torch.distributed as dist
+
+    from pytorch_block_sparse_b200 import native
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -226,38 +586,26 @@ def run_gpu_arm(args, cfg):
     native.set_default_precision(prec_name)
     m, n, k = cfg["m"], cfg["n"], cfg["k"]
     nnz = nnz_of(cfg)
+    legs = set(filter(None, args.legs.split(","))) - {"none"}
 
-    # same pattern and weights on every rank (token-data-parallel), different tokens per rank
-    np.random.seed(1234)
-    torch.manual_seed(1234)
-    lin = BlockSparseLinear(k, n, bias=True, density=cfg["density"])
-    with torch.no_grad():
-        lin.weight.data.copy_((torch.randn(lin.weight.data.shape) * 0.02).to(dev))
-        lin.bias.copy_((torch.randn(n) * 0.02).to(dev))
-    w = lin.weight
-    assert w.data.shape[0] == nnz * 32
-    g = torch.Generator().manual_seed(99 + rank)
-    x_host = torch.randn(m, k, generator=g).pin_memory()
-    dy_host = torch.randn(m, n, generator=g).pin_memory()
-    x = x_host.to(dev)
-    dy = dy_host.to(dev)
-    y = torch.empty(m, n, device=dev)
-    dx = torch.empty(m, k, device=dev)
-    dw = torch.empty_like(w.data)
-    plan_f, plan_d, plan_w = w._plan(True), w._plan(False), w._sddmm_plan()
-    bias = lin.bias.detach()
-    data = w.data.detach()
+    case = LayerCase(cfg, dev, rank, host_buffers=True)
+    lin, w = case.lin, case.w
+    x, dy, y, dx, dw = case.x, case.dy, case.y, case.dx, case.dw
+    pack, fwd, dgrad, wgrad = case.ops(prec)
+    side = torch.cuda.Stream(device=dev)
 
-    launches_per_step = [0]
-
-    def step(count=False):
-        packed = native.pack_weights(data, prec)
-        native.dsd_matmul(x, plan_f, packed, n, True, bias=bias, out=y)
-        native.dsd_matmul(dy, plan_d, packed, k, False, out=dx)
-        native.sddmm(dy, True, x, True, w.blocks, dw, precision=prec, plan=plan_w)
+    def step():
+        # the weight gradient first: its all-reduce (N > 1) then travels while dgrad computes
+        pack()
+        fwd()
+        wgrad()
         if world > 1:
-            dist.all_reduce(dw)
-        return packed
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                dist.all_reduce(dw)
+        dgrad()
+        if world > 1:
+            torch.cuda.current_stream().wait_stream(side)
 
     # kernels of this library launched per step: pack, fwd, dgrad, wgrad (+ its token-range reduction)
     launches_per_step = 5 if native.load().bsmm_sddmm_workspace_bytes(n, k, m, nnz, prec) > 0 else 4
@@ -267,7 +615,8 @@ def run_gpu_arm(args, cfg):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         step()
     barrier()
     assert native.device_status() == 0, "a kernel abandoned a bounded wait during warm-up"
@@ -294,28 +643,13 @@ def run_gpu_arm(args, cfg):
     value = world * 3 * f_op / (ms_per_step / 1e3) / 1e12
 
     # ---- per-kernel timings (same stream, CUDA events, inputs larger than L2) ----
-    def time_op(fn, reps):
-        for _ in range(2):
-            fn()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(reps):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / reps
-
-    packed = native.pack_weights(data, prec)
+    pack()
     reps = max(3, min(20, args.steps))
-    kernels = {
-        "pack_ms": time_op(lambda: native.pack_weights(data, prec), reps),
-        "fwd_ms": time_op(lambda: native.dsd_matmul(x, plan_f, packed, n, True, bias=bias, out=y), reps),
-        "dgrad_ms": time_op(lambda: native.dsd_matmul(dy, plan_d, packed, k, False, out=dx), reps),
-        "wgrad_ms": time_op(lambda: native.sddmm(dy, True, x, True, w.blocks, dw, precision=prec, plan=plan_w), reps),
-    }
+    kernels = {"pack_ms": time_op(pack, reps), "fwd_ms": time_op(fwd, reps), "dgrad_ms": time_op(dgrad, reps),
+               "wgrad_ms": time_op(wgrad, reps)}
 
     # ---- end to end through the public layer API with host buffers ----
+    x_host, dy_host = case.x_host, case.dy_host
     y_host = torch.empty(m, n).pin_memory()
     dx_host = torch.empty(m, k).pin_memory()
     dw_host = torch.empty(w.data.shape).pin_memory()
@@ -356,7 +690,7 @@ def run_gpu_arm(args, cfg):
                 host.copy_(t, non_blocking=True)
                 t.record_stream(s_out)
 
-    e2e_steps = max(4, min(args.steps, 8))
+    e2e_steps = max(4, args.steps)
     for i in range(2):
         e2e_step(i)
     torch.cuda.current_stream().wait_stream(s_out)
@@ -377,16 +711,14 @@ def run_gpu_arm(args, cfg):
     h2d = (x_host.numel() + dy_host.numel()) * 4
     d2h = (y_host.numel() + dx_host.numel() + dw_host.numel()) * 4
     status = native.device_status()
+    del x_dev, dy_dev, y_host, dx_host, dw_host
 
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    # ---- comparators: cuBLAS dense nn.Linear fwd+bwd on the same shape ----
-    comparators = {}
-    if not args.no_comparators:
+    # ---- comparators (rank 0): cuBLAS dense nn.Linear fwd+bwd on the same shape, the reference's CUDA kernels ----
+    comparators, peaks_here = {}, None
+    if rank == 0 and not args.no_comparators:
+        peaks_here = measure_gemm_peaks(dev)
         wd = torch.randn(n, k, device=dev) * 0.02
+        bias = case.bias
 
         def dense_step():
             torch.addmm(bias, x, wd.t(), out=y)
@@ -420,34 +752,65 @@ def run_gpu_arm(args, cfg):
 
             comparators["reference_cuda_kernels_ms"] = time_op(reference_step, 3)
 
+    # ---- extra legs ----
+    extra = {}
+    if "sweep" in legs and world == 1:
+        del case, lin, w, x, dy, y, dx, dw, pack, fwd, dgrad, wgrad, x_host, dy_host
+        torch.cuda.empty_cache()
+        extra["sweep"] = run_sweep(dev, args.steps)
+    else:
+        del case, lin, w, x, dy, y, dx, dw, pack, fwd, dgrad, wgrad, x_host, dy_host
+        torch.cuda.empty_cache()
+    if "c5" in legs:
+        extra["c5"] = run_c5(dev, world, rank, args.steps, sorted({prec_name, "bf16"}))
+        torch.cuda.empty_cache()
+    if "c4" in legs:
+        extra["c4"] = run_c4(dev, world, rank, args.steps)
+        torch.cuda.empty_cache()
+    status |= native.device_status()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # ---- roofline of the dominant kernel ----
     peaks = measured_peaks()
-    op_names = {"fwd_ms": "dsd forward", "dgrad_ms": "dsd dgrad", "wgrad_ms": "sddmm wgrad"}
+    op_names = {"fwd_ms": ("dsd forward", "dsd_umma"), "dgrad_ms": ("dsd dgrad", "dsd_umma"), "wgrad_ms": ("sddmm wgrad", "sddmm_umma")}
     dom = max(op_names, key=lambda key: kernels[key])
     achieved = f_op / (kernels[dom] / 1e3) / 1e12
-    # tcgen05 kind::tf32 runs at half the bf16 rate; the measured dense bf16 peak (sustained, the
-    # kernel is timed inside a long loop) halved is the single-pass TF32 ceiling used here
-    peak = peaks["bf16_tflops_sustained"] / 2.0 if prec_name != "bf16" else peaks["bf16_tflops_sustained"]
-    # DRAM bytes (read + write) of one launch of that kernel from an ncu capture of this workload; null
-    # where no capture was taken (the summaries with the commands are under profiles/)
-    ncu_traffic = {
-        ("c3_d0.25", "tf32x3", "wgrad_ms"): (666.8e6, "profiles/sddmm_umma_tf32x3_c3_d0.25.md"),
-        ("c3_d0.25", "tf32x3", "fwd_ms"): (624.0e6, "profiles/dsd_umma_tf32x3_c3_d0.25.md"),
-    }.get((args.workload, prec_name, dom), (None, None))
+    if peaks_here is not None:
+        # the denominator is cuBLAS on this GPU in this run: TF32 for the tf32 kernels, bf16 for the bf16 mode
+        peak = peaks_here["bf16_tflops"] if prec_name == "bf16" else peaks_here["tf32_tflops"]
+        peak_source = "measured in this run: cuBLAS %s 8192^3, best of 5" % ("bf16" if prec_name == "bf16" else "TF32 (allow_tf32)")
+    else:
+        peak = peaks["bf16_tflops"] if prec_name == "bf16" else peaks["bf16_tflops"] / 2.0
+        peak_source = "%s bf16 burst %.1f TFLOP/s%s (comparators switched off: no TF32 GEMM was timed)" % (
+            peaks["source"], peaks["bf16_tflops"], "" if prec_name == "bf16" else " / 2")
+    traffic, traffic_source = profile_traffic(op_names[dom][1], prec_name, args.workload)
     roofline = {
-        "kernel": op_names[dom], "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": achieved / peak, "traffic": ncu_traffic[0], "traffic_source": ncu_traffic[1],
-        "peak_source": "%s bf16 sustained %.1f TFLOP/s %s" % (peaks["source"], peaks["bf16_tflops_sustained"], "/ 2 (tf32)" if prec_name != "bf16" else ""),
+        "kernel": op_names[dom][0], "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+        "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_source, "peak_source": peak_source,
         "algorithmic_flops_per_launch": f_op,
     }
+    if prec_name == "tf32x3":
+        # three tensor-core products per useful one: the ceiling of this mode on effective FLOPs
+        roofline["frac_of_3xtf32_ceiling"] = achieved / (peak / 3.0)
+    if peaks_here is not None:
+        roofline["gemm_peaks_this_run"] = peaks_here
+    roofline["step_frac"] = (3 * f_op / (ms_per_step / 1e3) / 1e12) / world / peak * world  # whole step vs the same peak
+
+    def ratio(key):  # > 1: this library's step is the faster one
+        return comparators[key] / ms_per_step if key in comparators else None
 
     if world == 1:
-        cpu_value, cpu_m, cpu_t = time_cpu_reference(cfg, target_seconds=args.cpu_seconds, reps=3)
-        cpu_sample = "first %d of %d tokens, median of 3; numpy to_dense + fp32 matmul" % (cpu_m, m)
+        cpu_value, cpu_m, cpu_kind = time_cpu_reference(cfg, target_seconds=args.cpu_seconds, reps=3)
+        cpu_sample = "first %d of %d tokens, median of 3; to_dense + fp32 matmul (%s)" % (
+            cpu_m, m, "the reference package on torch CPU" if cpu_kind == "reference" else "numpy restatement")
     else:  # the host cores are timed in the single-GPU run only
-        cpu_value, cpu_sample = None, "not timed when n_gpus > 1"
+        cpu_value, cpu_sample, cpu_kind = None, "not timed when n_gpus > 1", "port"
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": prec_name, "data": "synthetic",
         "config": dict(workload=args.workload, nnz=nnz, parallelism="token-dp%d" % world,
@@ -456,15 +819,21 @@ def run_gpu_arm(args, cfg):
                        ("x and dy (%d and %d MiB) fit the 126 MB L2 and are not flushed between steps"
                         % (m * k * 4 >> 20, m * n * 4 >> 20)), **cfg),
         "roofline": roofline,
-        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": os.cpu_count(), "kind": cpu_kind,
                          "sample": cpu_sample},
-        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
         "kernels": kernels,
         "comparators": comparators,
+        "vs_cublas_tf32": ratio("cublas_dense_tf32_ms"),
+        "vs_cublas_bf16": ratio("cublas_dense_bf16_ms"),
+        "vs_cublas_fp32": ratio("cublas_dense_fp32_ms"),
+        "vs_reference_cuda": ratio("reference_cuda_kernels_ms"),
         "device_status": status,
     }
+    line.update(extra)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -480,6 +849,8 @@ def main():
     ap.add_argument("--precision", default="tf32x3", choices=["tf32x3", "tf32", "bf16", "fp32"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-comparators", action="store_true")
+    ap.add_argument("--legs", default="sweep,c5,c4",
+                    help="comma list of extra legs timed after the headline: sweep (1 GPU only), c5, c4; 'none' for none")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -2,10 +2,23 @@
  * C-ABI of the B200 block-sparse matmul engine (libbsmm_b200.so).
  *
  * Plain pointers and sizes only: every pointer is a DEVICE pointer unless stated
- * otherwise, every size is in elements, the library allocates nothing and keeps no
- * state between calls, and each call only enqueues work on `stream` (a
+ * otherwise, every size is in elements, and each call only enqueues work on `stream` (a
  * cudaStream_t passed as void*; NULL = the legacy default stream).  Return value:
  * BSMM_OK or one of the BSMM_ERR_* codes; bsmm_status_string() names them.
+ *
+ * Memory and state.  No entry point calls cudaMalloc or cudaFree; all buffers are the caller's.
+ * What the library itself holds, per process: on every GPU that runs a kernel of it, a device
+ * health word (4 bytes, see bsmm_device_status) and the BSMM_SDDMM_STATIC_MAX_BYTES scratch array of
+ * bsmm_sddmm_static, both part of the library image; on the host, the device addresses of those two
+ * symbols cached per device after the first call that needs them (plain arrays filled without a lock:
+ * two threads racing on the first call both store the same value), the resolved driver entry point
+ * for tensor-map encoding, the optional trace pointer of bsmm_debug_trace_dsd, and the last CUDA
+ * error per thread.  Nothing else survives a call.
+ *
+ * Stream capture.  The first tensor-core call on a device (bsmm_dsd, bsmm_sddmm, bsmm_sddmm_static)
+ * resolves a driver entry point and a symbol address, and every tensor-core call sets a kernel
+ * attribute and binds the device's primary context to the calling thread (cudaFuncSetAttribute,
+ * cudaSetDevice on the current device): make the first call per device before a capture begins.
  *
  * The weight format is the reference's (pytorch_block_sparse/block_sparse.py:10-76,
  * :125-153): `data` fp32 [nnz*32, 32], slot s holding its 32x32 block transposed

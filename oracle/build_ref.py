@@ -30,5 +30,8 @@ def build(reference_root, verbose=True):
 
 
 if __name__ == "__main__":
-    build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BSMM_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: python oracle/build_ref.py /path/to/reference/checkout   (or set BSMM_REFERENCE_ROOT)")
+    build(root)
     print("built into oracle/_ref")

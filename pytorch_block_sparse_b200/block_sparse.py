@@ -41,6 +41,7 @@ class BlockSparseMatrixBase(torch.nn.Module):
         self.data = torch.nn.Parameter(data)
         self._plan_cache = {}
         self._pack_cache = {}
+        self.last_grad_block_sumsq = None  # per-slot sum of squares of the most recent weight gradient
         self.rebuild(block_mask, callback=False)
 
     # derived, device-specific caches never travel with a pickle or a replica's state
@@ -180,7 +181,14 @@ class BlockSparseMatrixBase(torch.nn.Module):
         return torch.stack([b[:, 1], b[:, 0]], 0)
 
     def block_norm(self, p=2):
-        """Per-slot norm of ``data`` (reference ``block_sparse.py:155-157``)."""
+        """Per-slot norm of ``data`` (reference ``block_sparse.py:155-157``).
+
+        The 2-norm of a 32x32-block matrix on the GPU is the square root of the per-slot sum of squares that
+        a kernel of the library emits (one pass over ``data``; the same statistic rides along with every weight
+        packing, see :meth:`packed_weights`, and with every weight gradient, ``last_grad_block_sumsq``).
+        Other norms, other block shapes and CPU matrices use ``torch.norm``."""
+        if p == 2 and self.data.is_cuda and tuple(self.block_shape) == (32, 32) and self.data.numel() > 0:
+            return native.block_sumsq(self.data).sqrt_()
         d = self.data.reshape(-1, self.block_shape[0], self.block_shape[1])
         return torch.norm(d, p=p, dim=(1, 2))
 
@@ -340,6 +348,40 @@ class BlockSparseMatrixBase(torch.nn.Module):
         grid[coo[0], coo[1]] = data.reshape(-1, bw, bh).transpose(1, 2)
         return grid.permute(0, 2, 1, 3).reshape(self.shape[0], self.shape[1])
 
+    # ------------------------------------------------------------- interchange
+    def to_bsr(self, data_replace=None):
+        """The matrix as a ``torch.sparse_bsr_tensor``: blocks in CSR order, each ``[bh, bw]`` tile un-transposed.
+        The reference's only sparse export is the hybrid COO tensor of :meth:`to_sparse`
+        (reference ``block_sparse.py:405-421``); BSR is what ``torch.sparse`` kernels and other libraries read."""
+        data = self.data.detach() if data_replace is None else data_replace
+        bh, bw = self.block_shape
+        slots = self.cols_a[:, 1].long()
+        values = data.reshape(-1, bw, bh)[slots].transpose(1, 2).contiguous()
+        return torch.sparse_bsr_tensor(
+            self.row_start_ends_a.long(), self.cols_a[:, 0].long(), values, size=tuple(self.shape)
+        )
+
+    @classmethod
+    def from_bsr(cls, bsr):
+        """Build from a ``torch.sparse_bsr_tensor`` (2-D, block size = the block shape).  Slot ``i`` is the
+        tensor's ``i``-th stored block, so ``to_bsr()`` of the result lists the same blocks (sorted by column
+        inside each row, as the index buffers of this class always are)."""
+        crow, col, values = bsr.crow_indices().long(), bsr.col_indices().long(), bsr.values()
+        if values.dim() != 3 or crow.dim() != 1:
+            raise Exception("from_bsr takes a 2-D BSR tensor without batch dimensions")
+        bh, bw = int(values.shape[1]), int(values.shape[2])
+        shape = tuple(bsr.shape)
+        X, Y = shape[0] // bh, shape[1] // bw
+        rows = torch.repeat_interleave(torch.arange(X, device=crow.device), crow[1:] - crow[:-1])
+        mask = torch.zeros((X, Y), dtype=torch.bool, device=values.device)
+        mask[rows, col] = True
+        if int(mask.sum()) != col.shape[0]:
+            raise Exception("the BSR tensor stores a block position twice")
+        data = values.to(torch.float32).transpose(1, 2).reshape(-1, bw).contiguous()
+        ret = cls(shape, mask, data, (bh, bw))
+        ret.rebuild(mask, torch.argsort(rows * Y + col))  # i-th position in row-major order -> its slot
+        return ret
+
     def check_with_dense(self, dense_version):
         coo = self.build_coo_block_index().long()
         bh, bw = self.block_shape
@@ -416,21 +458,33 @@ class BlockSparseMatrixBase(torch.nn.Module):
             self._plan_cache[key] = plan
         return plan
 
-    def packed_weights(self, precision=None):
-        """Kernel-ready images of ``data`` (tf32 hi/lo or bf16, both orientations) and the fused
-        per-slot sum of squares; rebuilt only when ``data`` changed since the last call."""
+    def packed_weights(self, precision=None, fresh=True):
+        """Kernel-ready images of ``data`` (tf32 hi/lo or bf16, both orientations) and the fused per-slot sum
+        of squares.
+
+        ``fresh=True`` (the default) packs now: one small kernel (about 1 % of a layer step) and the only way
+        to be right after writes that autograd's version counter does not see (``p.data.add_()``, fused
+        optimizers, EMA copies).  ``fresh=False`` reuses the last images while ``data``'s address and version
+        counter are unchanged -- for frozen weights; call :meth:`invalidate_packed` after writing ``data``
+        behind autograd's back."""
         precision = native.resolve_precision(precision)
         key = (self.data.data_ptr(), self.data._version, precision)
-        hit = self._pack_cache.get("key") == key
-        if not hit:
+        if fresh or self._pack_cache.get("key") != key:
             self._pack_cache = {"key": key, "pack": native.pack_weights(self.data, precision)}
         return self._pack_cache["pack"]
 
-    def reverse_matmul_(self, dense_a, transpose=True, bias=None, precision=None):
+    def invalidate_packed(self):
+        """Forget the cached weight images (see :meth:`packed_weights`)."""
+        self._pack_cache = {}
+
+    def reverse_matmul_(self, dense_a, transpose=True, bias=None, precision=None, packed=None):
         """``a @ W.T`` if ``transpose`` else ``a @ W`` (reference ``block_sparse.py:496-578``); ``a`` is 2-D.
 
-        ``bias`` (fwd only) is added in the kernel epilogue.  Returns a contiguous ``[M, n]``
-        tensor (the reference returns the transposed view of an ``[n, M]`` buffer; values agree).
+        ``bias`` (fwd only) is added in the kernel epilogue.  ``packed`` hands in weight images made
+        earlier (the autograd function packs once in forward and reuses the images in backward: the gradient
+        is then taken with the weights the forward saw); by default the weights are packed now.
+        Returns a contiguous ``[M, n]`` tensor (the reference returns the transposed view of an
+        ``[n, M]`` buffer; values agree).
         """
         if dense_a.dim() > 2:
             dense_a = dense_a.reshape(-1, dense_a.shape[-1])
@@ -448,17 +502,17 @@ class BlockSparseMatrixBase(torch.nn.Module):
         return native.dsd_matmul(
             dense_a,
             self._plan(transpose),
-            self.packed_weights(precision),
+            packed if packed is not None else self.packed_weights(precision),
             n_out=shape_b[1],
             transpose=transpose,
             bias=bias,
         )
 
-    def reverse_matmul(self, dense_a, transpose, bias=None, precision=None):
+    def reverse_matmul(self, dense_a, transpose, bias=None, precision=None, packed=None):
         """Any-rank wrapper of :meth:`reverse_matmul_` (reference ``block_sparse.py:597-604``)."""
         self._require_cuda()
         flat, lead = self.flatten_first_dims(dense_a)
-        ret = self.reverse_matmul_(flat, transpose=transpose, bias=bias, precision=precision)
+        ret = self.reverse_matmul_(flat, transpose=transpose, bias=bias, precision=precision, packed=packed)
         return self.unflatten_first_dims(ret, lead)
 
     def matmul_with_output_sparse_support_(self, dense_a, dense_b, overwrite_data=False, precision=None):
@@ -472,10 +526,14 @@ class BlockSparseMatrixBase(torch.nn.Module):
         out = self.data if overwrite_data else torch.empty_like(self.data)
         a, a_rowmajor = self._orient(dense_a)
         b, b_rowmajor = self._orient(dense_b)
+        # sum of squares of every gradient block, written by the kernel's epilogue (its token-range reduction)
+        sumsq = torch.empty(self.data.shape[0] // 32, dtype=torch.float32, device=self.data.device)
         with torch.no_grad():
             native.sddmm(
-                a, a_rowmajor, b, b_rowmajor, self.blocks, out.detach(), precision=precision, plan=self._sddmm_plan()
+                a, a_rowmajor, b, b_rowmajor, self.blocks, out.detach(), precision=precision,
+                block_sumsq=sumsq, plan=self._sddmm_plan(),
             )
+        self.last_grad_block_sumsq = sumsq
         if overwrite_data:
             self._pack_cache = {}  # the kernel wrote `data` behind autograd's version counter
         return out
@@ -490,14 +548,107 @@ class BlockSparseMatrixBase(torch.nn.Module):
 
 
 class BlockSparseMatrix(BlockSparseMatrixBase):
-    """32x32-block matrix served by the CUDA kernels (reference ``block_sparse.py:668-679``)."""
+    """Matrix served by the CUDA kernels (reference ``block_sparse.py:668-679``).
+
+    The kernels work on 32x32 blocks.  A matrix with larger square blocks (64x64, 128x128, any multiple of 32;
+    the reference sends those to its dense-masked emulator, ``block_sparse_linear.py:202-205``) keeps the
+    reference's ``data`` and index buffers in its own block units and carries a derived 32x32 matrix of the
+    same non-zeros -- every block becomes ``(b/32)^2`` adjacent fine blocks -- which the kernels run on.
+    ``data`` is re-tiled into the fine matrix before a product and the fine weight gradient is re-tiled back:
+    two copies of weight size per step."""
 
     def __init__(self, shape, block_mask, data, block_shape=(32, 32)):
         if len(shape) != 2 or shape[0] % 32 != 0 or shape[1] % 32 != 0:
             raise Exception("shape should be a tuple of 2 multiples of 32")
         if len(block_shape) != 2 or block_shape[0] % 32 != 0 or block_shape[1] % 32 != 0:
             raise Exception("block_shape should be a tuple of 2 multiples of 32")
+        if tuple(block_shape) != (32, 32) and block_shape[0] != block_shape[1]:
+            raise Exception("blocks larger than 32x32 must be square on the CUDA path, got %s" % (block_shape,))
+        object.__setattr__(self, "_fine", None)
         super().__init__(shape, block_mask, data, block_shape)
+
+    # the fine matrix is derived state: it never travels with a pickle, a state_dict or .to()
+    def __getstate__(self):
+        state = super().__getstate__()
+        state["_fine"] = None
+        return state
+
+    def _is_coarse(self):
+        return tuple(self.block_shape) != (32, 32)
+
+    def rebuild(self, block_mask, block_ptr=None, callback=True):
+        super().rebuild(block_mask, block_ptr, callback)
+        object.__setattr__(self, "_fine", None)
+
+    def _fine_matrix(self):
+        """The 32x32 matrix of the same non-zeros.  Fine slot ``(s * nb + i) * nb + j`` is the sub-block at
+        row part ``i``, column part ``j`` of slot ``s``; rebuilt when the index buffers changed."""
+        key = (self.blocks.data_ptr(), self.blocks._version, self.data.device)
+        if self._fine is not None and self._fine[0] == key:
+            return self._fine[1]
+        nb = self.block_shape[0] // 32
+        pairs = self.blocks.view(-1, 2).long()  # (block-col, block-row) per slot
+        col, row = pairs[:, 0], pairs[:, 1]
+        part = torch.arange(nb, device=col.device)
+        frow = (row[:, None, None] * nb + part[None, :, None]).expand(-1, nb, nb).reshape(-1)
+        fcol = (col[:, None, None] * nb + part[None, None, :]).expand(-1, nb, nb).reshape(-1)
+        X, Y = self.shape[0] // 32, self.shape[1] // 32
+        mask = torch.zeros((X, Y), dtype=torch.bool, device=col.device)
+        mask[frow, fcol] = True
+        data = torch.zeros((frow.shape[0] * 32, 32), dtype=torch.float32, device=self.data.device)
+        fine = BlockSparseMatrix(tuple(self.shape), mask, data, (32, 32))
+        fine.rebuild(mask, torch.argsort(frow * Y + fcol))
+        fine.requires_grad_(False)
+        object.__setattr__(self, "_fine", (key, fine))
+        return fine
+
+    def _to_fine(self, data):
+        """``data`` layout ``[nnz * b, b]`` -> the fine matrix's ``[nnz * nb * nb * 32, 32]``."""
+        nb = self.block_shape[0] // 32
+        # data[s, j, c', i, r'] -> fine[s, i, j, c', r']
+        return data.reshape(-1, nb, 32, nb, 32).permute(0, 3, 1, 2, 4).reshape(-1, 32)
+
+    def _from_fine(self, fine_data):
+        nb = self.block_shape[0] // 32
+        return fine_data.reshape(-1, nb, nb, 32, 32).permute(0, 2, 3, 1, 4).reshape(-1, self.block_shape[1])
+
+    def _fine_synced(self):
+        fine = self._fine_matrix()
+        with torch.no_grad():
+            fine.data.copy_(self._to_fine(self.data.detach()))
+        return fine
+
+    def packed_weights(self, precision=None, fresh=True):
+        if self._is_coarse():
+            return self._fine_synced().packed_weights(precision, fresh=True)
+        return super().packed_weights(precision, fresh)
+
+    def block_norm(self, p=2):
+        if self._is_coarse() and p == 2 and self.data.is_cuda and self.data.numel() > 0:
+            nb2 = (self.block_shape[0] // 32) ** 2
+            return native.block_sumsq(self._to_fine(self.data.detach()).contiguous()).view(-1, nb2).sum(1).sqrt_()
+        return super().block_norm(p)
+
+    def reverse_matmul_(self, dense_a, transpose=True, bias=None, precision=None, packed=None):
+        if self._is_coarse():
+            fine = self._fine_matrix()
+            if packed is None:
+                packed = self.packed_weights(precision)
+            return fine.reverse_matmul_(dense_a, transpose=transpose, bias=bias, precision=precision, packed=packed)
+        return super().reverse_matmul_(dense_a, transpose, bias, precision, packed)
+
+    def matmul_with_output_sparse_support_(self, dense_a, dense_b, overwrite_data=False, precision=None):
+        if self._is_coarse():
+            fine = self._fine_matrix()
+            grad = self._from_fine(fine.matmul_with_output_sparse_support_(dense_a, dense_b, False, precision))
+            nb2 = (self.block_shape[0] // 32) ** 2
+            self.last_grad_block_sumsq = fine.last_grad_block_sumsq.view(-1, nb2).sum(1)
+            if overwrite_data:
+                with torch.no_grad():
+                    self.data.copy_(grad)
+                return self.data
+            return grad.contiguous()
+        return super().matmul_with_output_sparse_support_(dense_a, dense_b, overwrite_data, precision)
 
 
 class BlockSparseMatrixEmulator(BlockSparseMatrixBase):
@@ -524,7 +675,7 @@ class BlockSparseMatrixEmulator(BlockSparseMatrixBase):
             self._dense = torch.nn.Parameter(super().to_dense())
             self._mask = super().to_dense(data_replace=torch.ones_like(self.data)) == 1
 
-    def reverse_matmul(self, dense_a, transpose=True, bias=None, precision=None):
+    def reverse_matmul(self, dense_a, transpose=True, bias=None, precision=None, packed=None):
         m = self._dense.t() if transpose else self._dense
         mask = self._mask.t() if transpose else self._mask
         out = dense_a.matmul(m * mask)

@@ -38,7 +38,11 @@ class BlockSparseLinearFunction(torch.autograd.Function):
         ctx.weight = weight
         ctx.n_extra = len(maybe_bias)
         ctx.has_bias = bias is not None
-        return weight.reverse_matmul(input, transpose=True, bias=bias)
+        # The weights are packed once per forward -- never from a cache keyed on autograd's version counter,
+        # which writes through ``.data`` do not bump -- and backward reuses these images, i.e. the weights
+        # the forward saw.
+        ctx.packed = weight.packed_weights() if isinstance(weight, BlockSparseMatrix) else None
+        return weight.reverse_matmul(input, transpose=True, bias=bias, packed=ctx.packed)
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -46,7 +50,7 @@ class BlockSparseLinearFunction(torch.autograd.Function):
         weight = ctx.weight
         grad_input = grad_weight = grad_bias = None
         if ctx.needs_input_grad[0]:
-            grad_input = weight.reverse_matmul(grad_output, transpose=False)
+            grad_input = weight.reverse_matmul(grad_output, transpose=False, packed=ctx.packed)
             assert grad_input.shape == input.shape
         if ctx.needs_input_grad[1]:
             grad_weight = weight.matmul_with_output_sparse_support(grad_output, input)
@@ -60,8 +64,9 @@ class BlockSparseLinear(nn.Module):
 
     ``density`` fixes the block count as ``int(density * in * out / (bh * bw))``.  Built from
     ``torch_nn_linear`` it takes that layer's sizes and bias, fills ``data`` through
-    ``from_dense`` and rescales by ``1/sqrt(density)``.  Block shapes other than 32x32 use the
-    dense-masked emulator class, as in the reference.  Parameters live on ``"cuda"``.
+    ``from_dense`` and rescales by ``1/sqrt(density)``.  Square blocks of 32, 64, 96, 128 ... run on the
+    tensor-core kernels; other block shapes use the dense-masked emulator class (the reference sends
+    everything but 32x32 there).  Parameters live on ``"cuda"``.
     """
 
     OPTIMIZED_BLOCK_SIZE = 32
@@ -80,7 +85,11 @@ class BlockSparseLinear(nn.Module):
         self.fn = BlockSparseLinearFunction.apply
         self.verbose = verbose
         self.block_shape = block_shape
-        self._optimized = block_shape[0] == self.OPTIMIZED_BLOCK_SIZE and block_shape[1] == self.OPTIMIZED_BLOCK_SIZE
+        # 32x32 blocks and larger square multiples of 32 run on the CUDA kernels (the latter through their
+        # 32x32 expansion); every other block shape uses the dense-masked emulator, as in the reference
+        self._optimized = (
+            block_shape[0] == block_shape[1] and block_shape[0] % self.OPTIMIZED_BLOCK_SIZE == 0 and block_shape[0] > 0
+        )
 
         if torch_nn_linear is not None:
             in_features = torch_nn_linear.in_features

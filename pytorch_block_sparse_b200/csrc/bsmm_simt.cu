@@ -3,7 +3,11 @@
 // They compute in the reference's arithmetic (fp32 FMA, fp32 accumulate; reference
 // cutlass/gemm/dp_accummulate.h:90-98) straight from the reference's `data` layout, so
 // they need no packed images and no plan.  They serve BSMM_PREC_FP32_SIMT and are the
-// on-device cross-check of the tensor-core kernels.
+// on-device cross-check of the tensor-core kernels.  The two dsd kernels are deterministic.  The
+// SDDMM kernel is deterministic only when one CTA covers a block's whole token axis (few tokens or
+// many blocks); otherwise it splits the tokens over CTAs that add their partial sums with float
+// atomics, so its low-order bits vary from run to run (the tensor-core SDDMM sums its partials in a
+// fixed order and is reproducible).
 #include "bsmm_common.cuh"
 
 namespace bsmm {

@@ -173,6 +173,22 @@ def pack_weights(data, precision):
     return PackedWeights(raw, precision, images, sumsq)
 
 
+def block_sumsq(data):
+    """Per-slot sum of squares of ``data`` (fp32 ``[nnz*32, 32]``) from the library's statistic kernel
+    (``bsmm_pack_weights`` asked for no images)."""
+    _need_cuda(data, "data")
+    lib = load()
+    nnz = data.shape[0] // 32
+    raw = data.detach()
+    if not raw.is_contiguous():
+        raw = raw.contiguous()
+    sumsq = torch.empty(nnz, dtype=torch.float32, device=data.device)
+    with torch.cuda.device(data.device):
+        check(lib.bsmm_pack_weights(_ptr(raw), nnz, PREC_FP32_SIMT, None, _ptr(sumsq), _stream(data.device)),
+              "bsmm_pack_weights")
+    return sumsq
+
+
 class DsdPlan:
     """Launch plans of the tensor-core dsd kernel for one (offsets, indices) pair, one per group size
     (the kernel's tile is 128 tokens x group*32 columns; the group is chosen from the token count)."""
@@ -264,15 +280,28 @@ class SddmmPlan:
 SDDMM_STATIC_MAX_BYTES = 64 << 20
 
 
-def sddmm_static(a, b, blocks, out, plan, block_sumsq=None):
+def sddmm_static(a, b, blocks, out, plan, block_sumsq=None, precision=None):
     """``bsmm_sddmm_static``: the weight gradient for callers that may not allocate device memory (stream
     capture in progress, a runtime that owns all device memory, allocator callbacks).  The token-range
     partial sums go to a scratch array inside the library image instead of a torch-allocated workspace;
-    this wrapper itself allocates nothing.  ``a``: dY ``[tokens, rows]``, ``b``: X ``[tokens, cols]``, both
-    contiguous fp32; problems whose scratch need exceeds ``SDDMM_STATIC_MAX_BYTES`` are refused.  Calls
-    that overlap on the GPU share the array and race; make the first call per device outside any capture."""
+    this wrapper itself allocates nothing, so it cannot convert its arguments either: ``a`` (dY
+    ``[tokens, rows]``) and ``b`` (X ``[tokens, cols]``) must be contiguous fp32 CUDA tensors, ``out`` contiguous
+    fp32, ``blocks`` int32 -- anything else raises.  Problems whose scratch need exceeds
+    ``SDDMM_STATIC_MAX_BYTES`` are refused.  Calls that overlap on the GPU share the array and race; make the
+    first call per device outside any capture."""
     _need_cuda(a, "dense_a")
+    _need_cuda(b, "dense_b")
+    for name, t, dtype in (("dense_a", a, torch.float32), ("dense_b", b, torch.float32), ("out", out, torch.float32),
+                           ("blocks", blocks, torch.int32)):
+        if t.dtype != dtype or not t.is_contiguous() or not t.is_cuda:
+            raise NativeError("%s must be a contiguous %s CUDA tensor (got %s, contiguous=%s, %s)"
+                              % (name, dtype, t.dtype, t.is_contiguous(), t.device))
+    if block_sumsq is not None and (block_sumsq.dtype != torch.float32 or not block_sumsq.is_contiguous()):
+        raise NativeError("block_sumsq must be a contiguous float32 tensor")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[0] != b.shape[0]:
+        raise NativeError("dense_a and dense_b must be [tokens, rows] and [tokens, cols]")
     lib = load()
+    prec = resolve_precision(precision) if not isinstance(precision, int) else precision
     tokens, rows = a.shape
     cols = b.shape[1]
     nnz = blocks.shape[0] // 2
@@ -280,7 +309,7 @@ def sddmm_static(a, b, blocks, out, plan, block_sumsq=None):
         check(
             lib.bsmm_sddmm_static(
                 _ptr(a), _ptr(b), rows, cols, tokens, _ptr(out), _ptr(blocks), nnz, _ptr(plan.idx), _ptr(plan.buffer),
-                _ptr(block_sumsq), PREC_TF32X3, _stream(a.device),
+                _ptr(block_sumsq), prec, _stream(a.device),
             ),
             "bsmm_sddmm_static",
         )

@@ -42,8 +42,6 @@ class MagnitudeSparseOptimizerStrategy(SparseOptimizerStrategy):
             raise Exception("Unknown new coefficients method %s" % self.new_coefficients_distribution)
 
     def block_norms(self, bsm):
-        if bsm.data.is_cuda and tuple(bsm.block_shape) == (32, 32):
-            return bsm.packed_weights().block_sumsq.sqrt()
         return bsm.block_norm()
 
     def run(self, block_sparse_matrix):

@@ -12,6 +12,8 @@ It imports ``pytorch_block_sparse`` (the reference), builds matrices with its ow
 * ``to_dense`` / ``from_dense`` values                             -> dense.npz
 * fwd / dgrad / wgrad of the reference's ``to_dense`` + ``torch.matmul`` path
   (a small case in full, benchmark configuration 1 as a strided sample)   -> linear.npz
+* the ``state_dict`` of a layer-shaped reference module (the keys a reference checkpoint holds for one
+  ``BlockSparseLinear``), its dense weight and one forward result        -> checkpoint.npz
 
 The committed .npz files are what the tests read; the reference is not needed to run them.
 """
@@ -166,7 +168,35 @@ def gen_linear():
     np.savez_compressed(os.path.join(OUT, "linear.npz"), **out)
 
 
+def gen_checkpoint():
+    """What a checkpoint written by the reference holds for one BlockSparseLinear: ``weight.data``, the five
+    index buffers under ``weight.*`` and ``bias`` (BlockSparseLinear itself is CUDA-only in the reference,
+    block_sparse_linear.py:217, so a module of the same attribute layout is assembled on the CPU)."""
+
+    class LayerShaped(torch.nn.Module):
+        def __init__(self, weight, bias):
+            super().__init__()
+            self.weight = weight
+            self.bias = torch.nn.Parameter(bias)
+
+    np.random.seed(41)
+    torch.manual_seed(41)
+    m = BSM.randn((128, 192), n_blocks=9, device="cpu")
+    # a pattern history: two slots moved, so slot order differs from row-major order
+    free = (~m.block_mask_build(None)).nonzero()
+    m.block_replace(torch.cat([free[[1, 4]], torch.tensor([[6], [2]])], -1))
+    layer = LayerShaped(m, torch.randn(128) * 0.02)
+    out = {"sd/" + k: v.detach().numpy() for k, v in layer.state_dict().items()}
+    out["keys"] = np.array(list(layer.state_dict().keys()))
+    out["dense"] = m.to_dense().detach().numpy()
+    x = torch.randn(10, 192)
+    out["x"] = x.numpy()
+    out["y"] = (x @ m.to_dense().t() + layer.bias).detach().numpy()
+    np.savez_compressed(os.path.join(OUT, "checkpoint.npz"), **out)
+
+
 if __name__ == "__main__":
+    gen_checkpoint()
     gen_indices()
     gen_replace()
     gen_dense()

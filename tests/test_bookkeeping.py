@@ -195,3 +195,74 @@ def test_patcher_names_cpu():
     mp.add_pattern("1", {"density": 0.5})
     with pytest.raises(Exception, match="not a Linear layer"):
         mp.patch_model(model)
+
+
+def _layer_shaped(weight, bias):
+    class LayerShaped(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = weight
+            self.bias = torch.nn.Parameter(bias)
+
+    return LayerShaped()
+
+
+def test_checkpoint_written_by_the_reference_loads(golden):
+    """tests/golden/checkpoint.npz is the state_dict the REFERENCE produces for one layer (keys of
+    reference block_sparse.py:23,58-65) after a block_replace, i.e. with slot order != row-major order.
+    Loading it into a matrix of this package built with another pattern must reproduce the reference's dense
+    weight exactly: the index buffers travel with the checkpoint."""
+    g = golden("checkpoint")
+    sd = {k: torch.from_numpy(g["sd/" + k]) for k in g["keys"]}
+    np.random.seed(7)
+    m = BlockSparseMatrix.zeros((128, 192), n_blocks=9, device="cpu")
+    layer = _layer_shaped(m, torch.zeros(128))
+    assert sorted(layer.state_dict().keys()) == sorted(sd.keys())
+    assert not np.array_equal(m.blocks.numpy(), g["sd/weight.blocks"])
+    layer.load_state_dict(sd, strict=True)
+    assert np.array_equal(m.to_dense().detach().numpy(), g["dense"])
+    y = torch.from_numpy(g["x"]) @ m.to_dense().t() + layer.bias
+    assert np.allclose(y.detach().numpy(), g["y"], rtol=1e-6, atol=1e-6)
+    # and back out: what this package saves is what the reference saved
+    for k, v in layer.state_dict().items():
+        assert np.array_equal(v.numpy(), g["sd/" + k]), k
+
+
+@pytest.mark.parametrize("block_shape", [(32, 32), (64, 64)])
+def test_bsr_round_trip(block_shape):
+    np.random.seed(8)
+    torch.manual_seed(8)
+    m = BlockSparseMatrix.randn((256, 384), n_blocks=7, block_shape=block_shape, device="cpu")
+    free = (~m.block_mask_build(None)).nonzero()
+    m.block_replace(torch.cat([free[:1], torch.tensor([[3]])], -1))  # slot order != row-major order
+    bsr = m.to_bsr()
+    assert bsr.layout == torch.sparse_bsr
+    assert torch.equal(bsr.to_dense(), m.to_dense())
+    back = BlockSparseMatrix.from_bsr(bsr)
+    assert torch.equal(back.to_dense(), m.to_dense())
+    assert torch.equal(back.row_start_ends_a, m.row_start_ends_a)
+    assert torch.equal(back.cols_a[:, 0], m.cols_a[:, 0])
+    assert torch.equal(back.col_start_ends_b, m.col_start_ends_b)
+    assert torch.equal(back.rows_b[:, 0], m.rows_b[:, 0])
+    # a BSR tensor whose columns are not sorted inside a row
+    crow = torch.tensor([0, 2, 2]); col = torch.tensor([1, 0]); vals = torch.randn(2, 32, 32)
+    odd = torch.sparse_bsr_tensor(crow, col, vals, size=(64, 64))
+    got = BlockSparseMatrix.from_bsr(odd)
+    want = torch.zeros(64, 64); want[:32, 32:] = vals[0]; want[:32, :32] = vals[1]
+    assert torch.equal(got.to_dense(), want)
+
+
+def test_larger_square_blocks_expand_to_the_same_non_zeros():
+    """64x64 and 128x128 matrices run on the 32x32 kernels through a derived fine matrix: same dense matrix,
+    and the two re-tilings are inverse to each other."""
+    for b in (64, 128):
+        np.random.seed(b)
+        torch.manual_seed(b)
+        m = BlockSparseMatrix.randn((256, 512), n_blocks=3, block_shape=(b, b), device="cpu")
+        fine = m._fine_matrix()
+        assert fine.block_shape == (32, 32) and fine.data.shape[0] == m.data.shape[0] * (b // 32)
+        with torch.no_grad():
+            fine.data.copy_(m._to_fine(m.data.detach()))
+        assert torch.equal(fine.to_dense(), m.to_dense())
+        assert torch.equal(m._from_fine(fine.data), m.data.detach())
+        assert "_fine" not in "".join(m.state_dict().keys())

@@ -12,6 +12,8 @@ import torch
 from oracle import block_sparse_oracle as orc
 from pytorch_block_sparse_b200 import native
 
+from oracle import ref_cuda
+
 from .gpu_util import TOL, assert_device_healthy, check, host, make_matrix, randn
 
 pytestmark = pytest.mark.gpu
@@ -355,20 +357,23 @@ def _rel_fro_gpu(got, want):
     return float((got.double() - want.double()).norm() / want.double().norm())
 
 
-@pytest.mark.parametrize("precision", ["tf32x3", "tf32", "bf16"])
-def test_full_size_config3(precision):
-    """Benchmark configuration 3 at density 0.25 in full (4096 x 4096, 4096 blocks, 16384 tokens): every persistent
-    CTA walks ~28 tiles.  The numpy oracle is too slow for the whole problem, so the tensor-core kernels are
-    compared (a) with the exact-fp32 CUDA-core kernels on the device, which the small cases pin to the
-    oracle, (b) with the oracle on a sample of 96 token rows / 8 blocks, and (c) through properties that do
-    not depend on the size: scaling an input by 4 scales the result by exactly 4, and permuting the token
-    rows permutes forward rows / leaves the weight gradient within rounding."""
+def _full_size_case(shape, n_blocks, tokens, precision, seed, check_reference_kernels=False, golden_pattern=None):
+    """One benchmark configuration at its full size, checked three ways.  The numpy oracle is too slow for the
+    whole problem, so the tensor-core kernels are compared (a) with the exact-fp32 CUDA-core kernels on the
+    device, which the small cases pin to the oracle, (b) with the oracle on a sample of 96 token rows / 8
+    blocks, (c) through properties that do not depend on the size: scaling an input by 4 scales the result by
+    exactly 4, and permuting the token rows permutes forward rows / leaves the weight gradient within rounding,
+    and optionally (d) with the reference's own CUDA kernels where they were built."""
     tol = TOL[precision]
-    m = make_matrix((4096, 4096), n_blocks=4096, seed=51)
-    g = torch.Generator().manual_seed(52)
-    x = torch.randn(16384, 4096, generator=g).cuda()
-    dy = torch.randn(16384, 4096, generator=g).cuda()
-    bias = (torch.randn(4096, generator=g) * 0.02).cuda()
+    n_out, n_in = shape
+    m = make_matrix(shape, n_blocks=n_blocks, seed=seed)
+    if golden_pattern is not None:  # the pattern is the one the reference draws from this seed
+        for key in ("blocks", "cols_a", "row_start_ends_a", "rows_b", "col_start_ends_b"):
+            assert np.array_equal(getattr(m, key).cpu().numpy(), golden_pattern[key]), key
+    g = torch.Generator().manual_seed(seed + 1)
+    x = torch.randn(tokens, n_in, generator=g).cuda()
+    dy = torch.randn(tokens, n_out, generator=g).cuda()
+    bias = (torch.randn(n_out, generator=g) * 0.02).cuda()
 
     y = m.reverse_matmul(x, transpose=True, bias=bias, precision=precision)
     dx = m.reverse_matmul(dy, transpose=False, precision=precision)
@@ -381,28 +386,76 @@ def test_full_size_config3(precision):
         assert torch.isfinite(got).all(), what
         err = _rel_fro_gpu(got, want)
         assert err <= tol, f"{what}: {err:.3e}"
+    del y_ref, dx_ref
 
     # (b) oracle on a sample: 96 token rows spread over the range; 8 blocks of the weight gradient
-    shape, blocks, data = host(m)
-    rows = torch.arange(0, 16384, 171)[:96]
-    want = orc.forward(x[rows].cpu().numpy(), shape, blocks, data, bias.cpu().numpy())
+    shp, blocks, data = host(m)
+    rows = torch.arange(0, tokens, max(1, tokens // 96))[:96]
+    want = orc.forward(x[rows].cpu().numpy(), shp, blocks, data, bias.cpu().numpy())
     assert orc.rel_fro(y[rows].cpu().numpy(), want) <= tol
-    want = orc.dgrad(dy[rows].cpu().numpy(), shape, blocks, data)
+    want = orc.dgrad(dy[rows].cpu().numpy(), shp, blocks, data)
     assert orc.rel_fro(dx[rows].cpu().numpy(), want) <= tol
     dw_blocks = dw.view(-1, 32, 32)
     coo = blocks.reshape(-1, 2)
-    for s in range(0, 4096, 512):
+    for s in range(0, n_blocks, max(1, n_blocks // 8)):
         c, r = int(coo[s, 0]), int(coo[s, 1])
         want = (x[:, c * 32:(c + 1) * 32].double().t() @ dy[:, r * 32:(r + 1) * 32].double()).cpu().numpy()
         assert orc.rel_fro(dw_blocks[s].cpu().numpy(), want) <= tol, s
+
+    # (d) the reference's own CUDA kernels (int indexing: tokens x features below 2^31)
+    if check_reference_kernels and ref_cuda.available() and tokens * max(n_out, n_in) < 2 ** 31 and tokens % 32 == 0:
+        torch.cuda.synchronize()
+        ref_y = ref_cuda.reverse_matmul(m, x, True) + bias
+        ref_dx = ref_cuda.reverse_matmul(m, dy, False)
+        ref_dw = ref_cuda.sddmm(m, dy, x)
+        torch.cuda.synchronize()  # the reference launches on the legacy default stream
+        assert _rel_fro_gpu(y, ref_y) <= tol and _rel_fro_gpu(dx, ref_dx) <= tol and _rel_fro_gpu(dw, ref_dw) <= tol
+        del ref_y, ref_dx, ref_dw
+    del dx, dw_ref
 
     # (c) size-independent properties
     y0 = m.reverse_matmul(x, transpose=True, precision=precision)
     y4 = m.reverse_matmul(x * 4.0, transpose=True, precision=precision)
     assert torch.equal(y4, y0 * 4.0)  # powers of two commute with every rounding step
-    perm = torch.randperm(16384, generator=g).cuda()
+    del y4
+    perm = torch.randperm(tokens, generator=g).cuda()
     yp = m.reverse_matmul(x[perm].contiguous(), transpose=True, precision=precision)
     assert torch.equal(yp, y0[perm])  # a token's result does not depend on its position
+    del yp, y0
     dwp = m.matmul_with_output_sparse_support(dy[perm].contiguous(), x[perm].contiguous(), precision=precision)
     assert _rel_fro_gpu(dwp, dw) <= tol  # a sum over tokens in another order
     assert_device_healthy()
+
+
+@pytest.mark.parametrize("precision", ["tf32x3", "tf32", "bf16"])
+def test_full_size_config3(precision):
+    """Benchmark configuration 3 at density 0.25 in full (4096 x 4096, 4096 blocks, 16384 tokens): every
+    persistent CTA walks ~28 tiles."""
+    _full_size_case((4096, 4096), 4096, 16384, precision, seed=51, check_reference_kernels=precision == "tf32x3")
+
+
+@pytest.mark.parametrize("density", [0.1, 0.5, 0.75])
+def test_full_size_config3_density_sweep(density):
+    """The other densities of benchmark configuration 3 in the default precision: rows of 13 (d = 0.1) to 96
+    (d = 0.75) blocks, i.e. no promotion at all up to three promotions per row and tile."""
+    _full_size_case((4096, 4096), int(density * 4096 * 4096 / 1024), 16384, "tf32x3", seed=61 + int(density * 100),
+                    check_reference_kernels=True)
+
+
+@pytest.mark.parametrize("shape", [(3072, 768), (768, 3072)])
+def test_full_size_config2(shape, golden):
+    """Benchmark configuration 2: the two RoBERTa-base FFN layers (768 -> 3072 and 3072 -> 768, density 0.5) on
+    4096 tokens.  The 768 x 3072 pattern is the one the reference itself draws from numpy seed 2 (committed
+    fixture), so the whole chain pattern -> indices -> plans -> kernels is pinned to the reference here."""
+    pattern = None
+    if shape == (768, 3072):
+        idx = golden("indices")
+        name = "random_s2_768x3072_n1152"
+        pattern = {k: idx[name + "/" + k] for k in ("blocks", "cols_a", "row_start_ends_a", "rows_b", "col_start_ends_b")}
+    _full_size_case(shape, 1152, 4096, "tf32x3", seed=2, check_reference_kernels=True, golden_pattern=pattern)
+
+
+def test_full_size_config5_shard():
+    """One GPU's block-row shard of benchmark configuration 5 (32768 x 8192 at density 0.1 over 8 GPUs:
+    4096 x 8192 per GPU) on its 65536 tokens: 512 token tiles, 8 token ranges in the weight gradient."""
+    _full_size_case((4096, 8192), int(0.1 * 4096 * 8192 / 1024), 65536, "tf32x3", seed=71)

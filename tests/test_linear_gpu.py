@@ -240,3 +240,97 @@ def test_kernels_run_on_the_callers_stream():
     side.synchronize()
     assert torch.equal(xs.grad, want[0])
     assert torch.allclose(lin.weight.data.grad, want[1], rtol=1e-5, atol=1e-6)
+
+
+def test_writes_through_dot_data_are_seen_by_the_next_forward():
+    """``p.data.mul_()`` does not bump autograd's version counter (fused optimizers, EMA copies and
+    ``weight.data.data[...] = ...`` write this way).  The layer packs its weight images on every forward, so the
+    tensor-core paths cannot run on stale images; the opt-in cache (``fresh=False``) is dropped by
+    ``invalidate_packed()``."""
+    np.random.seed(21)
+    torch.manual_seed(21)
+    lin = BlockSparseLinear(128, 96, bias=False, density=0.5)
+    x = torch.randn(40, 128, device="cuda")
+    y0 = lin(x).detach().clone()
+    version = lin.weight.data._version
+    lin.weight.data.data.mul_(2.0)
+    assert lin.weight.data._version == version  # the write is invisible to the version counter
+    y1 = lin(x).detach()
+    assert torch.allclose(y1, 2.0 * y0, rtol=1e-6, atol=0)
+    # dgrad uses the images of its own forward
+    xg = x.clone().requires_grad_(True)
+    lin(xg).sum().backward()
+    want = torch.ones(40, 96, device="cuda") @ lin.weight.to_dense()
+    assert torch.allclose(xg.grad, want, rtol=1e-4, atol=1e-5)
+    # the opt-in cache, and its invalidation
+    w = lin.weight
+    cached = w.packed_weights(fresh=False)
+    assert w.packed_weights(fresh=False) is cached
+    w.data.data.mul_(0.5)
+    assert w.packed_weights(fresh=False) is cached  # stale by design until told
+    w.invalidate_packed()
+    assert w.packed_weights(fresh=False) is not cached
+    y2 = w.reverse_matmul(x, transpose=True, packed=w.packed_weights(fresh=False))
+    assert torch.allclose(y2, y0, rtol=1e-6, atol=0)
+
+
+def test_block_norm_comes_from_the_statistic_kernel():
+    np.random.seed(22)
+    torch.manual_seed(22)
+    lin = BlockSparseLinear(256, 128, bias=False, density=0.5)
+    w = lin.weight
+    want = torch.norm(w.data.detach().reshape(-1, 32, 32), p=2, dim=(1, 2))
+    assert torch.allclose(w.block_norm(), want, rtol=1e-5)
+    assert torch.allclose(w.block_norm(p=1), torch.norm(w.data.detach().reshape(-1, 32, 32), p=1, dim=(1, 2)), rtol=1e-5)
+    # the weight gradient's statistic is kept beside the matrix
+    x = torch.randn(64, 256, device="cuda", requires_grad=True)
+    lin(x).sum().backward()
+    g = w.data.grad.reshape(-1, 32, 32)
+    assert torch.allclose(w.last_grad_block_sumsq, (g * g).sum((1, 2)), rtol=1e-4)
+
+
+def test_checkpoint_written_by_the_reference_runs_on_the_kernels(golden):
+    g = golden("checkpoint")
+    np.random.seed(23)
+    lin = BlockSparseLinear(192, 128, bias=True, density=9 / 24)
+    assert lin.weight.data.shape == g["sd/weight.data"].shape
+    lin(torch.randn(4, 192, device="cuda"))  # plans of the constructor's own pattern are cached now
+    lin.load_state_dict({k: torch.from_numpy(g["sd/" + k]) for k in g["keys"]}, strict=True)
+    y = lin(torch.from_numpy(g["x"]).cuda())
+    err = float((y.detach().cpu().double() - torch.from_numpy(g["y"]).double()).norm() / np.linalg.norm(g["y"]))
+    assert err <= 1e-5, err
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("block", [64, 128])
+def test_larger_square_blocks_on_the_tensor_core_kernels(block):
+    """A layer with 64x64 / 128x128 blocks (the reference serves them with its dense-masked emulator,
+    block_sparse_linear.py:202-205): forward, input gradient and weight gradient against the dense masked layer."""
+    np.random.seed(block)
+    torch.manual_seed(block)
+    lin = BlockSparseLinear(512, 384, bias=True, density=0.5, block_shape=(block, block))
+    assert isinstance(lin.weight, BlockSparseMatrix) and lin.weight.block_shape == (block, block)
+    with torch.no_grad():
+        lin.weight.data.normal_(0, 0.05)
+        lin.bias.normal_(0, 0.05)
+    dense = lin.weight.to_dense().detach().double()
+    mask = lin.weight.to_dense(data_replace=torch.ones_like(lin.weight.data)).double()
+    x = torch.randn(3, 70, 512, device="cuda", requires_grad=True)
+    dy = torch.randn(3, 70, 384, device="cuda")
+    y = lin(x)
+    y.backward(dy)
+    xd, dyd = x.detach().double().reshape(-1, 512), dy.double().reshape(-1, 384)
+
+    def rel(got, want):
+        return float((got.double() - want).norm() / want.norm())
+
+    assert rel(y.detach().reshape(-1, 384), xd @ dense.t() + lin.bias.detach().double()) <= 1e-5
+    assert rel(x.grad.reshape(-1, 512), dyd @ dense) <= 1e-5
+    want_dw = (dyd.t() @ xd) * mask
+    got_dw = lin.weight.to_dense(data_replace=lin.weight.data.grad).double()
+    assert rel(got_dw, want_dw) <= 1e-5
+    assert rel(lin.bias.grad, dyd.sum(0)) <= 1e-5
+    norms = lin.weight.block_norm()
+    want_norms = torch.norm(lin.weight.data.detach().reshape(-1, block, block), dim=(1, 2))
+    assert torch.allclose(norms, want_norms, rtol=1e-5)
+    assert_device_healthy()
