@@ -150,6 +150,38 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
                void* workspace, uint32_t flags, bsmm_stream_t stream);
 
 /*
+ * Pattern maintenance on the device (no host round trip, nothing allocated).  Together these replace the
+ * tensor-op sequences of BlockSparseMatrixBase.build_indices / block_replace (reference
+ * block_sparse.py:85-153, :167-219) and of MagnitudeSparseOptimizerStrategy.run (reference
+ * sparse_optimizer.py:38-87).  A block position ("cell") is block-row * n_block_cols + block-col.
+ * `status` is a DEVICE int32 the kernels OR flags into (the caller zeroes it and reads it when it wants
+ * the check): 1 = two slots at one position, 2 = a position or slot out of range, 4 = the number of
+ * empty cells differs from `n_free`.
+ *
+ * bsmm_rebuild_indices: from `blocks` (int32 [2*nnz], (block-col, block-row) per slot) the CSR arrays
+ *   row_ptr int32 [n_block_rows+1], cols_a int32 [nnz,2] = (block-col, slot) sorted by (row, col), and the
+ *   CSC arrays col_ptr int32 [n_block_cols+1], rows_b int32 [nnz,2] = (block-row, slot) sorted by (col, row)
+ *   -- bit-identical to the reference's buffers for the same pattern.  `cell_slot` (int32
+ *   [n_block_rows*n_block_cols], scratch and result) receives the slot at every position, -1 where empty.
+ * bsmm_select_lowest: out_idx int32 [k] = the k indices of smallest stat[0..n) (ties in index order; first the
+ *   elements strictly below the k-th smallest value in index order, then the ties).  Used on the per-slot sums
+ *   of squares to choose the blocks a pruning step recycles.
+ * bsmm_sample_free_cells: out_cells int32 [k] = k distinct empty positions of `cell_slot`, uniformly at random,
+ *   a pure function of (pattern, seed): every rank of a data-parallel job that passes the same seed draws
+ *   the same positions.  n_free must equal the number of empty cells (cells - nnz); free_cells int32 [n_free]
+ *   is scratch.
+ * bsmm_move_blocks: blocks[slots[j]] = position cells[j] for j < k (then call bsmm_rebuild_indices).
+ */
+int bsmm_rebuild_indices(const int32_t* blocks, int64_t nnz, int64_t n_block_rows, int64_t n_block_cols,
+                         int32_t* cell_slot, int32_t* row_ptr, int32_t* cols_a, int32_t* col_ptr, int32_t* rows_b,
+                         int32_t* status, bsmm_stream_t stream);
+int bsmm_select_lowest(const float* stat, int64_t n, int64_t k, int32_t* out_idx, bsmm_stream_t stream);
+int bsmm_sample_free_cells(const int32_t* cell_slot, int64_t cells, int64_t n_free, int64_t k, uint64_t seed,
+                           int32_t* free_cells, int32_t* out_cells, int32_t* status, bsmm_stream_t stream);
+int bsmm_move_blocks(int32_t* blocks, const int32_t* slots, const int32_t* cells, int64_t k, int64_t n_block_cols,
+                     int64_t nnz, int32_t* status, bsmm_stream_t stream);
+
+/*
  * bsmm_sddmm for callers that cannot allocate device memory.  No counterpart in the reference.
  *
  * Some hosts of this library may not call cudaMalloc at the point where the weight gradient is

@@ -49,6 +49,7 @@ class BlockSparseMatrixBase(torch.nn.Module):
         state = dict(super().__getstate__() if hasattr(super(), "__getstate__") else self.__dict__)
         state["_plan_cache"] = {}
         state["_pack_cache"] = {}
+        state.pop("_cells", None)
         return state
 
     # ------------------------------------------------------------------ hooks
@@ -139,6 +140,7 @@ class BlockSparseMatrixBase(torch.nn.Module):
         self.sanity_check(self.rows_b, self.col_start_ends_b, self.shape[::-1], self.block_shape[::-1])
         self.check_ = False
         self._plan_cache = {}
+        self.__dict__.pop("_cells", None)
         if callback:
             self.updated_data()
 
@@ -200,7 +202,16 @@ class BlockSparseMatrixBase(torch.nn.Module):
         return mask
 
     def block_replace(self, block_replacements):
-        """Move slots to new positions: rows of ``(block-row, block-col, slot)`` (reference ``block_sparse.py:167-219``)."""
+        """Move slots to new positions: rows of ``(block-row, block-col, slot)`` (reference ``block_sparse.py:167-219``).
+
+        On a GPU the move and the re-indexing are two kernels of the library writing the existing buffers in
+        place (:meth:`move_blocks_`); the checking mode (``check_``) and CPU matrices use torch ops on the host
+        side, as the reference does.  Both give bit-identical buffers."""
+        if self.data.is_cuda and not self.check_ and self.blocks.numel() > 0:
+            repl = block_replacements.to(device=self.data.device, dtype=torch.long)
+            _, Y = self.blocks_count()
+            self.move_blocks_(repl[:, 2].to(torch.int32).contiguous(), (repl[:, 0] * Y + repl[:, 1]).to(torch.int32).contiguous())
+            return
         pos = self.build_coo_block_index().long()
         repl = block_replacements.to(dtype=torch.long, device=pos.device)
         _, Y = self.blocks_count()
@@ -218,6 +229,56 @@ class BlockSparseMatrixBase(torch.nn.Module):
         # slot of the i-th set position in row-major order
         block_ptr = torch.argsort(pos[0] * Y + pos[1])
         self.rebuild(new_mask, block_ptr)
+
+    # ------------------------------------------------------- pattern kernels (GPU)
+    def _pattern_scratch(self):
+        """``(cell_slot, status)``: the slot at every block position (-1 where empty) as the pattern kernels
+        keep it, and their device-side flag word; created (and filled) on first use per pattern."""
+        cached = self.__dict__.get("_cells")
+        X, Y = self.blocks_count()
+        if cached is None or cached[0].device != self.data.device or cached[0].numel() != X * Y:
+            cell_slot = torch.empty(X * Y, dtype=torch.int32, device=self.data.device)
+            status = torch.zeros(1, dtype=torch.int32, device=self.data.device)
+            self.__dict__["_cells"] = cached = (cell_slot, status)
+            self._rebuild_indices_device()
+        return cached
+
+    def _rebuild_indices_device(self):
+        cell_slot, status = self.__dict__["_cells"]
+        X, Y = self.blocks_count()
+        native.rebuild_indices(
+            self.blocks, X, Y, cell_slot, self.row_start_ends_a, self.cols_a, self.col_start_ends_b, self.rows_b, status
+        )
+        self._plan_cache = {}
+
+    def pattern_status(self):
+        """Flag word of the pattern kernels since the last call (synchronizes): 0, or 1 = two slots at one
+        position, 2 = position or slot out of range, 4 = empty-cell count mismatch."""
+        _, status = self._pattern_scratch()
+        value = int(status.item())
+        status.zero_()
+        return value
+
+    def sample_free_positions(self, k, seed):
+        """int32 ``[k]`` distinct empty block positions (``row * Y + col``), a pure function of the pattern and
+        ``seed`` (``bsmm_sample_free_cells``)."""
+        cell_slot, status = self._pattern_scratch()
+        X, Y = self.blocks_count()
+        return native.sample_free_cells(cell_slot, X * Y - self.blocks.shape[0] // 2, k, seed, status)
+
+    def move_blocks_(self, slots, positions):
+        """Slots ``slots[j]`` (int32) move to block positions ``positions[j]`` (int32 ``row * Y + col``); ``blocks``,
+        the CSR and the CSC buffers are rewritten in place by the library's kernels, no host round trip."""
+        _, status = self._pattern_scratch()
+        _, Y = self.blocks_count()
+        native.move_blocks(self.blocks, slots, positions, Y, status)
+        self._rebuild_indices_device()
+        self._pattern_changed()
+
+    def _pattern_changed(self):
+        """Derived state keyed on the index buffers is dropped (kernels wrote them behind the version counters)."""
+        self._plan_cache = {}
+        self.updated_data()
 
     # ------------------------------------------------------------------ factories
     @classmethod
@@ -579,6 +640,10 @@ class BlockSparseMatrix(BlockSparseMatrixBase):
     def rebuild(self, block_mask, block_ptr=None, callback=True):
         super().rebuild(block_mask, block_ptr, callback)
         object.__setattr__(self, "_fine", None)
+
+    def _pattern_changed(self):
+        object.__setattr__(self, "_fine", None)
+        super()._pattern_changed()
 
     def _fine_matrix(self):
         """The 32x32 matrix of the same non-zeros.  Fine slot ``(s * nb + i) * nb + j`` is the sub-block at

@@ -186,6 +186,49 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
                                                b_col, rows, cols, tokens, sparse_c, blocks, nnz, block_sumsq, s));
 }
 
+int bsmm_rebuild_indices(const int32_t* blocks, int64_t nnz, int64_t n_block_rows, int64_t n_block_cols,
+                         int32_t* cell_slot, int32_t* row_ptr, int32_t* cols_a, int32_t* col_ptr, int32_t* rows_b,
+                         int32_t* status, bsmm_stream_t stream) {
+    forget_earlier_errors();
+    if (nnz < 0 || n_block_rows <= 0 || n_block_cols <= 0) return BSMM_ERR_INVALID_ARGUMENT;
+    if (cell_slot == nullptr || row_ptr == nullptr || col_ptr == nullptr || status == nullptr ||
+        (nnz > 0 && (blocks == nullptr || cols_a == nullptr || rows_b == nullptr)))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (!aligned(blocks, 8) || !aligned(cols_a, 8) || !aligned(rows_b, 8)) return BSMM_ERR_INVALID_ARGUMENT;
+    if (n_block_rows > 0x7fffffff / n_block_cols || nnz > n_block_rows * n_block_cols) return BSMM_ERR_TOO_LARGE;
+    return cuda_status(bsmm::launch_rebuild_indices(blocks, nnz, n_block_rows, n_block_cols, cell_slot, row_ptr, cols_a,
+                                                    col_ptr, rows_b, status, static_cast<cudaStream_t>(stream)));
+}
+
+int bsmm_select_lowest(const float* stat, int64_t n, int64_t k, int32_t* out_idx, bsmm_stream_t stream) {
+    forget_earlier_errors();
+    if (n < 0 || k < 0 || k > n || (k > 0 && (stat == nullptr || out_idx == nullptr))) return BSMM_ERR_INVALID_ARGUMENT;
+    if (n > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
+    return cuda_status(bsmm::launch_select_lowest(stat, n, k, out_idx, static_cast<cudaStream_t>(stream)));
+}
+
+int bsmm_sample_free_cells(const int32_t* cell_slot, int64_t cells, int64_t n_free, int64_t k, uint64_t seed,
+                           int32_t* free_cells, int32_t* out_cells, int32_t* status, bsmm_stream_t stream) {
+    forget_earlier_errors();
+    if (cells <= 0 || n_free < 0 || n_free > cells || k < 0 || k > n_free) return BSMM_ERR_INVALID_ARGUMENT;
+    if (cell_slot == nullptr || status == nullptr || (k > 0 && (free_cells == nullptr || out_cells == nullptr)))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (cells > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
+    return cuda_status(bsmm::launch_sample_free_cells(cell_slot, cells, n_free, k, seed, free_cells, out_cells, status,
+                                                      static_cast<cudaStream_t>(stream)));
+}
+
+int bsmm_move_blocks(int32_t* blocks, const int32_t* slots, const int32_t* cells, int64_t k, int64_t n_block_cols,
+                     int64_t nnz, int32_t* status, bsmm_stream_t stream) {
+    forget_earlier_errors();
+    if (k < 0 || nnz < 0 || n_block_cols <= 0 || status == nullptr ||
+        (k > 0 && (blocks == nullptr || slots == nullptr || cells == nullptr)))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    if (!aligned(blocks, 8)) return BSMM_ERR_INVALID_ARGUMENT;
+    return cuda_status(bsmm::launch_move_blocks(blocks, slots, cells, k, n_block_cols, nnz, status,
+                                                static_cast<cudaStream_t>(stream)));
+}
+
 int bsmm_sddmm_static(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens, float* sparse_c,
                       const int32_t* blocks, int64_t nnz, const int32_t* csr_idx, const void* plan,
                       float* block_sumsq, uint32_t flags, bsmm_stream_t stream) {

@@ -56,4 +56,14 @@ cudaError_t launch_pack(const float* data, int64_t nnz, uint32_t precision, void
                         cudaStream_t stream);
 cudaError_t launch_block_sumsq(const float* data, int64_t nnz, float* block_sumsq, cudaStream_t stream);
 
+// pattern maintenance (bsmm_pattern.cu)
+cudaError_t launch_rebuild_indices(const int32_t* blocks, int64_t nnz, int64_t n_rows, int64_t n_cols,
+                                   int32_t* cell_slot, int32_t* row_ptr, int32_t* cols_a, int32_t* col_ptr,
+                                   int32_t* rows_b, int32_t* status, cudaStream_t stream);
+cudaError_t launch_select_lowest(const float* stat, int64_t n, int64_t k, int32_t* out, cudaStream_t stream);
+cudaError_t launch_sample_free_cells(const int32_t* cell_slot, int64_t cells, int64_t n_free, int64_t k, uint64_t seed,
+                                     int32_t* free_cells, int32_t* out_cells, int32_t* status, cudaStream_t stream);
+cudaError_t launch_move_blocks(int32_t* blocks, const int32_t* slots, const int32_t* cells, int64_t k, int64_t n_cols,
+                               int64_t nnz, int32_t* status, cudaStream_t stream);
+
 }  // namespace bsmm

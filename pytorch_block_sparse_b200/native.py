@@ -37,6 +37,10 @@ EXPORTS = (
     "bsmm_sddmm_workspace_bytes",
     "bsmm_sddmm",
     "bsmm_sddmm_static",
+    "bsmm_rebuild_indices",
+    "bsmm_select_lowest",
+    "bsmm_sample_free_cells",
+    "bsmm_move_blocks",
 )
 
 _lib = None
@@ -92,6 +96,14 @@ def load():
     lib.bsmm_sddmm_plan_bytes.argtypes = [i64, i64]
     lib.bsmm_build_sddmm_plan.restype = i32
     lib.bsmm_build_sddmm_plan.argtypes = [vp, i64, i64, vp, vp]
+    lib.bsmm_rebuild_indices.restype = i32
+    lib.bsmm_rebuild_indices.argtypes = [vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp]
+    lib.bsmm_select_lowest.restype = i32
+    lib.bsmm_select_lowest.argtypes = [vp, i64, i64, vp, vp]
+    lib.bsmm_sample_free_cells.restype = i32
+    lib.bsmm_sample_free_cells.argtypes = [vp, i64, i64, i64, c.c_uint64, vp, vp, vp, vp]
+    lib.bsmm_move_blocks.restype = i32
+    lib.bsmm_move_blocks.argtypes = [vp, vp, vp, i64, i64, i64, vp, vp]
     if lib.bsmm_abi_version() != ABI_VERSION:
         raise NativeError("libbsmm_b200.so has ABI %d, this package expects %d" % (lib.bsmm_abi_version(), ABI_VERSION))
     _lib = lib
@@ -187,6 +199,61 @@ def block_sumsq(data):
         check(lib.bsmm_pack_weights(_ptr(raw), nnz, PREC_FP32_SIMT, None, _ptr(sumsq), _stream(data.device)),
               "bsmm_pack_weights")
     return sumsq
+
+
+def rebuild_indices(blocks, n_block_rows, n_block_cols, cell_slot, row_ptr, cols_a, col_ptr, rows_b, status):
+    """``bsmm_rebuild_indices``: CSR / CSC buffers (written in place) from the slot-order ``blocks`` list."""
+    _need_cuda(blocks, "blocks")
+    lib = load()
+    with torch.cuda.device(blocks.device):
+        check(
+            lib.bsmm_rebuild_indices(
+                _ptr(blocks), blocks.shape[0] // 2, n_block_rows, n_block_cols, _ptr(cell_slot), _ptr(row_ptr),
+                _ptr(cols_a), _ptr(col_ptr), _ptr(rows_b), _ptr(status), _stream(blocks.device),
+            ),
+            "bsmm_rebuild_indices",
+        )
+
+
+def select_lowest(stat, k):
+    """``bsmm_select_lowest``: int32 ``[k]`` indices of the ``k`` smallest entries of the fp32 vector ``stat``."""
+    _need_cuda(stat, "stat")
+    lib = load()
+    stat = stat.detach().contiguous()
+    out = torch.empty(k, dtype=torch.int32, device=stat.device)
+    with torch.cuda.device(stat.device):
+        check(lib.bsmm_select_lowest(_ptr(stat), stat.shape[0], k, _ptr(out), _stream(stat.device)), "bsmm_select_lowest")
+    return out
+
+
+def sample_free_cells(cell_slot, n_free, k, seed, status):
+    """``bsmm_sample_free_cells``: int32 ``[k]`` distinct empty positions of ``cell_slot``, a function of the seed."""
+    _need_cuda(cell_slot, "cell_slot")
+    lib = load()
+    scratch = torch.empty(max(n_free, 1), dtype=torch.int32, device=cell_slot.device)
+    out = torch.empty(k, dtype=torch.int32, device=cell_slot.device)
+    with torch.cuda.device(cell_slot.device):
+        check(
+            lib.bsmm_sample_free_cells(
+                _ptr(cell_slot), cell_slot.numel(), n_free, k, ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), _ptr(scratch),
+                _ptr(out), _ptr(status), _stream(cell_slot.device),
+            ),
+            "bsmm_sample_free_cells",
+        )
+    return out
+
+
+def move_blocks(blocks, slots, cells, n_block_cols, status):
+    """``bsmm_move_blocks``: ``blocks[slots[j]]`` becomes position ``cells[j]`` (in place)."""
+    lib = load()
+    with torch.cuda.device(blocks.device):
+        check(
+            lib.bsmm_move_blocks(
+                _ptr(blocks), _ptr(slots), _ptr(cells), slots.shape[0], n_block_cols, blocks.shape[0] // 2, _ptr(status),
+                _stream(blocks.device),
+            ),
+            "bsmm_move_blocks",
+        )
 
 
 class DsdPlan:
