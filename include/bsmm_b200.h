@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define BSMM_ABI_VERSION 1
+#define BSMM_ABI_VERSION 2
 
 /* status codes */
 #define BSMM_OK 0
@@ -56,6 +56,7 @@ extern "C" {
 #define BSMM_DSD_DGRAD 0x10u        /* 0: out = a * W^T (CSR given); 1: out = a * W (CSC given) */
 #define BSMM_DSD_OUT_COLMAJOR 0x20u /* 0: out is [m, n] row-major; 1: out is [n, m] (the reference's buffer) */
 #define BSMM_DSD_GROUP(g) (((uint32_t)(g)&0xFFu) << 8) /* group size the plan was built with (tensor-core precisions) */
+#define BSMM_DSD_GELU 0x40u         /* bsmm_dsd_fused only: out = gelu(a * W^T + bias + residual), erf form */
 
 /* bsmm_sddmm flags */
 #define BSMM_SDDMM_A_COLMAJOR 0x10u /* dY given as [rows, tokens] contiguous instead of [tokens, rows] */
@@ -124,6 +125,22 @@ int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks
 int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
              const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
              uint32_t flags, bsmm_stream_t stream);
+
+/*
+ * bsmm_dsd with the layer's neighbours fused into the forward epilogue (tensor-core precisions, row-major
+ * output, forward only).  The reference fuses nothing: its layer adds the bias in a separate pass
+ * (block_sparse_linear.py:229-233) and a transformer then runs the activation or the residual add as further
+ * elementwise kernels over the same [m, n] tensor.
+ *   out = act(a * W^T + bias + residual)
+ * residual: fp32 [m, n] row-major or NULL.  act = GELU (erf form) with BSMM_DSD_GELU, else identity.
+ * pre_activation (fp32 [m, n] row-major or NULL, only with BSMM_DSD_GELU): receives a * W^T + bias + residual,
+ * what a backward pass needs for the activation's derivative.  Rows of more than 48 blocks are promoted from
+ * tensor memory in several parts; the parts then gather in pre_activation (in `out` itself when it is NULL) and
+ * the last part reads the total back before it applies the activation.
+ */
+int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+                   const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
+                   const float* residual, float* pre_activation, uint32_t flags, bsmm_stream_t stream);
 
 /*
  * Dense^T x dense -> block-sparse (SDDMM).  Replaces blocksparse_matmul_back_cutlass

@@ -569,6 +569,35 @@ class BlockSparseMatrixBase(torch.nn.Module):
             bias=bias,
         )
 
+    def reverse_matmul_fused(self, dense_a, bias=None, residual=None, activation=None, precision=None, packed=None,
+                             keep_pre=False):
+        """``act(a @ W.T + bias + residual)`` with everything after the product done in the forward kernel's
+        epilogue (tensor-core precisions).  Returns ``(out, pre)``: ``pre`` is the sum before the activation when
+        ``keep_pre`` and an activation are given, else ``None``.  The reference has no counterpart: its layer adds
+        the bias in a separate pass (``block_sparse_linear.py:229-233``)."""
+        self._require_cuda()
+        flat, lead = self.flatten_first_dims(dense_a)
+        if flat.shape[1] != self.shape[1]:
+            raise Exception(
+                "Invalid matrices sizes (%d, %d) x (%d, %d)" % (flat.shape[0], flat.shape[1], self.shape[1], self.shape[0])
+            )
+        if not flat.is_contiguous():
+            flat = flat.contiguous()
+        fine = self._fine_matrix() if getattr(self, "_is_coarse", lambda: False)() else self
+        if packed is None:
+            packed = self.packed_weights(precision)
+        pre = None
+        if keep_pre and activation is not None:
+            pre = torch.empty((flat.shape[0], self.shape[0]), dtype=torch.float32, device=flat.device)
+        out = native.dsd_matmul(
+            flat, fine._plan(True), packed, n_out=self.shape[0], transpose=True, bias=bias, residual=residual,
+            activation=activation, pre_activation=pre,
+        )
+        out = self.unflatten_first_dims(out, lead)
+        if pre is not None:
+            pre = self.unflatten_first_dims(pre, lead)
+        return out, pre
+
     def reverse_matmul(self, dense_a, transpose, bias=None, precision=None, packed=None):
         """Any-rank wrapper of :meth:`reverse_matmul_` (reference ``block_sparse.py:597-604``)."""
         self._require_cuda()

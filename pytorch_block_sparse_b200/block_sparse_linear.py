@@ -23,40 +23,67 @@ from .block_sparse import BlockSparseMatrix, BlockSparseMatrixBase, BlockSparseM
 
 
 class BlockSparseLinearFunction(torch.autograd.Function):
-    """``apply(input, weight_data, weight[, bias])``.
+    """``apply(input, weight_data, weight[, bias[, residual[, activation]]])``.
 
     ``weight_data`` is ``weight.get_differentiable_data()`` passed separately so that the
     Parameter receives the gradient (reference ``block_sparse_linear.py:15-53``, ``:154``).
-    The optional 4th argument fuses the bias add into the forward kernel.
+    The optional arguments are fused into the forward kernel's epilogue:
+    ``y = act(x @ W.T + bias + residual)`` with ``activation`` ``None`` or ``"gelu"`` (erf form).
+    With an activation the kernel also writes the pre-activation sum, which backward needs.
     """
 
     @staticmethod
-    def forward(ctx, input, weight_data, weight, *maybe_bias):
+    def forward(ctx, input, weight_data, weight, *extras):
         assert isinstance(weight, BlockSparseMatrixBase)
-        bias = maybe_bias[0] if maybe_bias else None
-        ctx.save_for_backward(input, weight_data)
+        bias = extras[0] if len(extras) > 0 else None
+        residual = extras[1] if len(extras) > 1 else None
+        activation = extras[2] if len(extras) > 2 else None
         ctx.weight = weight
-        ctx.n_extra = len(maybe_bias)
+        ctx.n_extra = len(extras)
         ctx.has_bias = bias is not None
+        ctx.has_residual = residual is not None
+        ctx.activation = activation
         # The weights are packed once per forward -- never from a cache keyed on autograd's version counter,
         # which writes through ``.data`` do not bump -- and backward reuses these images, i.e. the weights
         # the forward saw.
         ctx.packed = weight.packed_weights() if isinstance(weight, BlockSparseMatrix) else None
-        return weight.reverse_matmul(input, transpose=True, bias=bias, packed=ctx.packed)
+        fused = residual is not None or activation is not None
+        if not fused:
+            ctx.save_for_backward(input, weight_data)
+            return weight.reverse_matmul(input, transpose=True, bias=bias, packed=ctx.packed)
+        if not (isinstance(weight, BlockSparseMatrix) and ctx.packed.images is not None):
+            # emulated block shapes and the exact-fp32 CUDA-core precision have no fused epilogue
+            pre = weight.reverse_matmul(input, transpose=True, bias=bias, packed=ctx.packed)
+            if residual is not None:
+                pre = pre + residual
+            out = torch.nn.functional.gelu(pre) if activation == "gelu" else pre
+        else:
+            need_pre = activation is not None and any(ctx.needs_input_grad)
+            out, pre = weight.reverse_matmul_fused(
+                input, bias=bias, residual=residual, activation=activation, packed=ctx.packed, keep_pre=need_pre
+            )
+        ctx.save_for_backward(input, weight_data, pre if activation is not None else None)
+        return out
 
     @staticmethod
     def backward(ctx, grad_output):
-        input, weight_data = ctx.saved_tensors
+        saved = ctx.saved_tensors
+        input = saved[0]
         weight = ctx.weight
-        grad_input = grad_weight = grad_bias = None
+        if ctx.activation == "gelu":
+            grad_output = torch.ops.aten.gelu_backward(grad_output.contiguous(), saved[2].view_as(grad_output))
+        grad_input = grad_weight = grad_bias = grad_residual = None
+        # the weight gradient first: in data-parallel training its all-reduce can then overlap the input gradient
+        if ctx.needs_input_grad[1]:
+            grad_weight = weight.matmul_with_output_sparse_support(grad_output, input)
         if ctx.needs_input_grad[0]:
             grad_input = weight.reverse_matmul(grad_output, transpose=False, packed=ctx.packed)
             assert grad_input.shape == input.shape
-        if ctx.needs_input_grad[1]:
-            grad_weight = weight.matmul_with_output_sparse_support(grad_output, input)
         if ctx.has_bias and ctx.needs_input_grad[3]:
             grad_bias = grad_output.reshape(-1, grad_output.shape[-1]).sum(0)
-        return (grad_input, grad_weight, None, grad_bias)[: 3 + ctx.n_extra]
+        if ctx.has_residual and ctx.needs_input_grad[4]:
+            grad_residual = grad_output
+        return (grad_input, grad_weight, None, grad_bias, grad_residual, None)[: 3 + ctx.n_extra]
 
 
 class BlockSparseLinear(nn.Module):
@@ -80,11 +107,15 @@ class BlockSparseLinear(nn.Module):
         torch_nn_linear=None,
         verbose: bool = False,
         block_shape: Tuple[int, int] = (32, 32),
+        activation=None,
     ):
         super().__init__()
         self.fn = BlockSparseLinearFunction.apply
         self.verbose = verbose
         self.block_shape = block_shape
+        if activation not in (None, "gelu"):
+            raise Exception(f"BlockSparseLinear invalid activation={activation}, expected None or 'gelu'")
+        self.activation = activation  # not in the reference: applied inside the forward kernel's epilogue
         # 32x32 blocks and larger square multiples of 32 run on the CUDA kernels (the latter through their
         # 32x32 expansion); every other block shape uses the dense-masked emulator, as in the reference
         self._optimized = (
@@ -126,13 +157,19 @@ class BlockSparseLinear(nn.Module):
         else:
             self.register_parameter("bias", None)
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """``act(x @ W.T + bias + residual)``; ``residual`` (not in the reference) has the output's shape and is
+        added in the kernel's epilogue, like the bias and the layer's ``activation``."""
         if self._optimized:
-            return self.fn(x, self.weight.get_differentiable_data(), self.weight, self.bias)
+            if residual is None and self.activation is None:
+                return self.fn(x, self.weight.get_differentiable_data(), self.weight, self.bias)
+            return self.fn(x, self.weight.get_differentiable_data(), self.weight, self.bias, residual, self.activation)
         x = self.fn(x, self.weight.get_differentiable_data(), self.weight)
         if self.bias is not None:
             x = x + self.bias
-        return x
+        if residual is not None:
+            x = x + residual
+        return torch.nn.functional.gelu(x) if self.activation == "gelu" else x
 
     def extra_repr(self):
         return "in_features={}, out_features={}, bias={}, block_count={}".format(

@@ -101,40 +101,59 @@ int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks
         bsmm::launch_build_plan(ptr, idx, n_out_blocks, nnz, group, plan, static_cast<cudaStream_t>(stream)));
 }
 
-int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
-             const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
-             uint32_t flags, bsmm_stream_t stream) {
+int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+                   const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
+                   const float* residual, float* pre_activation, uint32_t flags, bsmm_stream_t stream) {
     forget_earlier_errors();
     const uint32_t precision = flags & BSMM_PREC_MASK;
     const bool dgrad = (flags & BSMM_DSD_DGRAD) != 0;
     const bool colmajor = (flags & BSMM_DSD_OUT_COLMAJOR) != 0;
+    const bool gelu = (flags & BSMM_DSD_GELU) != 0;
+    const bool fused = gelu || residual != nullptr || pre_activation != nullptr;
     if (m < 0 || n < 0 || k < 0 || nnz < 0 || (n % 32) != 0 || (k % 32) != 0) return BSMM_ERR_INVALID_ARGUMENT;
     if (m == 0 || n == 0) return BSMM_OK;
     if (ptr == nullptr || out == nullptr || (nnz > 0 && (idx == nullptr || data == nullptr || a == nullptr)))
         return BSMM_ERR_INVALID_ARGUMENT;
-    if (!aligned(a, 16) || !aligned(out, 16) || !aligned(data, 16) || !aligned(idx, 8))
+    if (!aligned(a, 16) || !aligned(out, 16) || !aligned(data, 16) || !aligned(idx, 8) || !aligned(residual, 16) ||
+        !aligned(pre_activation, 16))
         return BSMM_ERR_INVALID_ARGUMENT;
-    if (dgrad && bias != nullptr) return BSMM_ERR_UNSUPPORTED;
+    if (dgrad && (bias != nullptr || fused)) return BSMM_ERR_UNSUPPORTED;
+    if (fused && colmajor) return BSMM_ERR_UNSUPPORTED;
+    if (pre_activation != nullptr && !gelu) return BSMM_ERR_UNSUPPORTED;
     if (nnz > 0x7fffffff || n / 32 > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (precision == BSMM_PREC_FP32_SIMT) {
+        if (fused) return BSMM_ERR_UNSUPPORTED;  // the epilogue fusions live in the tensor-core kernel
         if (colmajor && (m + 127) / 128 > 65535) return BSMM_ERR_TOO_LARGE;
         return cuda_status(bsmm::launch_dsd_simt(static_cast<const float*>(a), m, k, ptr, idx, data, n,
                                                  static_cast<float*>(out), bias, dgrad, colmajor, s));
     }
     if (bsmm::is_tf32_precision(precision) || precision == BSMM_PREC_BF16) {
-        if (k == 0 || nnz == 0)  // nothing to contract: the CUDA-core kernel writes the zeros (+bias)
+        if (k == 0 || nnz == 0) {  // nothing to contract: the CUDA-core kernel writes the zeros (+bias)
+            if (fused) return BSMM_ERR_UNSUPPORTED;
             return cuda_status(bsmm::launch_dsd_simt(static_cast<const float*>(a), m, k, ptr, idx, data, n,
                                                      static_cast<float*>(out), bias, dgrad, colmajor, s));
+        }
         const int group = (int)((flags >> 8) & 0xFFu);
         if (packed == nullptr || plan == nullptr || !aligned(packed, 256) || !aligned(plan, 16) ||
             !bsmm::plan_group_valid(group) || (group == 8 && precision == BSMM_PREC_TF32X3) ||
             (group == 5 && precision != BSMM_PREC_TF32X3))
             return BSMM_ERR_INVALID_ARGUMENT;
+        bsmm::DsdEpilogue epilogue;
+        epilogue.residual = residual;
+        epilogue.pre_act = pre_activation;
+        epilogue.activation = gelu ? 1 : 0;
         return cuda_status(bsmm::launch_dsd_umma(a, m, k, nnz, packed, plan, group, n, out, bias, precision, dgrad,
-                                                 colmajor, s));
+                                                 colmajor, epilogue, s));
     }
     return BSMM_ERR_UNSUPPORTED;
+}
+
+int bsmm_dsd(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+             const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
+             uint32_t flags, bsmm_stream_t stream) {
+    if ((flags & BSMM_DSD_GELU) != 0) return BSMM_ERR_UNSUPPORTED;  // the activation belongs to bsmm_dsd_fused
+    return bsmm_dsd_fused(a, m, k, ptr, idx, nnz, data, packed, plan, n, out, bias, nullptr, nullptr, flags, stream);
 }
 
 int64_t bsmm_sddmm_plan_bytes(int64_t n_block_rows, int64_t nnz) {

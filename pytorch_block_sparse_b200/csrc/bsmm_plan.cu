@@ -59,7 +59,7 @@ build_plan_kernel(const int32_t* __restrict__ ptr, const int2* __restrict__ idx,
         const bool drain = ((ord + 1) % kDrainEvery) == 0 || e + 1 == rp[r + 1];
         const int idle = kDsdMmaWarps - __popc(warps_present);
         pe.flags = (before ? 0 : kPlanFirst) | (after ? 0 : kPlanLast | (idle << kPlanIdleShift)) |
-                   (drain ? kPlanDrain : 0) | (warp_after ? 0 : kPlanWarpLast);
+                   (drain ? kPlanDrain : 0) | (warp_after ? 0 : kPlanWarpLast) | (e + 1 == rp[r + 1] ? kPlanRowEnd : 0);
         entries[base + rank] = pe;
         if (!before) atomicAdd(&slabs, 1);
     }

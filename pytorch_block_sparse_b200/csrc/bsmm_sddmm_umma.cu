@@ -597,9 +597,20 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     if (splits > 65535) return cudaErrorInvalidValue;
 
     const bool x3 = precision == BSMM_PREC_TF32X3, bf16 = precision == BSMM_PREC_BF16;
-    cudaError_t err = cudaFuncSetAttribute(x3 ? sddmm_umma_tf32_kernel<3> : bf16 ? sddmm_umma_tf32_kernel<0> : sddmm_umma_tf32_kernel<1>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    // the shared-memory attribute is per device and kernel variant: set once each, then remembered
+    constexpr int kMaxDevices = 64;
+    static bool attribute_set[kMaxDevices][3] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    const int variant = x3 ? 0 : bf16 ? 1 : 2;
+    if (!attribute_set[dev][variant]) {
+        err = cudaFuncSetAttribute(x3 ? sddmm_umma_tf32_kernel<3> : bf16 ? sddmm_umma_tf32_kernel<0> : sddmm_umma_tf32_kernel<1>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (err != cudaSuccess) return err;
+        attribute_set[dev][variant] = true;
+    }
     CUtensorMap tmap_x, tmap_dy;
     err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)cols, (uint64_t)tokens, 32,
                        kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B);

@@ -27,7 +27,7 @@
 //
 // Measured on an idle SM, one block costs the tensor pipe 255 clk (3xTF32) or 165 clk (single pass)
 // in this form, against 422 / 232 clk with A read from shared memory (4 KiB per instruction).
-// Keeping the main term apart from the corrections and promoting it every 32 blocks bounds the
+// Keeping the main term apart from the corrections and promoting it every 48 blocks bounds the
 // tensor core's systematic fp32-accumulate error (about 2e-8 relative per accumulation).
 // Every wait is bounded; on expiry the CTA raises the device status word, stops issuing and drains.
 #include <cuda_bf16.h>
@@ -90,6 +90,9 @@ struct DsdParams {
     const int32_t* group_slabs; // [groups]
     const PlanEntry* entries;
     const float* bias;          // may be null
+    const float* residual;      // may be null: [m, n] row-major, added with the bias (row-major output only)
+    float* pre_act;             // may be null: [m, n] row-major, receives the sum before the activation
+    int32_t act;                // 0 none, 1 GELU: applied to a row's completed sum (row-major output only)
     float* out;
     unsigned int* status;       // device status word
     int64_t m, n;
@@ -110,10 +113,14 @@ enum TraceSlot {
     kTrDrainPReady = 12, kTrDrainTotal,
 };
 
+// Out of line: the erf expansion would otherwise be inlined 32 times into the epilogue and cost the whole
+// kernel registers that its hot loops want.
+__device__ __noinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
 template <int G, int kPasses>
 __global__ void __launch_bounds__((Cfg<G, kPasses>::kThreads), 1)
 dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_out,
-                     const DsdParams p) {
+                     const __grid_constant__ CUtensorMap tmap_pre, const DsdParams p) {
     using C = Cfg<G, kPasses>;
     constexpr int XS = C::kXStages;
     constexpr int kFirstDrainWarp = C::kFirstDrainWarp;
@@ -460,12 +467,14 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         // Returns false, to all four warps alike, when a thread of any of them has given up on a wait: the
         // first barrier carries that vote, so that the warps leave their loops together and none is left
         // behind at a barrier.
-        auto stage_out = [&](const float (&v)[32], int64_t col0, int32_t tok0, bool first) -> bool {
+        // put_tile: the 128 threads' rows v go to the tile (col0, tok0) of the tensor behind `tmap`, overwriting it
+        // or adding to it.
+        auto put_tile = [&](const float (&v)[32], const CUtensorMap* tmap, int64_t col0, int32_t tok0, bool overwrite) -> bool {
             const uint32_t buf = smem_base + C::kOffOut + (n_out & 1u) * kSlabBytes;
             // the tile's previous store (two promotions ago) must have read it; a reduction additionally waits
             // until every earlier store of this thread is complete in global memory
             if (issuer) {
-                if (!first) bulk_wait_group<0>();
+                if (!overwrite) bulk_wait_group<0>();
                 else bulk_wait_group_read<1>();
             }
             uint32_t any_bad;
@@ -478,21 +487,68 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             if (any_bad) return false;
             uint8_t* dst = smem_gen + C::kOffOut + (n_out & 1u) * kSlabBytes + row * 128;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (first && p.bias != nullptr) add = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+            for (int j = 0; j < 8; ++j)
                 *reinterpret_cast<float4*>(dst + ((j ^ (row & 7)) << 4)) =
-                    make_float4(v[j * 4 + 0] + add.x, v[j * 4 + 1] + add.y, v[j * 4 + 2] + add.z, v[j * 4 + 3] + add.w);
-            }
+                    make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
             fence_proxy_async_smem();  // generic-proxy writes, read by the TMA through the async proxy
             asm volatile("bar.sync 2, 128;" ::: "memory");
             if (issuer) {
-                if (first) tma_store_2d(&tmap_out, buf, (int32_t)col0, tok0);
-                else tma_reduce_add_2d(&tmap_out, buf, (int32_t)col0, tok0);
+                if (overwrite) tma_store_2d(tmap, buf, (int32_t)col0, tok0);
+                else tma_reduce_add_2d(tmap, buf, (int32_t)col0, tok0);
                 bulk_commit_group();
             }
             ++n_out;
             return true;
+        };
+        auto gelu = [](float (&v)[32]) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+        };
+        // One promotion of a row.  Without an activation the partial sums of a row simply add up in the output.
+        // With one, they add up in the tensor that keeps the pre-activation values (pre_act if given, else the
+        // output itself), and the row's last promotion produces the activated values from the completed sum --
+        // directly when it is also the first (rows of up to kDrainEvery blocks: the usual case), else by adding
+        // its part, waiting for that reduction, reading the total back and overwriting the output tile.
+        auto stage_out = [&](float (&v)[32], int64_t col0, int32_t tok0, int64_t tok, bool live, bool first, bool last) -> bool {
+            if (first) {
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 add = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + j);
+                        v[j * 4 + 0] += add.x; v[j * 4 + 1] += add.y; v[j * 4 + 2] += add.z; v[j * 4 + 3] += add.w;
+                    }
+                }
+                if (p.residual != nullptr && live) {
+                    const float4* res = reinterpret_cast<const float4*>(p.residual + tok * p.n + col0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 add = __ldg(res + j);
+                        v[j * 4 + 0] += add.x; v[j * 4 + 1] += add.y; v[j * 4 + 2] += add.z; v[j * 4 + 3] += add.w;
+                    }
+                }
+            }
+            if (p.act == 0) return put_tile(v, &tmap_out, col0, tok0, first);
+            const bool keep_pre = p.pre_act != nullptr;
+            const CUtensorMap* sums = keep_pre ? &tmap_pre : &tmap_out;
+            if (!last) return put_tile(v, sums, col0, tok0, first);
+            if (!first) {
+                if (!put_tile(v, sums, col0, tok0, false)) return false;
+                if (issuer) {
+                    bulk_wait_group<0>();                              // the reduction has reached global memory
+                    asm volatile("fence.proxy.async;" ::: "memory");   // async-proxy writes before the generic reads below
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                const float* total = (keep_pre ? p.pre_act : p.out) + tok * p.n + col0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 t4 = live ? __ldcg(reinterpret_cast<const float4*>(total) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[j * 4 + 0] = t4.x; v[j * 4 + 1] = t4.y; v[j * 4 + 2] = t4.z; v[j * 4 + 3] = t4.w;
+                }
+            } else if (keep_pre) {
+                if (!put_tile(v, &tmap_pre, col0, tok0, true)) return false;
+            }
+            gelu(v);
+            return put_tile(v, &tmap_out, col0, tok0, true);
         };
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += tile_step) {
             const int g = tile % p.groups;
@@ -516,13 +572,13 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     *dst = v[j] + add;
                 }
             };
-            auto emit = [&](int r, const float (&v)[32], bool first) -> bool {
+            auto emit = [&](int r, float (&v)[32], bool first, bool last) -> bool {
                 if (p.out_colmajor) {
                     if (__any_sync(0xffffffffu, bad != 0)) return false;
                     emit_colmajor(r, v, first);
                     return true;
                 }
-                return stage_out(v, ((int64_t)g * G + r) * 32, tok0, first);
+                return stage_out(v, ((int64_t)g * G + r) * 32, tok0, tok, live, first, last);
             };
 
             uint32_t seen = 0;      // bit r: the row has been written once in this tile
@@ -530,6 +586,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 const int4 mine = ahead;
                 ahead = prefetch(tile, base, e1);
                 uint32_t drains = __ballot_sync(0xffffffffu, (mine.w & kPlanDrain) != 0);
+                const uint32_t row_ends = __ballot_sync(0xffffffffu, (mine.w & kPlanRowEnd) != 0);
                 while (drains != 0) {
                     const int i = __ffs(drains) - 1;
                     drains &= drains - 1;
@@ -553,18 +610,20 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     }
                     tc_fence_before();
                     mbar_arrive(p_taken(r));
-                    ok = emit(r, v, !((seen >> r) & 1u));
+                    ok = emit(r, v, !((seen >> r) & 1u), ((row_ends >> i) & 1u) != 0);
                     if (!ok) break;
                     seen |= 1u << r;
                 }
             }
             if (ok) {
-                // block-rows without any block: bias (or zero)
-                float z[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) z[j] = 0.f;
+                // block-rows without any block: bias (+ residual, activated) or zero
                 for (int r = 0; r < nrows && ok; ++r)
-                    if (!((seen >> r) & 1u)) ok = emit(r, z, true);
+                    if (!((seen >> r) & 1u)) {
+                        float z[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) z[j] = 0.f;
+                        ok = emit(r, z, true, true);
+                    }
             }
         }
         if (issuer) bulk_wait_group<0>();  // the staging tiles are read until the last store has finished
@@ -603,21 +662,29 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 template <int G, int kPasses>
-cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const CUtensorMap& tmap_out, const DsdParams& p, int64_t tiles,
-                         cudaStream_t stream) {
-    // per call: the attribute is per device and the caller may switch devices
-    cudaError_t err = cudaFuncSetAttribute(dsd_umma_tf32_kernel<G, kPasses>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)Cfg<G, kPasses>::kSmemBytes);
+cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const CUtensorMap& tmap_out, const CUtensorMap& tmap_pre,
+                         const DsdParams& p, int64_t tiles, cudaStream_t stream) {
+    // The shared-memory attribute and the SM count are per device: asked once per device and kernel variant,
+    // then remembered (plain arrays; two threads racing on the first call store the same values).
+    constexpr int kMaxDevices = 64;
+    static int sm_count[kMaxDevices] = {0};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
-    int dev = 0, sms = 0;
-    err = cudaGetDevice(&dev);
-    if (err != cudaSuccess) return err;
-    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (sm_count[dev] == 0) {
+        err = cudaFuncSetAttribute(dsd_umma_tf32_kernel<G, kPasses>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)Cfg<G, kPasses>::kSmemBytes);
+        if (err != cudaSuccess) return err;
+        int count = 0;
+        err = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+        if (err != cudaSuccess) return err;
+        sm_count[dev] = count;
+    }
+    const int sms = sm_count[dev];
     const int64_t n_tiles = (int64_t)p.groups * tiles;
     const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);  // persistent: one CTA per SM
-    dsd_umma_tf32_kernel<G, kPasses><<<grid, Cfg<G, kPasses>::kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, tmap_out, p);
+    dsd_umma_tf32_kernel<G, kPasses><<<grid, Cfg<G, kPasses>::kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, tmap_out, tmap_pre, p);
     return cudaGetLastError();
 }
 
@@ -672,8 +739,10 @@ cudaError_t device_status_address(unsigned int** addr) {
 
 cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
-                            bool out_colmajor, cudaStream_t stream) {
+                            bool out_colmajor, const DsdEpilogue& epilogue, cudaStream_t stream) {
     if (!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return cudaErrorNotSupported;
+    if (out_colmajor && (epilogue.residual != nullptr || epilogue.pre_act != nullptr || epilogue.activation != 0))
+        return cudaErrorNotSupported;
     if (!plan_group_valid(group)) return cudaErrorInvalidValue;
     if (m == 0 || n == 0) return cudaSuccess;
     if (k == 0) return cudaErrorInvalidValue;  // nothing to contract over; a tensor map cannot describe it
@@ -697,7 +766,17 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
         if (err != cudaSuccess) return err;
     }
 
+    CUtensorMap tmap_pre = tmap_out;
+    if (epilogue.pre_act != nullptr) {
+        err = make_tmap_2d(&tmap_pre, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, epilogue.pre_act, (uint64_t)n, (uint64_t)m, 32,
+                           box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (err != cudaSuccess) return err;
+    }
+
     DsdParams p;
+    p.residual = epilogue.residual;
+    p.pre_act = epilogue.pre_act;
+    p.act = epilogue.activation;
     p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * packed_slot_bytes(precision) : 0);
     p.group_off = static_cast<const int32_t*>(plan);
     p.group_slabs = p.group_off + groups + 1;
@@ -721,16 +800,16 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     if (precision == BSMM_PREC_BF16) {
         if (group == 5) return cudaErrorInvalidValue;  // the 5-row tile exists for 3xTF32 only
         switch (group) {
-            case 4: return launch_dsd_g<4, 0>(tmap_a, tmap_out, p, tiles, stream);
-            case 6: return launch_dsd_g<6, 0>(tmap_a, tmap_out, p, tiles, stream);
-            default: return launch_dsd_g<8, 0>(tmap_a, tmap_out, p, tiles, stream);
+            case 4: return launch_dsd_g<4, 0>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+            case 6: return launch_dsd_g<6, 0>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+            default: return launch_dsd_g<8, 0>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
         }
     }
-    if (group == 5) return split ? launch_dsd_g<5, 3>(tmap_a, tmap_out, p, tiles, stream) : cudaErrorInvalidValue;
+    if (group == 5) return split ? launch_dsd_g<5, 3>(tmap_a, tmap_out, tmap_pre, p, tiles, stream) : cudaErrorInvalidValue;
     switch (group) {
-        case 4: return split ? launch_dsd_g<4, 3>(tmap_a, tmap_out, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, tmap_out, p, tiles, stream);
-        case 6: return split ? launch_dsd_g<6, 3>(tmap_a, tmap_out, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, tmap_out, p, tiles, stream);
-        default: return launch_dsd_g<8, 1>(tmap_a, tmap_out, p, tiles, stream);
+        case 4: return split ? launch_dsd_g<4, 3>(tmap_a, tmap_out, tmap_pre, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+        case 6: return split ? launch_dsd_g<6, 3>(tmap_a, tmap_out, tmap_pre, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+        default: return launch_dsd_g<8, 1>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
     }
 }
 

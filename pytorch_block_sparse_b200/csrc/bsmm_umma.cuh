@@ -23,11 +23,12 @@ constexpr int32_t kPlanLast = 2;      // last entry of its activation slab
 constexpr int32_t kPlanDrain = 4;     // after this entry the row's tensor-memory partial sum is promoted
 constexpr int32_t kPlanWarpLast = 8;  // last entry of its slab among the rows of the same MMA warp
 constexpr int kPlanIdleShift = 4;     // on the slab's last entry, 2 bits: MMA warps without a block in the slab
+constexpr int32_t kPlanRowEnd = 64;   // last block of its output row: the promotion after it completes the row
 // Blocks of one output row accumulated in tensor memory between two promotions.  The tensor core
 // adds into its fp32 accumulator with a systematic rounding error of about 2e-8 (relative) per
 // accumulation.  The kernel keeps the main term (hi*hi: 4 accumulations per block) apart from the
-// small correction terms, so 32 blocks cost 128 accumulations of the main term: about 3e-6.
-constexpr int kDrainEvery = 32;
+// small correction terms, so 48 blocks cost 192 accumulations of the main term: about 4e-6.
+constexpr int kDrainEvery = 48;
 
 inline bool plan_group_valid(int group) { return group == 4 || group == 5 || group == 6 || group == 8; }
 
@@ -46,9 +47,15 @@ __host__ __device__ constexpr int64_t plan_bytes(int64_t n_out_blocks, int64_t n
 cudaError_t launch_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks, int64_t nnz, int group,
                               void* plan, cudaStream_t stream);
 
+// Optional work fused into the epilogue of the row-major forward product: out = act(a * W^T + bias + residual).
+struct DsdEpilogue {
+    const float* residual = nullptr;  // [m, n] row-major, added with the bias
+    float* pre_act = nullptr;         // [m, n] row-major: receives a * W^T + bias + residual when an activation is applied
+    int activation = 0;               // 0 none, 1 GELU (erf form)
+};
 cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
-                            bool out_colmajor, cudaStream_t stream);
+                            bool out_colmajor, const DsdEpilogue& epilogue, cudaStream_t stream);
 
 // SDDMM: item table built from the CSR offsets (one item = up to 8 blocks of one block-row)
 int64_t sddmm_plan_bytes(int64_t n_rows, int64_t nnz);

@@ -13,10 +13,10 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG_DIR, "libbsmm_b200.so")
 
 # mirrors include/bsmm_b200.h
-ABI_VERSION = 1
+ABI_VERSION = 2
 OK = 0
 PREC_FP32_SIMT, PREC_TF32X3, PREC_BF16, PREC_TF32 = 0, 1, 2, 3
-DSD_DGRAD, DSD_OUT_COLMAJOR = 0x10, 0x20
+DSD_DGRAD, DSD_OUT_COLMAJOR, DSD_GELU = 0x10, 0x20, 0x40
 SDDMM_A_COLMAJOR, SDDMM_B_COLMAJOR = 0x10, 0x20
 
 PRECISIONS = {"fp32": PREC_FP32_SIMT, "simt": PREC_FP32_SIMT, "tf32x3": PREC_TF32X3, "tf32": PREC_TF32, "bf16": PREC_BF16}
@@ -32,6 +32,7 @@ EXPORTS = (
     "bsmm_plan_bytes",
     "bsmm_build_plan",
     "bsmm_dsd",
+    "bsmm_dsd_fused",
     "bsmm_sddmm_plan_bytes",
     "bsmm_build_sddmm_plan",
     "bsmm_sddmm_workspace_bytes",
@@ -86,6 +87,8 @@ def load():
     lib.bsmm_build_plan.argtypes = [vp, vp, i64, i64, i32, vp, vp]
     lib.bsmm_dsd.restype = i32
     lib.bsmm_dsd.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, vp, u32, vp]
+    lib.bsmm_dsd_fused.restype = i32
+    lib.bsmm_dsd_fused.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, vp, vp, vp, u32, vp]
     lib.bsmm_sddmm_workspace_bytes.restype = i64
     lib.bsmm_sddmm_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
     lib.bsmm_sddmm.restype = i32
@@ -295,8 +298,13 @@ class DsdPlan:
         return buf
 
 
-def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colmajor=False):
-    """``a @ W.T (+bias)`` (``transpose=True``) or ``a @ W`` through ``bsmm_dsd``.  ``a``: contiguous ``[m, k]``."""
+def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colmajor=False, residual=None,
+               activation=None, pre_activation=None):
+    """``a @ W.T (+bias)`` (``transpose=True``) or ``a @ W`` through ``bsmm_dsd``.  ``a``: contiguous ``[m, k]``.
+
+    Forward only, tensor-core precisions: ``residual`` (``[m, n_out]``) is added with the bias,
+    ``activation="gelu"`` is applied to the sum, and ``pre_activation`` (an ``[m, n_out]`` tensor to fill)
+    receives the sum before the activation -- all inside the kernel's epilogue (``bsmm_dsd_fused``)."""
     _need_cuda(a, "dense_a")
     lib = load()
     m, k = a.shape
@@ -306,7 +314,10 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
         a = a.to(want)
     if out is None:
         out = torch.empty((n_out, m) if out_colmajor else (m, n_out), dtype=want, device=a.device)
+    if activation not in (None, "gelu"):
+        raise ValueError("unknown activation %r (None or 'gelu')" % (activation,))
     flags = prec | (0 if transpose else DSD_DGRAD) | (DSD_OUT_COLMAJOR if out_colmajor else 0)
+    flags |= DSD_GELU if activation == "gelu" else 0
     plan_buf = None
     if prec != PREC_FP32_SIMT:
         group = plan.group_for(m, prec)
@@ -314,12 +325,17 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
         flags |= group << 8
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
+    if residual is not None:
+        residual = residual.detach().reshape(m, n_out).to(want).contiguous()
+    if pre_activation is not None and (pre_activation.dtype != want or not pre_activation.is_contiguous()
+                                       or pre_activation.numel() != m * n_out):
+        raise NativeError("pre_activation must be a contiguous float32 tensor of the output's size")
     with torch.cuda.device(a.device):
         check(
-            lib.bsmm_dsd(
+            lib.bsmm_dsd_fused(
                 _ptr(a), m, k, _ptr(plan.ptr), _ptr(plan.idx), plan.nnz, _ptr(packed.data), _ptr(packed.images),
-                _ptr(plan_buf), n_out, _ptr(out), _ptr(bias.detach() if bias is not None else None), flags,
-                _stream(a.device),
+                _ptr(plan_buf), n_out, _ptr(out), _ptr(bias.detach() if bias is not None else None), _ptr(residual),
+                _ptr(pre_activation), flags, _stream(a.device),
             ),
             "bsmm_dsd",
         )

@@ -223,7 +223,7 @@ def test_pack_statistic_matches_block_norm():
 
 @pytest.mark.parametrize("group", [4, 5, 6, 8])
 def test_plan_is_the_group_merge_of_the_csr(group):
-    m = make_matrix((512, 2048), n_blocks=700, seed=8)  # rows of ~44 blocks: promotions inside a row
+    m = make_matrix((512, 2048), n_blocks=880, seed=8)  # rows of ~55 of 64 blocks: promotions inside a row
     plan = m._plan(True)
     raw = plan.buffer(group)
     torch.cuda.synchronize()
@@ -235,7 +235,7 @@ def test_plan_is_the_group_merge_of_the_csr(group):
     ent = raw[ent_off: ent_off + plan.nnz * 16].view(np.int32).reshape(-1, 4)
     ptr = m.row_start_ends_a.cpu().numpy()
     idx = m.cols_a.cpu().numpy()
-    assert (np.diff(ptr) > 32).any()
+    assert (np.diff(ptr) > 48).any()
     for g in range(groups):
         rows = range(g * group, min(16, g * group + group))
         want = sorted((int(idx[e, 0]), r - g * group, int(idx[e, 1])) for r in rows for e in range(ptr[r], ptr[r + 1]))
@@ -249,14 +249,15 @@ def test_plan_is_the_group_merge_of_the_csr(group):
             last = i == len(got) - 1 or got[i + 1][0] != c
             seen[r] = seen.get(r, 0) + 1
             row_len = ptr[g * group + r + 1] - ptr[g * group + r]
-            drain = seen[r] % 32 == 0 or seen[r] == row_len  # promotion every 32 blocks of a row and at its end
+            drain = seen[r] % 48 == 0 or seen[r] == row_len  # promotion every 48 blocks of a row and at its end
+            row_end = seen[r] == row_len                       # bit 6: the promotion after it completes the row
             # MMA warp of a row: row mod 4.  Bit 3: last block of its slab for its warp; on the slab's last
             # block, bits 4-5: warps without a block in the slab
             slab = [int(q[2]) for q in got if q[0] == c]
             warp_last = not any(q > r and q % 4 == r % 4 for q in slab)
             idle = 4 - len({q % 4 for q in slab})
             assert flags == ((1 if first else 0) | (2 if last else 0) | (4 if drain else 0) | (8 if warp_last else 0)
-                             | ((idle << 4) if last else 0))
+                             | ((idle << 4) if last else 0) | (64 if row_end else 0))
 
 
 @pytest.mark.parametrize("group", ["4", "6", "8"])

@@ -334,3 +334,50 @@ def test_larger_square_blocks_on_the_tensor_core_kernels(block):
     want_norms = torch.norm(lin.weight.data.detach().reshape(-1, block, block), dim=(1, 2))
     assert torch.allclose(norms, want_norms, rtol=1e-5)
     assert_device_healthy()
+
+
+@pytest.mark.parametrize("activation,with_residual", [("gelu", False), (None, True), ("gelu", True)])
+@pytest.mark.parametrize("density", [0.3, 1.0])
+def test_fused_epilogue_matches_the_unfused_layer(activation, with_residual, density):
+    """bias + residual + GELU applied inside the forward kernel against the same layer followed by torch ops,
+    forward and all gradients.  Density 1.0 on 2048 input features gives rows of 64 blocks: two promotions per
+    row, i.e. the path where the activation waits for the completed sum."""
+    np.random.seed(31)
+    torch.manual_seed(31)
+    fused = BlockSparseLinear(2048, 128, bias=True, density=density, activation=activation)
+    with torch.no_grad():
+        fused.weight.data.normal_(0, 0.03)
+        fused.bias.normal_(0, 0.5)
+    plain = BlockSparseLinear(2048, 128, bias=True, density=density)
+    plain.load_state_dict(fused.state_dict())
+    x = torch.randn(3, 67, 2048, device="cuda")
+    res = torch.randn(3, 67, 128, device="cuda") if with_residual else None
+    dy = torch.randn(3, 67, 128, device="cuda")
+
+    def run(layer, use_fused):
+        xg = x.clone().requires_grad_(True)
+        rg = res.clone().requires_grad_(True) if res is not None else None
+        layer.weight.data.grad = None
+        layer.bias.grad = None
+        if use_fused:
+            y = layer(xg, residual=rg)
+        else:
+            y = layer(xg)
+            if rg is not None:
+                y = y + rg
+            if activation == "gelu":
+                y = torch.nn.functional.gelu(y)
+        y.backward(dy)
+        return y.detach(), xg.grad, layer.weight.data.grad.clone(), layer.bias.grad.clone(), None if rg is None else rg.grad
+
+    got, want = run(fused, True), run(plain, False)
+    for g, w, what in zip(got, want, ("y", "dx", "dw", "dbias", "dres")):
+        if w is None:
+            continue
+        err = float((g.double() - w.double()).norm() / w.double().norm())
+        assert err <= 1e-5, (what, err)
+    # inference path (no pre-activation kept)
+    with torch.no_grad():
+        y_eval = fused(x, residual=res)
+    assert float((y_eval.double() - want[0].double()).norm() / want[0].double().norm()) <= 1e-5
+    assert_device_healthy()
