@@ -150,8 +150,8 @@ int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
  * rows/cols multiples of 32, tokens free.  sparse_c fp32 [nnz*32, 32] is overwritten (beta = 0).
  * `block_sumsq` (fp32 [nnz], may be NULL) receives sum(sparse_c[s]^2).
  *
- * The tensor-core kernel (BSMM_PREC_TF32X3, BSMM_PREC_TF32 or BSMM_PREC_BF16; row-major fp32 operands, at
- * least 32 tokens) walks the matrix by block-rows and therefore also wants the CSR index array `csr_idx`
+ * The tensor-core kernel (BSMM_PREC_TF32X3, BSMM_PREC_TF32 or BSMM_PREC_BF16; fp32 operands in any of the four
+ * contiguity combinations, at least 32 tokens, and a multiple of 4 tokens when an operand is feature-major) walks the matrix by block-rows and therefore also wants the CSR index array `csr_idx`
  * (cols_a) and the item table bsmm_build_sddmm_plan makes from the CSR offsets (row_start_ends_a); `plan`
  * must hold bsmm_sddmm_plan_bytes(n_block_rows, nnz) bytes, 16-byte aligned, and depends only on the pattern.
  * When the token axis is split over several CTAs the partial results go through `workspace`

@@ -172,7 +172,7 @@ int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, i
     if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0) return -1;
     const uint32_t precision = flags & BSMM_PREC_MASK;
     if (!bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return 0;
-    if ((flags & (BSMM_SDDMM_A_COLMAJOR | BSMM_SDDMM_B_COLMAJOR)) != 0) return 0;
+    if ((flags & (BSMM_SDDMM_A_COLMAJOR | BSMM_SDDMM_B_COLMAJOR)) != 0 && (tokens % 4) != 0) return 0;
     return bsmm::sddmm_umma_workspace_bytes(rows, cols, tokens, nnz, precision);
 }
 
@@ -195,9 +195,9 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
     if (precision != BSMM_PREC_FP32_SIMT && !bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16)
         return BSMM_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (precision != BSMM_PREC_FP32_SIMT && !a_col && !b_col) {
-        const cudaError_t err = bsmm::launch_sddmm_umma(a, b, rows, cols, tokens, sparse_c, csr_idx, plan, nnz,
-                                                        block_sumsq, workspace, precision, s);
+    if (precision != BSMM_PREC_FP32_SIMT) {
+        const cudaError_t err = bsmm::launch_sddmm_umma(a, a_col, b, b_col, rows, cols, tokens, sparse_c, csr_idx, plan,
+                                                        nnz, block_sumsq, workspace, precision, s);
         if (err != cudaErrorNotSupported) return cuda_status(err);
         // shapes the tensor-core kernel does not take run on the CUDA-core kernel (same fp32-class result)
     }

@@ -100,7 +100,12 @@ __device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint3
 // kPasses = 3: 3xTF32 as described above; kPasses = 1: single-pass TF32 (no lo parts, no correction columns);
 // kPasses = 0: bf16 operands (kind::f16, K = 16 per instruction): the dY split warp writes the slab transposed
 // and rounded as a K-major bf16 tile (the layout of the bf16 weight images), the X split warps pack token pairs
-template <int kPasses>
+// kXFm / kDyFm: the operand is given feature-major ([features, tokens] contiguous, the reference's other
+// contiguity case, native/block_sparse_cutlass_kernel_back.cu:145-157) instead of token-major.  The TMA box is then
+// 32 features x 32 tokens with 128-byte token rows: for X that is already the orientation tensor memory wants
+// (lane = feature), read with 16-byte loads instead of the transposing 4-byte ones; for dY it is the K-major
+// canonical operand tile (plain 128-byte swizzle, 8-feature atoms of 1 KiB).
+template <int kPasses, bool kXFm, bool kDyFm>
 __global__ void __launch_bounds__(kThreads, 1)
 sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
                          const SddmmParams p) {
@@ -198,7 +203,10 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    if (j < nb) tma_load_2d(dst + j * kSlabBytes, &tmap_x, bcol[j], tok, x_full(xs));
+                    if (j < nb) {
+                        if (kXFm) tma_load_2d(dst + j * kSlabBytes, &tmap_x, tok, bcol[j], x_full(xs));
+                        else tma_load_2d(dst + j * kSlabBytes, &tmap_x, bcol[j], tok, x_full(xs));
+                    }
             }
             const bool wrap = xs + 2 >= kStages;
             xs = wrap ? xs + 2 - kStages : xs + 2;
@@ -212,7 +220,8 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             wait(dy_empty(ds), ((uint32_t)(step / kDyStages) & 1u) ^ 1u);
             if (elect_one() && !bad) {
                 mbar_arrive_expect_tx(dy_full(ds), kSlabBytes);
-                tma_load_2d(smem_base + kOffDy + ds * kDyStageBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
+                if (kDyFm) tma_load_2d(smem_base + kOffDy + ds * kDyStageBytes, &tmap_dy, tok, brow * 32, dy_full(ds));
+                else tma_load_2d(smem_base + kOffDy + ds * kDyStageBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
             }
         }
     } else if (warp < kFirstMmaWarp) {
@@ -236,6 +245,23 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                     l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
                     *reinterpret_cast<float4*>(base + kSlabBytes + (lane + 32 * i) * 16) = l;
                 }
+            } else if (kDyFm) {
+                // lane = feature r owns row r of the slab: 32 tokens = 8 chunks of 16 bytes (chunk index XOR r mod 8)
+                const uint8_t* rowp = base + lane * 128;
+#pragma unroll
+                for (int j = 2 * half; j < 2 * half + 2; ++j) {   // this warp's 16 tokens: chunks 4 half .. 4 half + 3
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const int c = 2 * j + q;
+                        const float4 v = *reinterpret_cast<const float4*>(rowp + ((c ^ (lane & 7)) << 4));
+                        const __nv_bfloat162 p01 = __floats2bfloat162_rn(v.x, v.y), p23 = __floats2bfloat162_rn(v.z, v.w);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<const uint32_t*>(&p01);
+                        packed.y = *reinterpret_cast<const uint32_t*>(&p23);
+                        // tokens 4c .. 4c + 3 of feature r: 8 consecutive bytes of the K-major bf16 tile
+                        *reinterpret_cast<uint2*>(base + kSlabBytes + image16_offset((uint32_t)lane, (uint32_t)(4 * c))) = packed;
+                    }
+                }
             } else {
                 // lane = feature r; the slab (plain 128-byte swizzle in this mode) is read along the tokens
                 const uint8_t* col = base + ((lane & 3) << 2);
@@ -254,8 +280,8 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     } else if (warp < kFirstSplitWarp) {
         // ------------------------------------------------------------------ MMA issuers
         const int ch = warp - kFirstMmaWarp;  // accumulations into one chunk stay in one thread's program order
-        constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, true);
-        constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, true);
+        constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, !kDyFm);
+        constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, !kDyFm);
         constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, false);
         // The loop is cut into promotion segments (kDrainSteps steps) so that the per-step body has no
         // first-step / last-step decisions: a conditional branch costs this lone warp ~40 cycles, and the
@@ -277,7 +303,9 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 // while the dY barrier is polled
                 const int ds = step & (kDyStages - 1);
                 // B: atom 0 = the raw dY slab, atom 1 (N = 64 only) = its lo part, one slab further
-                const uint64_t b_desc = smem_desc_mnmajor_sw128(smem_base + kOffDy + ds * kDyStageBytes, kSlabBytes);
+                // (feature-major dY: K-major tile, 8-feature atoms 1 KiB apart; the lo tile continues the raw one)
+                const uint64_t b_desc = kDyFm ? smem_desc_sw128(smem_base + kOffDy + ds * kDyStageBytes, 16, 1024)
+                                              : smem_desc_mnmajor_sw128(smem_base + kOffDy + ds * kDyStageBytes, kSlabBytes);
                 const uint32_t a_tm = tmem + kAccCols + as * kAStageCols;
                 const uint32_t a_bar = a_empty(as), dy_bar = dy_empty(ds);
                 const uint32_t a_cnt = a_count(as);
@@ -297,7 +325,9 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                     } else {
 #pragma unroll
                         for (int s = 0; s < 4; ++s) {
-                            const uint64_t b = b_desc + (uint64_t)(s * (kKStepBytes >> 4));
+                            // k-step s = 8 tokens: 8 rows of 128 bytes further (token-major) or 32 bytes further inside
+                            // the swizzled rows (feature-major)
+                            const uint64_t b = b_desc + (uint64_t)(kDyFm ? s * 2 : s * (kKStepBytes >> 4));
                             if (kPasses == 3) {
                                 mma_ts_tf32(d, a_tm + s * 8, b, idesc_wide, s == 0 ? acc0 : 1u);     // x x [dy ; dy_lo]
                                 mma_ts_tf32(d + 32, a_tm + 32 + s * 8, b, idesc_narrow, 1u);         // x_lo x dy
@@ -340,12 +370,25 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             // accumulator rows are independent of the others and never stored)
             uint32_t hi[32], lo[32];
             {
-                const uint8_t* col = smem_gen + kOffX + xs * kXStageBytes + quarter * kSlabBytes + ((lane & 3) << 2);
+                if (kXFm) {
+                    // the slab is [feature][token]: this thread's feature is row `lane`, 8 chunks of 4 tokens
+                    const uint8_t* rowp = smem_gen + kOffX + xs * kXStageBytes + quarter * kSlabBytes + lane * 128;
 #pragma unroll
-                for (int t = 0; t < 32; ++t) {
-                    const uint32_t v = *reinterpret_cast<const uint32_t*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
-                    hi[t] = v;
-                    if (kPasses == 3) lo[t] = __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xffffe000u));
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 v4 = *reinterpret_cast<const uint4*>(rowp + ((j ^ (lane & 7)) << 4));
+                        hi[4 * j + 0] = v4.x; hi[4 * j + 1] = v4.y; hi[4 * j + 2] = v4.z; hi[4 * j + 3] = v4.w;
+                    }
+#pragma unroll
+                    for (int t = 0; t < 32; ++t)
+                        if (kPasses == 3) lo[t] = __float_as_uint(__uint_as_float(hi[t]) - __uint_as_float(hi[t] & 0xffffe000u));
+                } else {
+                    const uint8_t* col = smem_gen + kOffX + xs * kXStageBytes + quarter * kSlabBytes + ((lane & 3) << 2);
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) {
+                        const uint32_t v = *reinterpret_cast<const uint32_t*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
+                        hi[t] = v;
+                        if (kPasses == 3) lo[t] = __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xffffe000u));
+                    }
                 }
             }
             mbar_arrive(x_empty(xs));
@@ -583,12 +626,48 @@ int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, i
     return splits > 1 ? splits * nnz * (int64_t)kBlockElems * 4 : 0;
 }
 
-cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens,
-                              float* sparse_c, const int32_t* csr_idx, const void* plan, int64_t nnz,
-                              float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream) {
+namespace {
+
+template <int kPasses, bool kXFm, bool kDyFm>
+cudaError_t launch_variant(dim3 grid, const CUtensorMap& tmap_x, const CUtensorMap& tmap_dy, const SddmmParams& p,
+                           cudaStream_t stream) {
+    // the shared-memory attribute is per device and kernel variant: set once each, then remembered
+    constexpr int kMaxDevices = 64;
+    static bool attribute_set[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!attribute_set[dev]) {
+        err = cudaFuncSetAttribute(sddmm_umma_tf32_kernel<kPasses, kXFm, kDyFm>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (err != cudaSuccess) return err;
+        attribute_set[dev] = true;
+    }
+    sddmm_umma_tf32_kernel<kPasses, kXFm, kDyFm><<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
+    return cudaGetLastError();
+}
+
+template <int kPasses>
+cudaError_t launch_layout(bool x_fm, bool dy_fm, dim3 grid, const CUtensorMap& tmap_x, const CUtensorMap& tmap_dy,
+                          const SddmmParams& p, cudaStream_t stream) {
+    if (x_fm) return dy_fm ? launch_variant<kPasses, true, true>(grid, tmap_x, tmap_dy, p, stream)
+                           : launch_variant<kPasses, true, false>(grid, tmap_x, tmap_dy, p, stream);
+    return dy_fm ? launch_variant<kPasses, false, true>(grid, tmap_x, tmap_dy, p, stream)
+                 : launch_variant<kPasses, false, false>(grid, tmap_x, tmap_dy, p, stream);
+}
+
+}  // namespace
+
+// a = dY, b = X; *_feature_major: the tensor is [features, tokens] contiguous instead of [tokens, features]
+cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b, bool b_feature_major, int64_t rows,
+                              int64_t cols, int64_t tokens, float* sparse_c, const int32_t* csr_idx, const void* plan,
+                              int64_t nnz, float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream) {
     if ((!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) || plan == nullptr || csr_idx == nullptr)
         return cudaErrorNotSupported;
     if (tokens < kStepTokens) return cudaErrorNotSupported;  // a box may not exceed its tensor
+    // a feature-major tensor has rows of `tokens` floats: the tensor map wants that pitch to be a multiple of 16 bytes
+    if ((a_feature_major || b_feature_major) && (tokens % 4) != 0) return cudaErrorNotSupported;
     if (tokens > 0x7fffffffll) return cudaErrorInvalidValue;
     const int64_t n_rows = rows / 32;
     int64_t splits, per;
@@ -597,27 +676,23 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     if (splits > 65535) return cudaErrorInvalidValue;
 
     const bool x3 = precision == BSMM_PREC_TF32X3, bf16 = precision == BSMM_PREC_BF16;
-    // the shared-memory attribute is per device and kernel variant: set once each, then remembered
-    constexpr int kMaxDevices = 64;
-    static bool attribute_set[kMaxDevices][3] = {};
-    int dev = 0;
-    cudaError_t err = cudaGetDevice(&dev);
-    if (err != cudaSuccess) return err;
-    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-    const int variant = x3 ? 0 : bf16 ? 1 : 2;
-    if (!attribute_set[dev][variant]) {
-        err = cudaFuncSetAttribute(x3 ? sddmm_umma_tf32_kernel<3> : bf16 ? sddmm_umma_tf32_kernel<0> : sddmm_umma_tf32_kernel<1>,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-        if (err != cudaSuccess) return err;
-        attribute_set[dev][variant] = true;
-    }
     CUtensorMap tmap_x, tmap_dy;
-    err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)cols, (uint64_t)tokens, 32,
-                       kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B);
+    cudaError_t err;
+    if (b_feature_major)
+        err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)tokens, (uint64_t)cols, kStepTokens, 32,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+    else
+        err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)cols, (uint64_t)tokens, 32,
+                           kStepTokens, CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess) return err;
-    // dY is the MMA's operand as loaded in the tf32 modes (32-byte-atom swizzle); in bf16 mode a warp reads it
-    err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)rows, (uint64_t)tokens, 32,
-                       kStepTokens, bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    // token-major dY is the MMA's operand as loaded in the tf32 modes (32-byte-atom swizzle); in bf16 mode a warp
+    // reads it.  Feature-major dY is the K-major canonical tile under the plain 128-byte swizzle in every mode.
+    if (a_feature_major)
+        err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)tokens, (uint64_t)rows, kStepTokens, 32,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+    else
+        err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)rows, (uint64_t)tokens, 32,
+                           kStepTokens, bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (err != cudaSuccess) return err;
 
     SddmmParams p;
@@ -631,10 +706,9 @@ cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_
     p.tokens_per_split = per;
     p.split_stride = nnz * (int64_t)kBlockElems;
     dim3 grid((unsigned)max_items(n_rows, nnz), (unsigned)splits);
-    if (x3) sddmm_umma_tf32_kernel<3><<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
-    else if (bf16) sddmm_umma_tf32_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
-    else sddmm_umma_tf32_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmap_x, tmap_dy, p);
-    err = cudaGetLastError();
+    if (x3) err = launch_layout<3>(b_feature_major, a_feature_major, grid, tmap_x, tmap_dy, p, stream);
+    else if (bf16) err = launch_layout<0>(b_feature_major, a_feature_major, grid, tmap_x, tmap_dy, p, stream);
+    else err = launch_layout<1>(b_feature_major, a_feature_major, grid, tmap_x, tmap_dy, p, stream);
     if (err != cudaSuccess) return err;
     if (splits > 1) {
         sddmm_reduce_kernel<<<(unsigned)nnz, 256, 0, stream>>>(static_cast<const float*>(workspace), (int)splits,

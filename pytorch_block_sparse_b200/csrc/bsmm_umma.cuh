@@ -61,10 +61,11 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
 int64_t sddmm_plan_bytes(int64_t n_rows, int64_t nnz);
 cudaError_t launch_build_sddmm_plan(const int32_t* ptr, int64_t n_rows, int64_t nnz, void* plan, cudaStream_t stream);
 int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t precision);
-// returns cudaErrorNotSupported for shapes it does not take (fewer than 32 tokens, missing plan)
-cudaError_t launch_sddmm_umma(const void* a, const void* b, int64_t rows, int64_t cols, int64_t tokens,
-                              float* sparse_c, const int32_t* csr_idx, const void* plan, int64_t nnz,
-                              float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream);
+// returns cudaErrorNotSupported for shapes it does not take (fewer than 32 tokens, missing plan, a feature-major
+// operand whose token count is not a multiple of 4)
+cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b, bool b_feature_major, int64_t rows,
+                              int64_t cols, int64_t tokens, float* sparse_c, const int32_t* csr_idx, const void* plan,
+                              int64_t nnz, float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream);
 
 // Address and size of the library's static scratch array on the current device (first call per
 // device resolves the symbol).

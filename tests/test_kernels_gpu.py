@@ -348,6 +348,58 @@ def test_sddmm_long_token_axis_and_statistic(precision):
     assert_device_healthy()
 
 
+@pytest.mark.parametrize("precision", ["tf32x3", "tf32", "bf16"])
+@pytest.mark.parametrize("a_rowmajor,b_rowmajor", [(False, True), (True, False), (False, False)])
+def test_sddmm_feature_major_operands_stay_on_the_tensor_cores(precision, a_rowmajor, b_rowmajor):
+    """The reference serves all four contiguity combinations of (dY, X) with one kernel
+    (native/block_sparse_cutlass_kernel_back.cu:145-157).  Here the tensor-core kernel reads a feature-major
+    operand through a [features, tokens] tensor map; the test checks values against the oracle, that the library
+    asks for the tensor-core kernel's workspace (i.e. does not drop to the CUDA-core kernel), and -- on a shape
+    large enough to tell -- that it is as fast as the token-major case."""
+    m = make_matrix((128, 1024), n_blocks=90, seed=61)
+    tokens = 3000
+    dy = randn((tokens, 128), seed=62)
+    x = randn((tokens, 1024), seed=63)
+    a = dy.cuda() if a_rowmajor else dy.t().contiguous().cuda().t()
+    b = x.cuda() if b_rowmajor else x.t().contiguous().cuda().t()
+    flags = native.PRECISIONS[precision] | (0 if a_rowmajor else native.SDDMM_A_COLMAJOR) | (0 if b_rowmajor else native.SDDMM_B_COLMAJOR)
+    assert native.load().bsmm_sddmm_workspace_bytes(128, 1024, tokens, 90, flags) > 0
+    got = m.matmul_with_output_sparse_support(a, b, precision=precision)
+    torch.cuda.synchronize()
+    want = orc.wgrad(dy.numpy(), x.numpy(), (128, 1024), m.blocks.cpu().numpy())
+    check(got, want, precision)
+    # a token count that is not a multiple of 4 cannot be described by a feature-major tensor map: CUDA-core kernel
+    got = m.matmul_with_output_sparse_support(a[:2999], b[:2999], precision=precision)
+    check(got, orc.wgrad(dy.numpy()[:2999], x.numpy()[:2999], (128, 1024), m.blocks.cpu().numpy()), precision)
+    assert_device_healthy()
+
+
+def test_sddmm_feature_major_speed_class():
+    big = make_matrix((2048, 2048), n_blocks=1024, seed=64)
+    g = torch.Generator().manual_seed(65)
+    dy_t = torch.randn(2048, 8192, generator=g).cuda()   # feature-major storage
+    x_t = torch.randn(2048, 8192, generator=g).cuda()
+    dy_c, x_c = dy_t.t().contiguous(), x_t.t().contiguous()
+
+    def timed(a, b):
+        for _ in range(2):
+            out = big.matmul_with_output_sparse_support(a, b)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            out = big.matmul_with_output_sparse_support(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 5, out
+
+    t_tm, ref = timed(dy_c, x_c)
+    t_fm, got = timed(dy_t.t(), x_t.t())
+    assert float((got.double() - ref.double()).norm() / ref.double().norm()) < 1e-5
+    assert t_fm < 1.5 * t_tm, (t_fm, t_tm)   # the CUDA-core kernel is about four times slower
+    assert_device_healthy()
+
+
 def test_missing_cuda_tensor_is_rejected():
     m = make_matrix((64, 64), n_blocks=2, seed=9)
     with pytest.raises(native.NativeError):
