@@ -49,8 +49,10 @@ WORKLOADS = {
 }
 C5 = dict(m=65536, n=32768, k=8192, density=0.1)
 # what the sweep leg times beside the headline (workload, precision)
-SWEEP = [("c3_d0.25", "tf32"), ("c3_d0.25", "bf16"), ("c3_d0.10", "tf32x3"), ("c3_d0.50", "tf32x3"),
-         ("c3_d0.75", "tf32x3"), ("c2_up", "tf32x3"), ("c2_down", "tf32x3")]
+# ("bf16io" = 'bf16' precision on bf16 activation / output tensors: half the activation bytes in HBM)
+SWEEP = [("c3_d0.25", "tf32"), ("c3_d0.25", "bf16"), ("c3_d0.25", "bf16io"), ("c3_d0.10", "tf32x3"), ("c3_d0.10", "bf16io"),
+         ("c3_d0.50", "tf32x3"), ("c3_d0.75", "tf32x3"), ("c2_up", "tf32x3"), ("c2_down", "tf32x3"),
+         ("c5_shard", "tf32x3"), ("c5_shard", "bf16io")]
 
 
 def nnz_of(cfg):
@@ -351,25 +353,32 @@ class LayerCase:
         self.bias = self.lin.bias.detach()
         self.data = self.w.data.detach()
 
-    def ops(self, prec):
-        """(pack, fwd, dgrad, wgrad) closures for one precision."""
+    def ops(self, prec, io_bf16=False):
+        """(pack, fwd, dgrad, wgrad) closures for one precision; io_bf16: on bf16 copies of the activations, with
+        bf16 outputs."""
+        import torch
+
         from pytorch_block_sparse_b200 import native
 
         n, k = self.cfg["n"], self.cfg["k"]
         plan_f, plan_d, plan_w = self.plans
         state = {}
+        x, dy, y, dx = self.x, self.dy, self.y, self.dx
+        if io_bf16:
+            x, dy = x.bfloat16(), dy.bfloat16()
+            y, dx = torch.empty_like(y, dtype=torch.bfloat16), torch.empty_like(dx, dtype=torch.bfloat16)
 
         def pack():
             state["packed"] = native.pack_weights(self.data, prec)
 
         def fwd():
-            native.dsd_matmul(self.x, plan_f, state["packed"], n, True, bias=self.bias, out=self.y)
+            native.dsd_matmul(x, plan_f, state["packed"], n, True, bias=self.bias, out=y)
 
         def dgrad():
-            native.dsd_matmul(self.dy, plan_d, state["packed"], k, False, out=self.dx)
+            native.dsd_matmul(dy, plan_d, state["packed"], k, False, out=dx)
 
         def wgrad():
-            native.sddmm(self.dy, True, self.x, True, self.w.blocks, self.dw, precision=prec, plan=plan_w)
+            native.sddmm(dy, True, x, True, self.w.blocks, self.dw, precision=prec, plan=plan_w)
 
         return pack, fwd, dgrad, wgrad
 
@@ -388,15 +397,35 @@ def run_sweep(dev, steps):
             torch.cuda.empty_cache()
             cases[workload] = LayerCase(WORKLOADS[workload], dev)
         case = cases[workload]
-        pack, fwd, dgrad, wgrad = case.ops(native.resolve_precision(prec_name))
+        io16 = prec_name == "bf16io"
+        pack, fwd, dgrad, wgrad = case.ops(native.resolve_precision("bf16" if io16 else prec_name), io_bf16=io16)
 
         def step():
             pack(); fwd(); wgrad(); dgrad()
 
         ms = time_op(step, max(3, min(steps, 10)), warm=3)
-        out["%s/%s" % (workload, prec_name)] = {
-            "ms_per_step": ms, "effective_tflops": 3 * flops_per_op(case.cfg) / (ms / 1e3) / 1e12}
+        entry = {"ms_per_step": ms, "effective_tflops": 3 * flops_per_op(case.cfg) / (ms / 1e3) / 1e12}
+        if io16:  # these are the HBM-bound cases: activation bytes in + out, weight images, fp32 weight gradient
+            c = case.cfg
+            nbytes = 2 * (3 * c["m"] * c["k"] + 3 * c["m"] * c["n"]) + nnz_of(c) * (2 * 2048 + 4096 + 4096)
+            entry["algorithmic_gbs"] = nbytes / (ms / 1e3) / 1e9
+            entry["frac_of_measured_hbm"] = entry["algorithmic_gbs"] / measured_peaks()["hbm_gbs"]
+        out["%s/%s" % (workload, prec_name)] = entry
+        del pack, fwd, dgrad, wgrad
+    # one step of the sparsity optimizer (pruning + regrowth of 10 % of the blocks, Adam state attached) on the
+    # headline layer: statistic kernel, k-smallest selection, sampling of empty positions, index rebuild
     cases.clear()
+    torch.cuda.empty_cache()
+    from pytorch_block_sparse_b200 import SparseOptimizer
+
+    case = LayerCase(WORKLOADS["c3_d0.25"], dev)
+    adam = torch.optim.Adam([case.w.data], lr=1e-3)
+    case.w.data.grad = torch.zeros_like(case.w.data)
+    adam.step()
+    so = SparseOptimizer([case.w], lr=0.1, seed=1)
+    so.attach_optimizer(adam)
+    out["sparse_optimizer_step_ms/c3_d0.25"] = time_op(so.step, 5, warm=2)
+    del case, adam, so
     torch.cuda.empty_cache()
     return out
 
@@ -434,12 +463,18 @@ def run_c5(dev, world, rank, steps, precisions):
     plan_f, plan_d, plan_w = w._plan(True), w._plan(False), w._sddmm_plan()
     side = torch.cuda.Stream(device=dev)
     data = w.data.detach()
-    out = {"shape": dict(C5, nnz=nnz), "block_rows_per_rank": n_local // 32, "scaling": "strong",
-           "all_gather_bytes_per_rank": (world - 1) * m * n_local * 4 if world > 1 else 0,
-           "all_reduce_bytes": m * k * 4 if world > 1 else 0}
+    out = {"shape": dict(C5, nnz=nnz), "block_rows_per_rank": n_local // 32, "scaling": "strong"}
     f_total = 3 * 2.0 * m * nnz * 1024
+    tensors32 = (x, dy, y, dx, y_all)
     for prec_name in precisions:
         prec = native.resolve_precision(prec_name)
+        if prec_name == "bf16":  # the configuration says "X bf16": bf16 activations and outputs in HBM
+            x, dy = tensors32[0].bfloat16(), tensors32[1].bfloat16()
+            y, dx = torch.empty_like(tensors32[2], dtype=torch.bfloat16), torch.empty_like(tensors32[3], dtype=torch.bfloat16)
+            y_all = torch.empty(world, m, n_local, device=dev, dtype=torch.bfloat16) if world > 1 else None
+        else:
+            x, dy, y, dx, y_all = tensors32
+        elem = 2 if prec_name == "bf16" else 4
 
         def step(collectives):
             packed = native.pack_weights(data, prec)
@@ -467,6 +502,9 @@ def run_c5(dev, world, rank, steps, precisions):
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 ms = float(t.item())
             res[name] = ms
+        res["tensors"] = "bf16 activations and outputs" if elem == 2 else "fp32"
+        res["all_gather_bytes_per_rank"] = (world - 1) * m * n_local * elem if world > 1 else 0
+        res["all_reduce_bytes"] = m * k * elem if world > 1 else 0
         res["effective_tflops"] = f_total / (res["with_collectives_ms"] / 1e3) / 1e12
         res["effective_tflops_compute_only"] = f_total / (res["compute_ms"] / 1e3) / 1e12
         out[prec_name] = res

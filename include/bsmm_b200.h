@@ -57,10 +57,12 @@ extern "C" {
 #define BSMM_DSD_OUT_COLMAJOR 0x20u /* 0: out is [m, n] row-major; 1: out is [n, m] (the reference's buffer) */
 #define BSMM_DSD_GROUP(g) (((uint32_t)(g)&0xFFu) << 8) /* group size the plan was built with (tensor-core precisions) */
 #define BSMM_DSD_GELU 0x40u         /* bsmm_dsd_fused only: out = gelu(a * W^T + bias + residual), erf form */
+#define BSMM_DSD_IO_BF16 0x80u      /* with BSMM_PREC_BF16: `a` and `out` are bf16 tensors (row-major); bias stays fp32 */
 
 /* bsmm_sddmm flags */
 #define BSMM_SDDMM_A_COLMAJOR 0x10u /* dY given as [rows, tokens] contiguous instead of [tokens, rows] */
 #define BSMM_SDDMM_B_COLMAJOR 0x20u /* X  given as [cols, tokens] contiguous instead of [tokens, cols] */
+#define BSMM_SDDMM_IO_BF16 0x40u    /* with BSMM_PREC_BF16: dY and X are bf16 tensors (token-major, at least 32 tokens); sparse_c stays fp32 */
 
 typedef void* bsmm_stream_t;
 
@@ -116,7 +118,7 @@ int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks
  * (reference native/block_sparse_native.cpp:6-16, native/block_sparse_cutlass_kernel.cu:113-150):
  *   fwd   (flags without BSMM_DSD_DGRAD): out[m, n] = a[m, k] * W^T (+ bias[n]),  W is [n, k], ptr/idx = CSR
  *   dgrad (BSMM_DSD_DGRAD)              : out[m, n] = a[m, k] * W,               W is [k, n], ptr/idx = CSC
- * a: [m, k] row-major fp32; out: fp32; m is free,
+ * a: [m, k] row-major fp32; out: fp32 (both bf16 with BSMM_DSD_IO_BF16); m is free,
  * n and k are multiples of 32.  Every output element is written (empty block-rows give zeros),
  * so `out` needs no pre-zeroing.  `data` is always required; `packed`/`plan` (and the plan's group size
  * in the flags, BSMM_DSD_GROUP) are required by the tensor-core precisions and ignored by FP32_SIMT.

@@ -80,7 +80,7 @@ class BlockSparseLinearFunction(torch.autograd.Function):
             grad_input = weight.reverse_matmul(grad_output, transpose=False, packed=ctx.packed)
             assert grad_input.shape == input.shape
         if ctx.has_bias and ctx.needs_input_grad[3]:
-            grad_bias = grad_output.reshape(-1, grad_output.shape[-1]).sum(0)
+            grad_bias = grad_output.reshape(-1, grad_output.shape[-1]).sum(0, dtype=torch.float32)
         if ctx.has_residual and ctx.needs_input_grad[4]:
             grad_residual = grad_output
         return (grad_input, grad_weight, None, grad_bias, grad_residual, None)[: 3 + ctx.n_extra]

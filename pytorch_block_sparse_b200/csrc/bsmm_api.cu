@@ -109,6 +109,7 @@ int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
     const bool dgrad = (flags & BSMM_DSD_DGRAD) != 0;
     const bool colmajor = (flags & BSMM_DSD_OUT_COLMAJOR) != 0;
     const bool gelu = (flags & BSMM_DSD_GELU) != 0;
+    const bool io16 = (flags & BSMM_DSD_IO_BF16) != 0;
     const bool fused = gelu || residual != nullptr || pre_activation != nullptr;
     if (m < 0 || n < 0 || k < 0 || nnz < 0 || (n % 32) != 0 || (k % 32) != 0) return BSMM_ERR_INVALID_ARGUMENT;
     if (m == 0 || n == 0) return BSMM_OK;
@@ -120,6 +121,8 @@ int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
     if (dgrad && (bias != nullptr || fused)) return BSMM_ERR_UNSUPPORTED;
     if (fused && colmajor) return BSMM_ERR_UNSUPPORTED;
     if (pre_activation != nullptr && !gelu) return BSMM_ERR_UNSUPPORTED;
+    if (io16 && (precision != BSMM_PREC_BF16 || colmajor || residual != nullptr || pre_activation != nullptr || nnz == 0 || k == 0))
+        return BSMM_ERR_UNSUPPORTED;
     if (nnz > 0x7fffffff || n / 32 > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (precision == BSMM_PREC_FP32_SIMT) {
@@ -143,6 +146,7 @@ int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
         epilogue.residual = residual;
         epilogue.pre_act = pre_activation;
         epilogue.activation = gelu ? 1 : 0;
+        epilogue.io_bf16 = io16;
         return cuda_status(bsmm::launch_dsd_umma(a, m, k, nnz, packed, plan, group, n, out, bias, precision, dgrad,
                                                  colmajor, epilogue, s));
     }
@@ -195,12 +199,15 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
     if (precision != BSMM_PREC_FP32_SIMT && !bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16)
         return BSMM_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool io16 = (flags & BSMM_SDDMM_IO_BF16) != 0;
+    if (io16 && (precision != BSMM_PREC_BF16 || a_col || b_col)) return BSMM_ERR_UNSUPPORTED;
     if (precision != BSMM_PREC_FP32_SIMT) {
         const cudaError_t err = bsmm::launch_sddmm_umma(a, a_col, b, b_col, rows, cols, tokens, sparse_c, csr_idx, plan,
-                                                        nnz, block_sumsq, workspace, precision, s);
+                                                        nnz, block_sumsq, workspace, precision, io16, s);
         if (err != cudaErrorNotSupported) return cuda_status(err);
         // shapes the tensor-core kernel does not take run on the CUDA-core kernel (same fp32-class result)
     }
+    if (io16) return BSMM_ERR_UNSUPPORTED;  // the CUDA-core kernel reads fp32 tensors only
     return cuda_status(bsmm::launch_sddmm_simt(static_cast<const float*>(a), a_col, static_cast<const float*>(b),
                                                b_col, rows, cols, tokens, sparse_c, blocks, nnz, block_sumsq, s));
 }

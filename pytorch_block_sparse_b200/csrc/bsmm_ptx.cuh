@@ -214,6 +214,10 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
 __device__ __forceinline__ uint64_t smem_desc_sw128_base32(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     return smem_desc_noswizzle(addr, lbo_bytes, sbo_bytes) | (1ull << 61);
 }
+// Same with the 64-byte swizzle mode (layout type 4).
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return smem_desc_noswizzle(addr, lbo_bytes, sbo_bytes) | (4ull << 61);
+}
 // Instruction descriptor, fp32 accumulate.  fmt: 0 f16, 1 bf16, 2 tf32.  *_mn_major: operand is
 // MN-major (its M/N index is the contiguous one) instead of K-major.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t m, uint32_t n, bool a_mn_major,

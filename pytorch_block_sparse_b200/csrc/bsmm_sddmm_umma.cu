@@ -100,6 +100,9 @@ __device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint3
 // kPasses = 3: 3xTF32 as described above; kPasses = 1: single-pass TF32 (no lo parts, no correction columns);
 // kPasses = 0: bf16 operands (kind::f16, K = 16 per instruction): the dY split warp writes the slab transposed
 // and rounded as a K-major bf16 tile (the layout of the bf16 weight images), the X split warps pack token pairs
+// kPasses = 4: bf16 operands that are bf16 tensors in memory already (token-major): the dY box, loaded with the
+// 64-byte swizzle, IS the MN-major canonical bf16 operand tile (atoms of 8 token rows x 64 bytes), so the dY split
+// warps have nothing to do; the X split warps read 2-byte values and pack token pairs.
 // kXFm / kDyFm: the operand is given feature-major ([features, tokens] contiguous, the reference's other
 // contiguity case, native/block_sparse_cutlass_kernel_back.cu:145-157) instead of token-major.  The TMA box is then
 // 32 features x 32 tokens with 128-byte token rows: for X that is already the orientation tensor memory wants
@@ -109,6 +112,9 @@ template <int kPasses, bool kXFm, bool kDyFm>
 __global__ void __launch_bounds__(kThreads, 1)
 sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
                          const SddmmParams p) {
+    constexpr bool kBf16 = kPasses == 0 || kPasses == 4, kIo16 = kPasses == 4;
+    static_assert(!kIo16 || (!kXFm && !kDyFm), "bf16 tensors are taken token-major");
+    constexpr uint32_t kLoadSlabBytes = kIo16 ? kSlabBytes / 2 : kSlabBytes;   // what one TMA box delivers
     const int n_items = p.items[0];
     if ((int)blockIdx.x >= n_items) return;
     const int4 item = reinterpret_cast<const int4*>(p.items + 4)[blockIdx.x];
@@ -200,7 +206,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             wait(x_empty(xs), parity);
             const uint32_t dst = smem_base + kOffX + xs * kXStageBytes;
             if (elect_one() & (bad == 0)) {
-                mbar_arrive_expect_tx(x_full(xs), nb * kSlabBytes);
+                mbar_arrive_expect_tx(x_full(xs), nb * kLoadSlabBytes);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                     if (j < nb) {
@@ -219,7 +225,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             const int32_t tok = (int32_t)(t_begin + (int64_t)step * kStepTokens);
             wait(dy_empty(ds), ((uint32_t)(step / kDyStages) & 1u) ^ 1u);
             if (elect_one() && !bad) {
-                mbar_arrive_expect_tx(dy_full(ds), kSlabBytes);
+                mbar_arrive_expect_tx(dy_full(ds), kLoadSlabBytes);
                 if (kDyFm) tma_load_2d(smem_base + kOffDy + ds * kDyStageBytes, &tmap_dy, tok, brow * 32, dy_full(ds));
                 else tma_load_2d(smem_base + kOffDy + ds * kDyStageBytes, &tmap_dy, brow * 32, tok, dy_full(ds));
             }
@@ -229,7 +235,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         // lo = v - trunc_tf32(v), elementwise at the same offset of the stage's second half: the swizzle
         // needs no decoding; consecutive lanes take consecutive 16-byte chunks
         const int half = warp - kDySplitWarp;  // which half of the slab this warp converts
-        for (int step = 0; step < nsteps && kPasses != 1; ++step) {
+        for (int step = 0; step < nsteps && kPasses != 1 && !kIo16; ++step) {
             const int ds = step & (kDyStages - 1);
             wait(dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
             if (__any_sync(0xffffffffu, bad != 0)) break;
@@ -282,7 +288,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const int ch = warp - kFirstMmaWarp;  // accumulations into one chunk stay in one thread's program order
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, !kDyFm);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, !kDyFm);
-        constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, false);
+        constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, kIo16);  // bf16 tensors: B is MN-major
         // The loop is cut into promotion segments (kDrainSteps steps) so that the per-step body has no
         // first-step / last-step decisions: a conditional branch costs this lone warp ~40 cycles, and the
         // body's length bounds how fast a chunk's stages turn around.
@@ -310,16 +316,19 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 const uint32_t a_bar = a_empty(as), dy_bar = dy_empty(ds);
                 const uint32_t a_cnt = a_count(as);
                 const uint32_t seen = smem_load_acquire(a_cnt);
-                wait(kPasses != 1 ? dylo_full(ds) : dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
+                wait(kPasses != 1 && !kIo16 ? dylo_full(ds) : dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
                 if ((int32_t)(seen - a_target) < 0) wait_count(a_cnt, a_target);
                 // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the columns) precede the MMAs
                 tc_fence_after();
                 if (elect_one() & (bad == 0)) {
-                    if (kPasses == 0) {
+                    if (kBf16) {
+                        // K-major bf16 tile made by the dY split warps, or (bf16 tensors) the box as TMA wrote it:
+                        // atoms of 8 token rows x 64 bytes, 512 bytes apart along K, 16 tokens = 1 KiB per instruction
                         const uint64_t b16 =
-                            smem_desc_noswizzle(smem_base + kOffDy + ds * kDyStageBytes + kSlabBytes, kImage16Lbo, kImage16Sbo);
+                            kIo16 ? smem_desc_sw64(smem_base + kOffDy + ds * kDyStageBytes, kSlabBytes, 512)
+                                  : smem_desc_noswizzle(smem_base + kOffDy + ds * kDyStageBytes + kSlabBytes, kImage16Lbo, kImage16Sbo);
 #pragma unroll
-                        for (int s = 0; s < 2; ++s)  // 16 tokens per instruction: 8 columns of token pairs, two k-chunks
+                        for (int s = 0; s < 2; ++s)  // 16 tokens per instruction: 8 columns of token pairs
                             mma_ts_f16(d, a_tm + s * 8, b16 + (uint64_t)(s * (kImage16StepBytes >> 4)), idesc_bf16,
                                        s == 0 ? acc0 : 1u);
                     } else {
@@ -370,7 +379,13 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             // accumulator rows are independent of the others and never stored)
             uint32_t hi[32], lo[32];
             {
-                if (kXFm) {
+                if (kIo16) {
+                    // bf16 slab [token][feature], 64-byte rows, 64-byte swizzle (16-byte chunk index XOR (token / 2) mod 4)
+                    const uint8_t* col = smem_gen + kOffX + xs * kXStageBytes + quarter * kSlabBytes + ((lane & 7) << 1);
+#pragma unroll
+                    for (int t = 0; t < 32; ++t)
+                        hi[t] = *reinterpret_cast<const uint16_t*>(col + t * 64 + (((lane >> 3) ^ ((t >> 1) & 3)) << 4));
+                } else if (kXFm) {
                     // the slab is [feature][token]: this thread's feature is row `lane`, 8 chunks of 4 tokens
                     const uint8_t* rowp = smem_gen + kOffX + xs * kXStageBytes + quarter * kSlabBytes + lane * 128;
 #pragma unroll
@@ -394,12 +409,16 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             mbar_arrive(x_empty(xs));
             tc_fence_after();
             const uint32_t a_tm = tmem_lane + kAccCols + xs * kAStageCols;
-            if (kPasses == 0) {
+            if (kBf16) {
                 uint32_t packed[16];  // column j: token 2j in the low half, token 2j + 1 in the high half
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(hi[2 * j]), __uint_as_float(hi[2 * j + 1]));
-                    packed[j] = *reinterpret_cast<const uint32_t*>(&pr);
+                    if (kIo16) {
+                        packed[j] = hi[2 * j] | (hi[2 * j + 1] << 16);
+                    } else {
+                        const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(hi[2 * j]), __uint_as_float(hi[2 * j + 1]));
+                        packed[j] = *reinterpret_cast<const uint32_t*>(&pr);
+                    }
                 }
                 tmem_st16(a_tm, packed);
             } else {
@@ -659,10 +678,13 @@ cudaError_t launch_layout(bool x_fm, bool dy_fm, dim3 grid, const CUtensorMap& t
 
 }  // namespace
 
-// a = dY, b = X; *_feature_major: the tensor is [features, tokens] contiguous instead of [tokens, features]
+// a = dY, b = X; *_feature_major: the tensor is [features, tokens] contiguous instead of [tokens, features];
+// io_bf16: both are bf16 tensors (token-major, BSMM_PREC_BF16)
 cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b, bool b_feature_major, int64_t rows,
                               int64_t cols, int64_t tokens, float* sparse_c, const int32_t* csr_idx, const void* plan,
-                              int64_t nnz, float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream) {
+                              int64_t nnz, float* block_sumsq, void* workspace, uint32_t precision, bool io_bf16,
+                              cudaStream_t stream) {
+    if (io_bf16 && (precision != BSMM_PREC_BF16 || a_feature_major || b_feature_major)) return cudaErrorNotSupported;
     if ((!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) || plan == nullptr || csr_idx == nullptr)
         return cudaErrorNotSupported;
     if (tokens < kStepTokens) return cudaErrorNotSupported;  // a box may not exceed its tensor
@@ -678,7 +700,13 @@ cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b
     const bool x3 = precision == BSMM_PREC_TF32X3, bf16 = precision == BSMM_PREC_BF16;
     CUtensorMap tmap_x, tmap_dy;
     cudaError_t err;
-    if (b_feature_major)
+    if (io_bf16) {
+        err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b, (uint64_t)cols, (uint64_t)tokens, 32, kStepTokens,
+                           CU_TENSOR_MAP_SWIZZLE_64B);
+        if (err != cudaSuccess) return err;
+        err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, (uint64_t)rows, (uint64_t)tokens, 32, kStepTokens,
+                           CU_TENSOR_MAP_SWIZZLE_64B);
+    } else if (b_feature_major)
         err = make_tmap_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b, (uint64_t)tokens, (uint64_t)cols, kStepTokens, 32,
                            CU_TENSOR_MAP_SWIZZLE_128B);
     else
@@ -687,7 +715,9 @@ cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b
     if (err != cudaSuccess) return err;
     // token-major dY is the MMA's operand as loaded in the tf32 modes (32-byte-atom swizzle); in bf16 mode a warp
     // reads it.  Feature-major dY is the K-major canonical tile under the plain 128-byte swizzle in every mode.
-    if (a_feature_major)
+    if (io_bf16)
+        ;  // both maps were made above
+    else if (a_feature_major)
         err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)tokens, (uint64_t)rows, kStepTokens, 32,
                            CU_TENSOR_MAP_SWIZZLE_128B);
     else
@@ -707,6 +737,7 @@ cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b
     p.split_stride = nnz * (int64_t)kBlockElems;
     dim3 grid((unsigned)max_items(n_rows, nnz), (unsigned)splits);
     if (x3) err = launch_layout<3>(b_feature_major, a_feature_major, grid, tmap_x, tmap_dy, p, stream);
+    else if (io_bf16) err = launch_variant<4, false, false>(grid, tmap_x, tmap_dy, p, stream);
     else if (bf16) err = launch_layout<0>(b_feature_major, a_feature_major, grid, tmap_x, tmap_dy, p, stream);
     else err = launch_layout<1>(b_feature_major, a_feature_major, grid, tmap_x, tmap_dy, p, stream);
     if (err != cudaSuccess) return err;

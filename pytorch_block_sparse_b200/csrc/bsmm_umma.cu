@@ -59,10 +59,13 @@ constexpr int kWStages = kMmaWarps * kWRing;
 
 template <int G, int kPasses>
 struct Cfg {
-    // kPasses: 3 = 3xTF32, 1 = single-pass TF32, 0 = bf16 operands (kind::f16), fp32 accumulation throughout
+    // kPasses: 3 = 3xTF32, 1 = single-pass TF32, 0 = bf16 operands (kind::f16) rounded in the kernel from fp32
+    // tensors, 4 = bf16 operands with bf16 activations and outputs in memory; fp32 accumulation throughout
+    static constexpr bool kBf16 = kPasses == 0 || kPasses == 4;
+    static constexpr bool kIo16 = kPasses == 4;
     static constexpr uint32_t kRowCols = kPasses == 3 ? 64 : 32;     // main | correction
     static constexpr uint32_t kAStageCols = kPasses == 3 ? 64 : kPasses == 1 ? 32 : 16;  // x_hi | x_lo; bf16 pairs
-    static constexpr uint32_t kWBytes = kPasses == 0 ? kImage16Bytes : kImage32Bytes;    // one block's image
+    static constexpr uint32_t kWBytes = kBf16 ? kImage16Bytes : kImage32Bytes;    // one block's image
     static constexpr uint32_t kAccCols = G * kRowCols;
     static constexpr int kAStagesMax = (int)((kTmemCols - kAccCols) / kAStageCols);
     static constexpr int kAStages = kAStagesMax >= 8 ? 8 : kAStagesMax >= 4 ? 4 : kAStagesMax;  // 8, 4, 3 or 2
@@ -93,7 +96,7 @@ struct DsdParams {
     const float* residual;      // may be null: [m, n] row-major, added with the bias (row-major output only)
     float* pre_act;             // may be null: [m, n] row-major, receives the sum before the activation
     int32_t act;                // 0 none, 1 GELU: applied to a row's completed sum (row-major output only)
-    float* out;
+    float* out;                 // (bf16 in the bf16-tensor variant, which writes only through tmap_out)
     unsigned int* status;       // device status word
     int64_t m, n;
     int32_t n_out_blocks, groups;
@@ -122,6 +125,9 @@ __global__ void __launch_bounds__((Cfg<G, kPasses>::kThreads), 1)
 dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_out,
                      const __grid_constant__ CUtensorMap tmap_pre, const DsdParams p) {
     using C = Cfg<G, kPasses>;
+    constexpr bool kBf16 = C::kBf16, kIo16 = C::kIo16;
+    // bf16 tensors need no promotion against accumulation drift: a row is drained once, at its end
+    constexpr int32_t kDrainFlag = kIo16 ? kPlanRowEnd : kPlanDrain;
     constexpr int XS = C::kXStages;
     constexpr int kFirstDrainWarp = C::kFirstDrainWarp;
     constexpr int kSplitGroups = C::kSplitGroups;
@@ -308,7 +314,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 const uint32_t firsts = __ballot_sync(0xffffffffu, (mine4.w & kPlanFirst) != 0);
                 const uint32_t lasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanLast) != 0);
                 const uint32_t wlasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanWarpLast) != 0);
-                const uint32_t drains = __ballot_sync(0xffffffffu, (mine4.w & kPlanDrain) != 0);
+                const uint32_t drains = __ballot_sync(0xffffffffu, (mine4.w & kDrainFlag) != 0);
                 const uint32_t idle_b0 = __ballot_sync(0xffffffffu, (mine4.w & (1 << kPlanIdleShift)) != 0);
                 const uint32_t idle_b1 = __ballot_sync(0xffffffffu, (mine4.w & (2 << kPlanIdleShift)) != 0);
                 const uint32_t row_b2 = __ballot_sync(0xffffffffu, (mine4.z & 4) != 0);
@@ -329,7 +335,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     // the warp that issues a slab's last block also arrives for the warps that have none in it
                     const uint32_t idle = ((lasts >> i) & 1u) * (((idle_b0 >> i) & 1u) | (((idle_b1 >> i) & 1u) << 1));
                     const uint64_t b_desc =
-                        kPasses == 0 ? smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage16Lbo, kImage16Sbo)
+                        kBf16 ? smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage16Lbo, kImage16Sbo)
                                      : smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
                     const uint32_t a_hi = tmem + C::kAccCols + as * C::kAStageCols;
                     const uint32_t d = tmem + row * C::kRowCols;
@@ -349,7 +355,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     tc_fence_after();
                     const long long ti = tracing ? clock64() : 0;
                     if (elect_one() & (bad == 0)) {
-                        if (kPasses == 0) {
+                        if (kBf16) {
 #pragma unroll
                             for (int s = 0; s < 2; ++s)  // k-step of 16: 8 columns (bf16 pairs) further, two k-chunks further
                                 mma_ts_f16(d, a_hi + s * 8, b_desc + (uint64_t)(s * (kImage16StepBytes >> 4)), idesc_bf16,
@@ -407,37 +413,53 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 // the test of the tensor-memory stage's release travels while the slab is read and split
                 const uint32_t a_parity = ((uint32_t)(s / AS) & 1u) ^ 1u;
                 const bool a_free = mbar_test_wait(a_empty(as), a_parity);
-                uint32_t hi[32], lo[32];
-                {
-                    const uint8_t* xrow = smem_gen + C::kOffX + xs * kSlabBytes + row * 128;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        // 128-byte swizzle: the 16-byte chunk index is XORed with (row mod 8)
-                        const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((j ^ (row & 7)) << 4));
-                        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            hi[j * 4 + q] = u[q];
-                            if (kPasses == 3)
-                                lo[j * 4 + q] = __float_as_uint(__uint_as_float(u[q]) - __uint_as_float(u[q] & 0xffffe000u));
-                        }
-                    }
-                }
-                mbar_arrive(x_empty(xs));
-                if (!a_free) wait(a_empty(as), a_parity, 1);
-                tc_fence_after();
                 const uint32_t a_hi = tmem_lane + C::kAccCols + as * C::kAStageCols;
-                if (kPasses == 0) {
-                    uint32_t packed[16];  // column j: k = 2j in the low half, k = 2j + 1 in the high half
+                if (kIo16) {
+                    // bf16 slab, 64-byte rows (64-byte swizzle: 16-byte chunk index XOR (row / 2) mod 4): the row's 32
+                    // values are the 16 k-pairs tensor memory wants, as they lie
+                    uint32_t packed[16];
+                    const uint8_t* xrow = smem_gen + C::kOffX + xs * kSlabBytes + row * 64;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(hi[2 * j]), __uint_as_float(hi[2 * j + 1]));
-                        packed[j] = *reinterpret_cast<const uint32_t*>(&pr);
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((j ^ ((row >> 1) & 3)) << 4));
+                        packed[4 * j + 0] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
                     }
+                    mbar_arrive(x_empty(xs));
+                    if (!a_free) wait(a_empty(as), a_parity, 1);
+                    tc_fence_after();
                     tmem_st16(a_hi, packed);
                 } else {
-                    tmem_st32(a_hi, hi);
-                    if (kPasses == 3) tmem_st32(a_hi + 32, lo);
+                    uint32_t hi[32], lo[32];
+                    {
+                        const uint8_t* xrow = smem_gen + C::kOffX + xs * kSlabBytes + row * 128;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            // 128-byte swizzle: the 16-byte chunk index is XORed with (row mod 8)
+                            const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((j ^ (row & 7)) << 4));
+                            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                hi[j * 4 + q] = u[q];
+                                if (kPasses == 3)
+                                    lo[j * 4 + q] = __float_as_uint(__uint_as_float(u[q]) - __uint_as_float(u[q] & 0xffffe000u));
+                            }
+                        }
+                    }
+                    mbar_arrive(x_empty(xs));
+                    if (!a_free) wait(a_empty(as), a_parity, 1);
+                    tc_fence_after();
+                    if (kBf16) {
+                        uint32_t packed[16];  // column j: k = 2j in the low half, k = 2j + 1 in the high half
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(hi[2 * j]), __uint_as_float(hi[2 * j + 1]));
+                            packed[j] = *reinterpret_cast<const uint32_t*>(&pr);
+                        }
+                        tmem_st16(a_hi, packed);
+                    } else {
+                        tmem_st32(a_hi, hi);
+                        if (kPasses == 3) tmem_st32(a_hi + 32, lo);
+                    }
                 }
                 tmem_wait_st();
                 tc_fence_before();
@@ -485,11 +507,25 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 "selp.u32 %0, 1, 0, r;\n\t}"
                 : "=r"(any_bad) : "r"(bad) : "memory");
             if (any_bad) return false;
-            uint8_t* dst = smem_gen + C::kOffOut + (n_out & 1u) * kSlabBytes + row * 128;
+            if (kIo16) {  // bf16 output tile: 64-byte rows under the 64-byte swizzle
+                uint8_t* dst = smem_gen + C::kOffOut + (n_out & 1u) * kSlabBytes + row * 64;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                *reinterpret_cast<float4*>(dst + ((j ^ (row & 7)) << 4)) =
-                    make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const __nv_bfloat162 pr = __floats2bfloat162_rn(v[j * 8 + 2 * q], v[j * 8 + 2 * q + 1]);
+                        w[q] = *reinterpret_cast<const uint32_t*>(&pr);
+                    }
+                    *reinterpret_cast<uint4*>(dst + ((j ^ ((row >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else {
+                uint8_t* dst = smem_gen + C::kOffOut + (n_out & 1u) * kSlabBytes + row * 128;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<float4*>(dst + ((j ^ (row & 7)) << 4)) =
+                        make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+            }
             fence_proxy_async_smem();  // generic-proxy writes, read by the TMA through the async proxy
             asm volatile("bar.sync 2, 128;" ::: "memory");
             if (issuer) {
@@ -585,7 +621,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             for (int base = e0; base < e1 && ok; base += 32) {
                 const int4 mine = ahead;
                 ahead = prefetch(tile, base, e1);
-                uint32_t drains = __ballot_sync(0xffffffffu, (mine.w & kPlanDrain) != 0);
+                uint32_t drains = __ballot_sync(0xffffffffu, (mine.w & kDrainFlag) != 0);
                 const uint32_t row_ends = __ballot_sync(0xffffffffu, (mine.w & kPlanRowEnd) != 0);
                 while (drains != 0) {
                     const int i = __ffs(drains) - 1;
@@ -741,6 +777,9 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
                             bool out_colmajor, const DsdEpilogue& epilogue, cudaStream_t stream) {
     if (!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return cudaErrorNotSupported;
+    const bool io16 = epilogue.io_bf16;
+    if (io16 && (precision != BSMM_PREC_BF16 || out_colmajor || epilogue.residual != nullptr || epilogue.pre_act != nullptr))
+        return cudaErrorNotSupported;
     if (out_colmajor && (epilogue.residual != nullptr || epilogue.pre_act != nullptr || epilogue.activation != 0))
         return cudaErrorNotSupported;
     if (!plan_group_valid(group)) return cudaErrorInvalidValue;
@@ -755,14 +794,19 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     // m rows; the remaining accumulator lanes see stale values and their outputs are never stored.
     const uint32_t box_rows = (uint32_t)(m < kTileTokens ? m : kTileTokens);
     CUtensorMap tmap_a;
-    cudaError_t err = make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)k, (uint64_t)m, 32,
-                                   box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
+    cudaError_t err =
+        io16 ? make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, (uint64_t)k, (uint64_t)m, 32, box_rows,
+                            CU_TENSOR_MAP_SWIZZLE_64B)
+             : make_tmap_2d(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)k, (uint64_t)m, 32, box_rows,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
     if (err != cudaSuccess) return err;
     // the epilogue's stores: boxes of 32 columns x up to 128 token rows of the row-major output
     CUtensorMap tmap_out = tmap_a;
     if (!out_colmajor) {
-        err = make_tmap_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, (uint64_t)n, (uint64_t)m, 32, box_rows,
-                           CU_TENSOR_MAP_SWIZZLE_128B);
+        err = io16 ? make_tmap_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, (uint64_t)n, (uint64_t)m, 32, box_rows,
+                                  CU_TENSOR_MAP_SWIZZLE_64B)
+                   : make_tmap_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, (uint64_t)n, (uint64_t)m, 32, box_rows,
+                                  CU_TENSOR_MAP_SWIZZLE_128B);
         if (err != cudaSuccess) return err;
     }
 
@@ -792,13 +836,20 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     p.groups = (int32_t)groups;
     p.n_tiles = (int32_t)(groups * tiles);
     p.out_colmajor = out_colmajor ? 1 : 0;
-    p.x_bytes = box_rows * 128u;
+    p.x_bytes = box_rows * (io16 ? 64u : 128u);
     p.trace = g_trace_buffer;
     p.trace_block = g_trace_block;
     const bool split = precision == BSMM_PREC_TF32X3;
     if (split && group == 8) return cudaErrorInvalidValue;  // 8 rows x 64 columns leave no tensor memory for A
     if (precision == BSMM_PREC_BF16) {
         if (group == 5) return cudaErrorInvalidValue;  // the 5-row tile exists for 3xTF32 only
+        if (io16) {
+            switch (group) {
+                case 4: return launch_dsd_g<4, 4>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+                case 6: return launch_dsd_g<6, 4>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+                default: return launch_dsd_g<8, 4>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+            }
+        }
         switch (group) {
             case 4: return launch_dsd_g<4, 0>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
             case 6: return launch_dsd_g<6, 0>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);

@@ -52,6 +52,7 @@ struct DsdEpilogue {
     const float* residual = nullptr;  // [m, n] row-major, added with the bias
     float* pre_act = nullptr;         // [m, n] row-major: receives a * W^T + bias + residual when an activation is applied
     int activation = 0;               // 0 none, 1 GELU (erf form)
+    bool io_bf16 = false;             // `a` and `out` are bf16 tensors (BSMM_PREC_BF16, row-major output)
 };
 cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
@@ -65,7 +66,8 @@ int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, i
 // operand whose token count is not a multiple of 4)
 cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b, bool b_feature_major, int64_t rows,
                               int64_t cols, int64_t tokens, float* sparse_c, const int32_t* csr_idx, const void* plan,
-                              int64_t nnz, float* block_sumsq, void* workspace, uint32_t precision, cudaStream_t stream);
+                              int64_t nnz, float* block_sumsq, void* workspace, uint32_t precision, bool io_bf16,
+                              cudaStream_t stream);
 
 // Address and size of the library's static scratch array on the current device (first call per
 // device resolves the symbol).

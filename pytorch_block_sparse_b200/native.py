@@ -16,8 +16,8 @@ LIB_PATH = os.path.join(_PKG_DIR, "libbsmm_b200.so")
 ABI_VERSION = 2
 OK = 0
 PREC_FP32_SIMT, PREC_TF32X3, PREC_BF16, PREC_TF32 = 0, 1, 2, 3
-DSD_DGRAD, DSD_OUT_COLMAJOR, DSD_GELU = 0x10, 0x20, 0x40
-SDDMM_A_COLMAJOR, SDDMM_B_COLMAJOR = 0x10, 0x20
+DSD_DGRAD, DSD_OUT_COLMAJOR, DSD_GELU, DSD_IO_BF16 = 0x10, 0x20, 0x40, 0x80
+SDDMM_A_COLMAJOR, SDDMM_B_COLMAJOR, SDDMM_IO_BF16 = 0x10, 0x20, 0x40
 
 PRECISIONS = {"fp32": PREC_FP32_SIMT, "simt": PREC_FP32_SIMT, "tf32x3": PREC_TF32X3, "tf32": PREC_TF32, "bf16": PREC_BF16}
 EXPORTS = (
@@ -309,15 +309,22 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
     lib = load()
     m, k = a.shape
     prec = packed.precision
-    want = torch.float32  # every mode reads and writes fp32 tensors; 'bf16' rounds the operands in the kernel
+    # fp32 tensors in and out ('bf16' precision then rounds the operands inside the kernel) -- except that the 'bf16'
+    # precision takes a bf16 activation tensor as it is and then also writes a bf16 output: half the bytes
+    io16 = (a.dtype == torch.bfloat16 and prec == PREC_BF16 and not out_colmajor and residual is None
+            and pre_activation is None and plan.nnz > 0 and k > 0)
+    want = torch.bfloat16 if io16 else torch.float32
     if a.dtype != want:
         a = a.to(want)
+    if out is not None and out.dtype != want:
+        raise NativeError("out must be %s for this call, got %s" % (want, out.dtype))
     if out is None:
         out = torch.empty((n_out, m) if out_colmajor else (m, n_out), dtype=want, device=a.device)
     if activation not in (None, "gelu"):
         raise ValueError("unknown activation %r (None or 'gelu')" % (activation,))
     flags = prec | (0 if transpose else DSD_DGRAD) | (DSD_OUT_COLMAJOR if out_colmajor else 0)
     flags |= DSD_GELU if activation == "gelu" else 0
+    flags |= DSD_IO_BF16 if io16 else 0
     plan_buf = None
     if prec != PREC_FP32_SIMT:
         group = plan.group_for(m, prec)
@@ -326,8 +333,8 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
     if residual is not None:
-        residual = residual.detach().reshape(m, n_out).to(want).contiguous()
-    if pre_activation is not None and (pre_activation.dtype != want or not pre_activation.is_contiguous()
+        residual = residual.detach().reshape(m, n_out).to(torch.float32).contiguous()
+    if pre_activation is not None and (pre_activation.dtype != torch.float32 or not pre_activation.is_contiguous()
                                        or pre_activation.numel() != m * n_out):
         raise NativeError("pre_activation must be a contiguous float32 tensor of the output's size")
     with torch.cuda.device(a.device):
@@ -410,9 +417,12 @@ def sddmm(a, a_rowmajor, b, b_rowmajor, blocks, out, precision=None, block_sumsq
     tokens, rows = a.shape
     cols = b.shape[1]
     nnz = blocks.shape[0] // 2
-    if a.dtype != torch.float32 or b.dtype != torch.float32:
+    io16 = (a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and prec == PREC_BF16 and a_rowmajor and b_rowmajor
+            and plan is not None and tokens >= 32)
+    if not io16 and (a.dtype != torch.float32 or b.dtype != torch.float32):
         a, b = a.float(), b.float()
     flags = prec | (0 if a_rowmajor else SDDMM_A_COLMAJOR) | (0 if b_rowmajor else SDDMM_B_COLMAJOR)
+    flags |= SDDMM_IO_BF16 if io16 else 0
     ws_bytes = lib.bsmm_sddmm_workspace_bytes(rows, cols, tokens, nnz, flags) if plan is not None else 0
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes > 0 else None
     with torch.cuda.device(a.device):

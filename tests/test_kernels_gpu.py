@@ -512,3 +512,45 @@ def test_full_size_config5_shard():
     """One GPU's block-row shard of benchmark configuration 5 (32768 x 8192 at density 0.1 over 8 GPUs:
     4096 x 8192 per GPU) on its 65536 tokens: 512 token tiles, 8 token ranges in the weight gradient."""
     _full_size_case((4096, 8192), int(0.1 * 4096 * 8192 / 1024), 65536, "tf32x3", seed=71)
+
+
+def test_bf16_tensors_in_memory():
+    """'bf16' precision with bf16 activations and outputs in HBM (benchmark configuration 5 says "X bf16"): the kernels
+    read bf16 boxes and write bf16 tiles, the weight gradient stays fp32.  Checked against the fp32 oracle on the
+    bf16-rounded inputs (<= 1e-2), and against the same precision on fp32 copies of those inputs (same operand
+    values, so only the output rounding differs)."""
+    m = make_matrix((512, 1024), n_blocks=200, seed=91)
+    x = randn((777, 1024), seed=92).bfloat16()
+    dy = randn((777, 512), seed=93).bfloat16()
+    bias = (randn((512,), seed=94) * 0.02)
+    shape, blocks, data = host(m)
+    y = m.reverse_matmul(x.cuda(), transpose=True, bias=bias.cuda(), precision="bf16")
+    dx = m.reverse_matmul(dy.cuda(), transpose=False, precision="bf16")
+    dw = m.matmul_with_output_sparse_support(dy.cuda(), x.cuda(), precision="bf16")
+    torch.cuda.synchronize()
+    assert y.dtype == torch.bfloat16 and dx.dtype == torch.bfloat16 and dw.dtype == torch.float32
+    xf, dyf = x.float(), dy.float()
+    check(y.float(), orc.forward(xf.numpy(), shape, blocks, data, bias.numpy()), "bf16", "fwd")
+    check(dx.float(), orc.dgrad(dyf.numpy(), shape, blocks, data), "bf16", "dgrad")
+    check(dw, orc.wgrad(dyf.numpy(), xf.numpy(), shape, blocks), "bf16", "wgrad")
+    y32 = m.reverse_matmul(xf.cuda(), transpose=True, bias=bias.cuda(), precision="bf16")
+    dw32 = m.matmul_with_output_sparse_support(dyf.cuda(), xf.cuda(), precision="bf16")
+    assert float((y.float() - y32).norm() / y32.norm()) < 4e-3      # one bf16 rounding of the output
+    assert float((dw - dw32).norm() / dw32.norm()) < 1e-5           # same operands, fp32 result
+    # through the layer: bf16 in, bf16 out, fp32 weight gradient
+    from pytorch_block_sparse_b200 import BlockSparseLinear
+    native.set_default_precision("bf16")
+    try:
+        np.random.seed(95)
+        lin = BlockSparseLinear(1024, 512, bias=True, density=0.4)
+        xb = x.cuda().requires_grad_(True)
+        out = lin(xb)
+        out.backward(dy.cuda())
+        assert out.dtype == torch.bfloat16 and xb.grad.dtype == torch.bfloat16
+        assert lin.weight.data.grad.dtype == torch.float32 and lin.bias.grad.dtype == torch.float32
+        dense = lin.weight.to_dense().detach()
+        want = xf.cuda() @ dense.t() + lin.bias.detach()
+        assert float((out.float() - want).norm() / want.norm()) < 1e-2
+    finally:
+        native.set_default_precision("tf32x3")
+    assert_device_healthy()
