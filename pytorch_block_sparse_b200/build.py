@@ -1,6 +1,11 @@
 """Builds libbsmm_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
 Usage: ``python -m pytorch_block_sparse_b200.build [--force] [--verbose]``.
+
+``python -m pytorch_block_sparse_b200.build --microbench [--run]`` compiles (and runs, on a B200) the
+single-CTA micro-benchmarks under ``csrc/microbench/``: cycles per ``tcgen05.mma`` by shape and operand source,
+the kernels' exact MMA sequences, mbarrier wait and ring hand-off costs, tensor-memory store/load costs and
+the L2 -> shared-memory bulk-copy bandwidth.  The kernels' cost model rests on these figures.
 """
 import os
 import subprocess
@@ -51,6 +56,33 @@ def build(force=False, verbose=False):
     return LIB_PATH
 
 
+MICROBENCH_DIR = os.path.join(CSRC, "microbench")
+MICROBENCH_BIN = os.path.join(PKG_DIR, "microbench_bin")
+
+
+def build_microbench(run=False):
+    """Compile every csrc/microbench/*.cu into microbench_bin/<name>; with run=True execute them in turn."""
+    os.makedirs(MICROBENCH_BIN, exist_ok=True)
+    built = []
+    for src in sorted(f for f in os.listdir(MICROBENCH_DIR) if f.endswith(".cu")):
+        exe = os.path.join(MICROBENCH_BIN, src[:-3])
+        cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+               "-I", CSRC, "-I", INCLUDE, "-o", exe, os.path.join(MICROBENCH_DIR, src)]
+        res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed:\n%s\n%s" % (" ".join(cmd), res.stdout))
+        built.append(exe)
+    if run:
+        for exe in built:
+            print("==", os.path.basename(exe), flush=True)
+            subprocess.run([exe], check=False)
+    return built
+
+
 if __name__ == "__main__":
-    build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
-    print(LIB_PATH)
+    if "--microbench" in sys.argv:
+        for path in build_microbench(run="--run" in sys.argv):
+            print(path)
+    else:
+        build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+        print(LIB_PATH)
