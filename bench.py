@@ -412,6 +412,25 @@ def run_sweep(dev, steps):
             entry["frac_of_measured_hbm"] = entry["algorithmic_gbs"] / measured_peaks()["hbm_gbs"]
         out["%s/%s" % (workload, prec_name)] = entry
         del pack, fwd, dgrad, wgrad
+    # host-side cost of one call: the smallest configuration is launch-bound, so the wall time of a long run of
+    # back-to-back asynchronous calls is what the Python layer, ctypes, the tensor-map encoding and the launch cost
+    import time as _time
+
+    case = LayerCase(WORKLOADS["c1"], dev)
+    pack, fwd, dgrad, wgrad = case.ops(native.resolve_precision("tf32x3"))
+    pack()
+    for name, fn in (("dsd", fwd), ("sddmm", wgrad), ("pack", pack)):
+        for _ in range(20):
+            fn()
+        torch.cuda.synchronize()
+        t0 = _time.perf_counter()
+        for _ in range(300):
+            fn()
+        host = (_time.perf_counter() - t0) / 300
+        torch.cuda.synchronize()
+        out["host_us_per_call/c1/" + name] = host * 1e6
+    del case, pack, fwd, dgrad, wgrad
+    torch.cuda.empty_cache()
     # one step of the sparsity optimizer (pruning + regrowth of 10 % of the blocks, Adam state attached) on the
     # headline layer: statistic kernel, k-smallest selection, sampling of empty positions, index rebuild
     cases.clear()
@@ -489,14 +508,46 @@ def run_c5(dev, world, rank, steps, precisions):
                 dist.all_reduce(dx)
                 torch.cuda.current_stream().wait_stream(side)
 
+        # the same step with the all-gather fused into the forward kernel: its epilogue stores this rank's columns into
+        # every rank's full-width output over NVLink peer mappings (symmetric memory) while it computes
+        fused_state = {}
+
+        def step_fused(_):
+            if "buf" not in fused_state:
+                from pytorch_block_sparse_b200.distributed import PeerOutputs
+
+                fused_state["outputs"] = PeerOutputs()
+                full_y, handle = fused_state["outputs"].get(m, world * n_local, y.dtype, dev)
+                fused_state["buf"], fused_state["handle"] = full_y, handle
+                fused_state["peers"] = [int(handle.buffer_ptrs[r]) for r in range(world) if r != rank]
+            handle = fused_state["handle"]
+            packed = native.pack_weights(data, prec)
+            handle.barrier()
+            native.dsd_matmul(x, plan_f, packed, n_local, True, bias=bias, out=fused_state["buf"],
+                              out_col0=rank * n_local, peer_outs=fused_state["peers"])
+            native.sddmm(dy, True, x, True, w.blocks, dw, precision=prec, plan=plan_w)
+            native.dsd_matmul(dy, plan_d, packed, k, False, out=dx)
+            dist.all_reduce(dx)
+            handle.barrier()
+
         res = {}
-        for name, coll in (("compute_ms", False), ("with_collectives_ms", True)):
+        legs_c5 = [("compute_ms", step, False), ("with_collectives_ms", step, True)]
+        if world > 1:
+            legs_c5.append(("with_fused_gather_ms", step_fused, True))
+        for name, fn, coll in legs_c5:
             if coll and world == 1:
                 res[name] = res["compute_ms"]
                 continue
             if world > 1:
                 dist.barrier()
-            ms = time_op(lambda: step(coll), max(2, min(steps, 5)), warm=2)
+            try:
+                ms = time_op(lambda: fn(coll), max(2, min(steps, 5)), warm=2)
+            except Exception as exc:  # symmetric memory may be unavailable on a box without peer access
+                if fn is step_fused:
+                    res[name] = None
+                    res["fused_gather_unavailable"] = str(exc)[:200]
+                    continue
+                raise
             if world > 1:
                 t = torch.tensor([ms], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -505,7 +556,10 @@ def run_c5(dev, world, rank, steps, precisions):
         res["tensors"] = "bf16 activations and outputs" if elem == 2 else "fp32"
         res["all_gather_bytes_per_rank"] = (world - 1) * m * n_local * elem if world > 1 else 0
         res["all_reduce_bytes"] = m * k * elem if world > 1 else 0
+        fused_state.clear()
         res["effective_tflops"] = f_total / (res["with_collectives_ms"] / 1e3) / 1e12
+        if res.get("with_fused_gather_ms"):
+            res["effective_tflops_fused_gather"] = f_total / (res["with_fused_gather_ms"] / 1e3) / 1e12
         res["effective_tflops_compute_only"] = f_total / (res["compute_ms"] / 1e3) / 1e12
         out[prec_name] = res
     return out

@@ -145,6 +145,25 @@ int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
                    const float* residual, float* pre_activation, uint32_t flags, bsmm_stream_t stream);
 
 /*
+ * bsmm_dsd_fused writing a column slice of a wider output and, tile by tile as rows complete, the same slice of
+ * further tensors -- the other GPUs' copies of the output, reached through NVLink peer mappings (plain TMA stores
+ * to a peer address).  This is the forward product of a layer sharded by output features fused
+ * with its all-gather: every rank's kernel delivers its columns to every rank's full-width output while it
+ * computes, and a barrier across the ranks after the kernel replaces the collective.  The reference has no
+ * multi-GPU path (its only artefact is a DataParallel smoke test, tests/test_data_parallel.py:11-17).
+ *   out            [m, out_ld] row-major; this call writes columns out_col0 .. out_col0 + n - 1 (multiples of 32);
+ *                  out_ld = 0 means n
+ *   peer_outs      HOST array of n_peer_outs (<= 8) device-visible pointers to tensors laid out like `out`
+ *   bias, residual, pre_activation stay [n] / [m, n] tensors of this rank's slice
+ * A tile leaves for the peers only when its row is complete (rows of more than 48 blocks gather their parts in
+ * the local output first).  Tensor-core precisions, forward, row-major output only.
+ */
+int bsmm_dsd_multi(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+                   const float* data, const void* packed, const void* plan, int64_t n, void* out, int64_t out_ld,
+                   int64_t out_col0, const float* bias, const float* residual, float* pre_activation,
+                   void* const* peer_outs, int n_peer_outs, uint32_t flags, bsmm_stream_t stream);
+
+/*
  * Dense^T x dense -> block-sparse (SDDMM).  Replaces blocksparse_matmul_back_cutlass
  * (reference native/block_sparse_native.cpp:18-29, native/block_sparse_cutlass_kernel_back.cu:118-160):
  *   sparse_c[s*32 + c][r] = sum_t a[t, R*32+r] * b[t, C*32+c],  (C, R) = blocks[2s], blocks[2s+1]

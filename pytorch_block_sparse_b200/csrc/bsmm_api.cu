@@ -104,13 +104,24 @@ int bsmm_build_plan(const int32_t* ptr, const int32_t* idx, int64_t n_out_blocks
 int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
                    const float* data, const void* packed, const void* plan, int64_t n, void* out, const float* bias,
                    const float* residual, float* pre_activation, uint32_t flags, bsmm_stream_t stream) {
+    return bsmm_dsd_multi(a, m, k, ptr, idx, nnz, data, packed, plan, n, out, 0, 0, bias, residual, pre_activation,
+                          nullptr, 0, flags, stream);
+}
+
+int bsmm_dsd_multi(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+                   const float* data, const void* packed, const void* plan, int64_t n, void* out, int64_t out_ld,
+                   int64_t out_col0, const float* bias, const float* residual, float* pre_activation,
+                   void* const* peer_outs, int n_peer_outs, uint32_t flags, bsmm_stream_t stream) {
     forget_earlier_errors();
+    if (n_peer_outs < 0 || n_peer_outs > 8 || (n_peer_outs > 0 && peer_outs == nullptr)) return BSMM_ERR_INVALID_ARGUMENT;
+    if (out_ld < 0 || out_col0 < 0) return BSMM_ERR_INVALID_ARGUMENT;
+    const bool placed = n_peer_outs > 0 || (out_ld != 0 && out_ld != n) || out_col0 != 0;
     const uint32_t precision = flags & BSMM_PREC_MASK;
     const bool dgrad = (flags & BSMM_DSD_DGRAD) != 0;
     const bool colmajor = (flags & BSMM_DSD_OUT_COLMAJOR) != 0;
     const bool gelu = (flags & BSMM_DSD_GELU) != 0;
     const bool io16 = (flags & BSMM_DSD_IO_BF16) != 0;
-    const bool fused = gelu || residual != nullptr || pre_activation != nullptr;
+    const bool fused = gelu || residual != nullptr || pre_activation != nullptr || placed;
     if (m < 0 || n < 0 || k < 0 || nnz < 0 || (n % 32) != 0 || (k % 32) != 0) return BSMM_ERR_INVALID_ARGUMENT;
     if (m == 0 || n == 0) return BSMM_OK;
     if (ptr == nullptr || out == nullptr || (nnz > 0 && (idx == nullptr || data == nullptr || a == nullptr)))
@@ -147,6 +158,13 @@ int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
         epilogue.pre_act = pre_activation;
         epilogue.activation = gelu ? 1 : 0;
         epilogue.io_bf16 = io16;
+        epilogue.out_ld = out_ld;
+        epilogue.out_col0 = out_col0;
+        epilogue.n_peer_outs = n_peer_outs;
+        for (int i = 0; i < n_peer_outs; ++i) {
+            if (!aligned(peer_outs[i], 16)) return BSMM_ERR_INVALID_ARGUMENT;
+            epilogue.peer_outs[i] = peer_outs[i];
+        }
         return cuda_status(bsmm::launch_dsd_umma(a, m, k, nnz, packed, plan, group, n, out, bias, precision, dgrad,
                                                  colmajor, epilogue, s));
     }

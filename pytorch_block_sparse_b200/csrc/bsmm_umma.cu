@@ -87,6 +87,13 @@ struct Cfg {
     static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
 };
 
+// Tensor maps of further output tensors: the same tiles are stored to each of them (peer GPUs' buffers reached
+// through NVLink; plain TMA stores).
+constexpr int kMaxPeerOutputs = 8;
+struct PeerMaps {
+    CUtensorMap map[kMaxPeerOutputs];
+};
+
 struct DsdParams {
     const uint8_t* packed;      // weight images of this orientation, slot-major
     const int32_t* group_off;   // [groups + 1]
@@ -96,6 +103,9 @@ struct DsdParams {
     const float* residual;      // may be null: [m, n] row-major, added with the bias (row-major output only)
     float* pre_act;             // may be null: [m, n] row-major, receives the sum before the activation
     int32_t act;                // 0 none, 1 GELU: applied to a row's completed sum (row-major output only)
+    int32_t n_peers;            // further output tensors (other GPUs' copies of the output) that receive every completed tile
+    int64_t out_ld;             // row pitch of the output tensor(s) in elements (n, or the full width when this call
+    int64_t out_col0;           //   writes a column slice starting at out_col0)
     float* out;                 // (bf16 in the bf16-tensor variant, which writes only through tmap_out)
     unsigned int* status;       // device status word
     int64_t m, n;
@@ -123,7 +133,8 @@ __device__ __noinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(
 template <int G, int kPasses>
 __global__ void __launch_bounds__((Cfg<G, kPasses>::kThreads), 1)
 dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_out,
-                     const __grid_constant__ CUtensorMap tmap_pre, const DsdParams p) {
+                     const __grid_constant__ CUtensorMap tmap_pre, const __grid_constant__ PeerMaps peers,
+                     const DsdParams p) {
     using C = Cfg<G, kPasses>;
     constexpr bool kBf16 = C::kBf16, kIo16 = C::kIo16;
     // bf16 tensors need no promotion against accumulation drift: a row is drained once, at its end
@@ -491,7 +502,8 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         // behind at a barrier.
         // put_tile: the 128 threads' rows v go to the tile (col0, tok0) of the tensor behind `tmap`, overwriting it
         // or adding to it.
-        auto put_tile = [&](const float (&v)[32], const CUtensorMap* tmap, int64_t col0, int32_t tok0, bool overwrite) -> bool {
+        auto put_tile = [&](const float (&v)[32], const CUtensorMap* tmap, int64_t col0, int32_t tok0, bool overwrite,
+                            bool to_peers = false) -> bool {
             const uint32_t buf = smem_base + C::kOffOut + (n_out & 1u) * kSlabBytes;
             // the tile's previous store (two promotions ago) must have read it; a reduction additionally waits
             // until every earlier store of this thread is complete in global memory
@@ -531,6 +543,8 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             if (issuer) {
                 if (overwrite) tma_store_2d(tmap, buf, (int32_t)col0, tok0);
                 else tma_reduce_add_2d(tmap, buf, (int32_t)col0, tok0);
+                if (to_peers)  // the completed tile also goes to every other GPU's copy of the output
+                    for (int i = 0; i < p.n_peers; ++i) tma_store_2d(&peers.map[i], buf, (int32_t)col0, tok0);
                 bulk_commit_group();
             }
             ++n_out;
@@ -563,18 +577,22 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     }
                 }
             }
-            if (p.act == 0) return put_tile(v, &tmap_out, col0, tok0, first);
+            // x coordinate of the tile in the output tensor(s): the column slice this call owns starts at out_col0
+            const int64_t xo = col0 + p.out_col0;
+            if (p.act == 0 && p.n_peers == 0) return put_tile(v, &tmap_out, xo, tok0, first);
+            // With an activation or peer outputs a tile leaves only when its row is complete.
             const bool keep_pre = p.pre_act != nullptr;
             const CUtensorMap* sums = keep_pre ? &tmap_pre : &tmap_out;
-            if (!last) return put_tile(v, sums, col0, tok0, first);
+            const int64_t xs = keep_pre ? col0 : xo;
+            if (!last) return put_tile(v, sums, xs, tok0, first);
             if (!first) {
-                if (!put_tile(v, sums, col0, tok0, false)) return false;
+                if (!put_tile(v, sums, xs, tok0, false)) return false;
                 if (issuer) {
                     bulk_wait_group<0>();                              // the reduction has reached global memory
                     asm volatile("fence.proxy.async;" ::: "memory");   // async-proxy writes before the generic reads below
                 }
                 asm volatile("bar.sync 2, 128;" ::: "memory");
-                const float* total = (keep_pre ? p.pre_act : p.out) + tok * p.n + col0;
+                const float* total = keep_pre ? p.pre_act + tok * p.n + col0 : p.out + tok * p.out_ld + xo;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float4 t4 = live ? __ldcg(reinterpret_cast<const float4*>(total) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -583,9 +601,10 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             } else if (keep_pre) {
                 if (!put_tile(v, &tmap_pre, col0, tok0, true)) return false;
             }
-            gelu(v);
-            return put_tile(v, &tmap_out, col0, tok0, true);
+            if (p.act != 0) gelu(v);
+            return put_tile(v, &tmap_out, xo, tok0, true, true);
         };
+
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += tile_step) {
             const int g = tile % p.groups;
             const int e0 = __ldg(p.group_off + g), e1 = __ldg(p.group_off + g + 1);
@@ -699,7 +718,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 template <int G, int kPasses>
 cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const CUtensorMap& tmap_out, const CUtensorMap& tmap_pre,
-                         const DsdParams& p, int64_t tiles, cudaStream_t stream) {
+                         const PeerMaps& peers, const DsdParams& p, int64_t tiles, cudaStream_t stream) {
     // The shared-memory attribute and the SM count are per device: asked once per device and kernel variant,
     // then remembered (plain arrays; two threads racing on the first call store the same values).
     constexpr int kMaxDevices = 64;
@@ -720,7 +739,7 @@ cudaError_t launch_dsd_g(const CUtensorMap& tmap_a, const CUtensorMap& tmap_out,
     const int sms = sm_count[dev];
     const int64_t n_tiles = (int64_t)p.groups * tiles;
     const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);  // persistent: one CTA per SM
-    dsd_umma_tf32_kernel<G, kPasses><<<grid, Cfg<G, kPasses>::kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, tmap_out, tmap_pre, p);
+    dsd_umma_tf32_kernel<G, kPasses><<<grid, Cfg<G, kPasses>::kThreads, Cfg<G, kPasses>::kSmemBytes, stream>>>(tmap_a, tmap_out, tmap_pre, peers, p);
     return cudaGetLastError();
 }
 
@@ -780,6 +799,11 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     const bool io16 = epilogue.io_bf16;
     if (io16 && (precision != BSMM_PREC_BF16 || out_colmajor || epilogue.residual != nullptr || epilogue.pre_act != nullptr))
         return cudaErrorNotSupported;
+    if (epilogue.n_peer_outs < 0 || epilogue.n_peer_outs > kMaxPeerOutputs) return cudaErrorInvalidValue;
+    const int64_t out_ld = epilogue.out_ld > 0 ? epilogue.out_ld : n;
+    if (out_colmajor && (epilogue.n_peer_outs > 0 || out_ld != n || epilogue.out_col0 != 0)) return cudaErrorNotSupported;
+    if (out_ld < n + epilogue.out_col0 || epilogue.out_col0 < 0 || (out_ld % 32) != 0 || (epilogue.out_col0 % 32) != 0)
+        return cudaErrorInvalidValue;
     if (out_colmajor && (epilogue.residual != nullptr || epilogue.pre_act != nullptr || epilogue.activation != 0))
         return cudaErrorNotSupported;
     if (!plan_group_valid(group)) return cudaErrorInvalidValue;
@@ -802,12 +826,22 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     if (err != cudaSuccess) return err;
     // the epilogue's stores: boxes of 32 columns x up to 128 token rows of the row-major output
     CUtensorMap tmap_out = tmap_a;
+    PeerMaps peers;
+    for (int i = 0; i < kMaxPeerOutputs; ++i) peers.map[i] = tmap_a;  // placeholders where unused
     if (!out_colmajor) {
-        err = io16 ? make_tmap_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, (uint64_t)n, (uint64_t)m, 32, box_rows,
-                                  CU_TENSOR_MAP_SWIZZLE_64B)
-                   : make_tmap_2d(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, (uint64_t)n, (uint64_t)m, 32, box_rows,
-                                  CU_TENSOR_MAP_SWIZZLE_128B);
+        auto out_map = [&](CUtensorMap* map, void* base) {
+            return io16 ? make_tmap_2d(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, (uint64_t)out_ld, (uint64_t)m, 32, box_rows,
+                                       CU_TENSOR_MAP_SWIZZLE_64B)
+                        : make_tmap_2d(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, (uint64_t)out_ld, (uint64_t)m, 32, box_rows,
+                                       CU_TENSOR_MAP_SWIZZLE_128B);
+        };
+        err = out_map(&tmap_out, out);
         if (err != cudaSuccess) return err;
+        for (int i = 0; i < epilogue.n_peer_outs; ++i) {
+            if (epilogue.peer_outs[i] == nullptr) return cudaErrorInvalidValue;
+            err = out_map(&peers.map[i], epilogue.peer_outs[i]);
+            if (err != cudaSuccess) return err;
+        }
     }
 
     CUtensorMap tmap_pre = tmap_out;
@@ -821,6 +855,9 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     p.residual = epilogue.residual;
     p.pre_act = epilogue.pre_act;
     p.act = epilogue.activation;
+    p.n_peers = epilogue.n_peer_outs;
+    p.out_ld = out_ld;
+    p.out_col0 = epilogue.out_col0;
     p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * packed_slot_bytes(precision) : 0);
     p.group_off = static_cast<const int32_t*>(plan);
     p.group_slabs = p.group_off + groups + 1;
@@ -845,22 +882,22 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
         if (group == 5) return cudaErrorInvalidValue;  // the 5-row tile exists for 3xTF32 only
         if (io16) {
             switch (group) {
-                case 4: return launch_dsd_g<4, 4>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
-                case 6: return launch_dsd_g<6, 4>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
-                default: return launch_dsd_g<8, 4>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+                case 4: return launch_dsd_g<4, 4>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
+                case 6: return launch_dsd_g<6, 4>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
+                default: return launch_dsd_g<8, 4>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
             }
         }
         switch (group) {
-            case 4: return launch_dsd_g<4, 0>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
-            case 6: return launch_dsd_g<6, 0>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
-            default: return launch_dsd_g<8, 0>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+            case 4: return launch_dsd_g<4, 0>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
+            case 6: return launch_dsd_g<6, 0>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
+            default: return launch_dsd_g<8, 0>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
         }
     }
-    if (group == 5) return split ? launch_dsd_g<5, 3>(tmap_a, tmap_out, tmap_pre, p, tiles, stream) : cudaErrorInvalidValue;
+    if (group == 5) return split ? launch_dsd_g<5, 3>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream) : cudaErrorInvalidValue;
     switch (group) {
-        case 4: return split ? launch_dsd_g<4, 3>(tmap_a, tmap_out, tmap_pre, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
-        case 6: return split ? launch_dsd_g<6, 3>(tmap_a, tmap_out, tmap_pre, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
-        default: return launch_dsd_g<8, 1>(tmap_a, tmap_out, tmap_pre, p, tiles, stream);
+        case 4: return split ? launch_dsd_g<4, 3>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream) : launch_dsd_g<4, 1>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
+        case 6: return split ? launch_dsd_g<6, 3>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream) : launch_dsd_g<6, 1>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
+        default: return launch_dsd_g<8, 1>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
     }
 }
 

@@ -53,6 +53,10 @@ struct DsdEpilogue {
     float* pre_act = nullptr;         // [m, n] row-major: receives a * W^T + bias + residual when an activation is applied
     int activation = 0;               // 0 none, 1 GELU (erf form)
     bool io_bf16 = false;             // `a` and `out` are bf16 tensors (BSMM_PREC_BF16, row-major output)
+    int64_t out_ld = 0;               // row pitch of `out` in elements when it is wider than n (0: n)
+    int64_t out_col0 = 0;             // first column of `out` this call writes (multiple of 32)
+    void* peer_outs[8] = {nullptr};   // further tensors laid out like `out` (other GPUs' copies) that receive every tile
+    int n_peer_outs = 0;
 };
 cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,

@@ -16,6 +16,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from . import native
 from .block_sparse import BlockSparseMatrix, BlockSparseMatrixBase
 from .block_sparse_linear import BlockSparseLinearFunction
 
@@ -114,15 +115,79 @@ class _SumInputGrad(torch.autograd.Function):
         return grad, None
 
 
+class PeerOutputs:
+    """Full-width output tensors in symmetric memory (one per rank, each mapped into every rank's address space
+    over NVLink) for the forward product fused with its all-gather: every rank's kernel stores its column slice
+    into all of them.  One tensor per (rows, width, dtype), kept for reuse."""
+
+    def __init__(self, group=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self._buffers = {}
+
+    def get(self, rows, width, dtype, device):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        key = (rows, width, dtype, str(device))
+        if key not in self._buffers:
+            buf = symm_mem.empty((rows, width), dtype=dtype, device=device)
+            handle = symm_mem.rendezvous(buf, self.group)
+            self._buffers[key] = (buf, handle)
+        return self._buffers[key]
+
+
+class _FusedColumnParallelFunction(torch.autograd.Function):
+    """Forward of this rank's block-row shard with the all-gather fused into the kernel's epilogue (peer stores),
+    backward as for the plain shard on this rank's column slice of the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, input, weight_data, weight, bias, outputs, group):
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        n_local = weight.shape[0]
+        flat = input.reshape(-1, input.shape[-1])
+        if not flat.is_contiguous():
+            flat = flat.contiguous()
+        packed = weight.packed_weights()
+        io16 = flat.dtype == torch.bfloat16 and packed.precision == native.PREC_BF16
+        full, handle = outputs.get(flat.shape[0], world * n_local, torch.bfloat16 if io16 else torch.float32, flat.device)
+        peers = [int(handle.buffer_ptrs[r]) for r in range(world) if r != rank]
+        handle.barrier()  # every rank is done reading the previous contents of its output
+        native.dsd_matmul(flat, weight._plan(True), packed, n_local, True, bias=bias, out=full,
+                          out_col0=rank * n_local, peer_outs=peers)
+        handle.barrier()  # every rank's columns have arrived everywhere
+        ctx.save_for_backward(input, weight_data)
+        ctx.weight, ctx.packed, ctx.has_bias = weight, packed, bias is not None
+        ctx.cols = (rank * n_local, (rank + 1) * n_local)
+        return full.view(*input.shape[:-1], world * n_local)
+
+    @staticmethod
+    def backward(ctx, grad):
+        input, _ = ctx.saved_tensors
+        weight = ctx.weight
+        g = grad[..., ctx.cols[0]:ctx.cols[1]].contiguous()
+        grad_input = grad_weight = grad_bias = None
+        if ctx.needs_input_grad[1]:
+            grad_weight = weight.matmul_with_output_sparse_support(g, input)
+        if ctx.needs_input_grad[0]:
+            grad_input = weight.reverse_matmul(g, transpose=False, packed=ctx.packed)
+        if ctx.has_bias and ctx.needs_input_grad[3]:
+            grad_bias = g.reshape(-1, g.shape[-1]).sum(0, dtype=torch.float32)
+        return grad_input, grad_weight, None, grad_bias, None, None
+
+
 class ColumnParallelBlockSparseLinear(nn.Module):
     """One large block-sparse Linear split by output features over the ranks of ``group``.
 
     Built on every rank from the same full ``weight`` (and ``bias``); keeps only its shard.
-    ``forward(x)`` takes the replicated input and returns the full output on every rank."""
+    ``forward(x)`` takes the replicated input and returns the full output on every rank.
+    ``fused_gather=True``: the forward kernel stores its columns straight into every rank's full-width output
+    (symmetric memory, NVLink peer stores from the epilogue) instead of a separate NCCL all-gather; the returned
+    tensor is then a buffer that the next forward of the same shape overwrites."""
 
-    def __init__(self, weight, bias=None, group=None):
+    def __init__(self, weight, bias=None, group=None, fused_gather=False):
         super().__init__()
         self.group = group
+        self.fused_gather = fused_gather
+        self._peer_outputs = None
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         self.weight = shard_block_rows(weight, rank, world)
         n_local = self.weight.shape[0]
@@ -134,6 +199,12 @@ class ColumnParallelBlockSparseLinear(nn.Module):
 
     def forward(self, x):
         x = _SumInputGrad.apply(x, self.group)
+        if self.fused_gather and isinstance(self.weight, BlockSparseMatrix):
+            if self._peer_outputs is None:
+                self._peer_outputs = PeerOutputs(self.group)
+            return _FusedColumnParallelFunction.apply(
+                x, self.weight.get_differentiable_data(), self.weight, self.bias, self._peer_outputs, self.group
+            )
         if isinstance(self.weight, BlockSparseMatrix):
             y = self.fn(x, self.weight.get_differentiable_data(), self.weight, self.bias)
         else:

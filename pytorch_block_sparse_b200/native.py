@@ -33,6 +33,7 @@ EXPORTS = (
     "bsmm_build_plan",
     "bsmm_dsd",
     "bsmm_dsd_fused",
+    "bsmm_dsd_multi",
     "bsmm_sddmm_plan_bytes",
     "bsmm_build_sddmm_plan",
     "bsmm_sddmm_workspace_bytes",
@@ -89,6 +90,8 @@ def load():
     lib.bsmm_dsd.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, vp, u32, vp]
     lib.bsmm_dsd_fused.restype = i32
     lib.bsmm_dsd_fused.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, vp, vp, vp, u32, vp]
+    lib.bsmm_dsd_multi.restype = i32
+    lib.bsmm_dsd_multi.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, i64, i64, vp, vp, vp, vp, i32, u32, vp]
     lib.bsmm_sddmm_workspace_bytes.restype = i64
     lib.bsmm_sddmm_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
     lib.bsmm_sddmm.restype = i32
@@ -299,12 +302,16 @@ class DsdPlan:
 
 
 def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colmajor=False, residual=None,
-               activation=None, pre_activation=None):
+               activation=None, pre_activation=None, out_col0=0, peer_outs=()):
     """``a @ W.T (+bias)`` (``transpose=True``) or ``a @ W`` through ``bsmm_dsd``.  ``a``: contiguous ``[m, k]``.
 
     Forward only, tensor-core precisions: ``residual`` (``[m, n_out]``) is added with the bias,
     ``activation="gelu"`` is applied to the sum, and ``pre_activation`` (an ``[m, n_out]`` tensor to fill)
-    receives the sum before the activation -- all inside the kernel's epilogue (``bsmm_dsd_fused``)."""
+    receives the sum before the activation -- all inside the kernel's epilogue (``bsmm_dsd_fused``).
+
+    ``out`` may be wider than ``n_out`` (``[m, width]``): the call then writes the column slice starting at
+    ``out_col0``, and ``peer_outs`` (device pointers, as integers, of tensors laid out like ``out`` -- other GPUs'
+    copies reached through peer mappings) receive the same slice tile by tile (``bsmm_dsd_multi``)."""
     _need_cuda(a, "dense_a")
     lib = load()
     m, k = a.shape
@@ -320,6 +327,12 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
         raise NativeError("out must be %s for this call, got %s" % (want, out.dtype))
     if out is None:
         out = torch.empty((n_out, m) if out_colmajor else (m, n_out), dtype=want, device=a.device)
+    out_ld = 0
+    if not out_colmajor and out.dim() == 2 and out.shape[1] != n_out:
+        out_ld = out.shape[1]
+        if not out.is_contiguous() or out.shape[0] != m:
+            raise NativeError("a wider out must be a contiguous [m, width] tensor")
+    peer_array = (ctypes.c_void_p * max(1, len(peer_outs)))(*[ctypes.c_void_p(int(ptr)) for ptr in peer_outs])
     if activation not in (None, "gelu"):
         raise ValueError("unknown activation %r (None or 'gelu')" % (activation,))
     flags = prec | (0 if transpose else DSD_DGRAD) | (DSD_OUT_COLMAJOR if out_colmajor else 0)
@@ -339,10 +352,11 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
         raise NativeError("pre_activation must be a contiguous float32 tensor of the output's size")
     with torch.cuda.device(a.device):
         check(
-            lib.bsmm_dsd_fused(
+            lib.bsmm_dsd_multi(
                 _ptr(a), m, k, _ptr(plan.ptr), _ptr(plan.idx), plan.nnz, _ptr(packed.data), _ptr(packed.images),
-                _ptr(plan_buf), n_out, _ptr(out), _ptr(bias.detach() if bias is not None else None), _ptr(residual),
-                _ptr(pre_activation), flags, _stream(a.device),
+                _ptr(plan_buf), n_out, _ptr(out), out_ld, out_col0, _ptr(bias.detach() if bias is not None else None),
+                _ptr(residual), _ptr(pre_activation), peer_array if peer_outs else None, len(peer_outs), flags,
+                _stream(a.device),
             ),
             "bsmm_dsd",
         )

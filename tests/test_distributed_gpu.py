@@ -64,6 +64,29 @@ def _worker(rank, world, port, results):
         full_dense = full.to_dense(data_replace=dw_ref)[rank * per:(rank + 1) * per]
         ok_dw = rel(shard_dense, full_dense) < 2e-6
 
+        # the same layer with the all-gather fused into the forward kernel: every rank's epilogue stores its columns
+        # into every rank's full-width output over NVLink peer mappings (symmetric memory), no NCCL all-gather
+        fused = bsd.ColumnParallelBlockSparseLinear(full, bias, fused_gather=True)
+        xf = x.clone().requires_grad_(True)
+        yf = fused(xf)
+        ok_fused = rel(yf, y_ref) < 2e-6 and tuple(yf.shape) == (300, 512)
+        yf.backward(g)
+        torch.cuda.synchronize()
+        ok_fused = ok_fused and rel(xf.grad, dx_ref) < 2e-6
+        ok_fused = ok_fused and rel(fused.weight.to_dense(data_replace=fused.weight.data.grad), full_dense) < 2e-6
+        # rows of 64 blocks (two promotions per row: the tile leaves for the peers after its sum is complete), twice
+        # in a row through the same symmetric buffer
+        np.random.seed(13)
+        torch.manual_seed(13)
+        long_rows = BlockSparseMatrix.zeros((256, 2048), n_blocks=8 * 64, device=dev)
+        with torch.no_grad():
+            long_rows.data.copy_((torch.randn(long_rows.data.shape) * 0.02).to(dev))
+        fused2 = bsd.ColumnParallelBlockSparseLinear(long_rows, None, fused_gather=True)
+        for seed in (21, 22):
+            x2 = torch.randn(150, 2048, generator=torch.Generator().manual_seed(seed)).to(dev)
+            want = long_rows.reverse_matmul(x2, transpose=True)
+            ok_fused = ok_fused and rel(fused2(x2), want) < 4e-6
+
         # token data parallelism: same layer everywhere, own tokens, gradients summed over the ranks
         np.random.seed(12)
         torch.manual_seed(12)
@@ -77,7 +100,7 @@ def _worker(rank, world, port, results):
         gathered = [torch.empty_like(local) for _ in range(world)]
         dist.all_gather(gathered, local)
         ok_ar = rel(lin.weight.data.grad, sum(gathered)) < 1e-6
-        results[rank] = (ok_fwd, ok_dx, ok_dw, ok_ar, native.device_status() == 0)
+        results[rank] = (ok_fwd, ok_dx, ok_dw, ok_ar, ok_fused, native.device_status() == 0)
     finally:
         dist.destroy_process_group()
 
@@ -90,4 +113,4 @@ def test_two_gpus_column_parallel_and_token_dp():
         results = mgr.dict()
         mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
         for rank in range(world):
-            assert results[rank] == (True, True, True, True, True), (rank, results[rank])
+            assert results[rank] == (True, True, True, True, True, True), (rank, results[rank])

@@ -38,7 +38,7 @@ class DenseTwin(torch.nn.Module):
 @pytest.mark.parametrize("precision", ["fp32", "tf32x3"])
 @pytest.mark.parametrize("bias", [True, False])
 def test_training_steps_match_dense_masked_twin(precision, bias):
-    # reference tests/test_linear_nn.py:58-134: output, dX and dW agree step after step under Adam
+    # reference tests/test_linear_nn.py:58-134: output, dX and dW agree step after step under Adam, 40 steps
     native.set_default_precision(precision)
     try:
         np.random.seed(0)
@@ -52,7 +52,7 @@ def test_training_steps_match_dense_masked_twin(precision, bias):
         twin = DenseTwin(lin).cuda()
         opt_a = torch.optim.Adam(lin.parameters(), lr=1e-3)
         opt_b = torch.optim.Adam(twin.parameters(), lr=1e-3)
-        for step in range(10):
+        for step in range(40):
             x = torch.randn(8, 50, 256, device="cuda", requires_grad=True)
             x2 = x.detach().clone().requires_grad_(True)
             y, y2 = lin(x), twin(x2)
@@ -380,4 +380,32 @@ def test_fused_epilogue_matches_the_unfused_layer(activation, with_residual, den
     with torch.no_grad():
         y_eval = fused(x, residual=res)
     assert float((y_eval.double() - want[0].double()).norm() / want[0].double().norm()) <= 1e-5
+    assert_device_healthy()
+
+
+@pytest.mark.parametrize("precision,tol", [("tf32", 2e-3), ("bf16", 1e-2)])
+def test_fused_epilogue_in_the_other_tensor_core_precisions(precision, tol):
+    np.random.seed(33)
+    torch.manual_seed(33)
+    native.set_default_precision(precision)
+    try:
+        lin = BlockSparseLinear(1024, 256, bias=True, density=0.5, activation="gelu")
+        with torch.no_grad():
+            lin.weight.data.normal_(0, 0.03)
+            lin.bias.normal_(0, 0.5)
+        x = torch.randn(300, 1024, device="cuda")
+        res = torch.randn(300, 256, device="cuda")
+        want = torch.nn.functional.gelu(x.double() @ lin.weight.to_dense().detach().double().t() + lin.bias.detach().double() + res.double())
+        got = lin(x, residual=res)
+        assert float((got.double() - want).norm() / want.norm()) <= tol
+        if precision == "bf16":  # bf16 tensors in memory: bias + GELU in the epilogue, bf16 result
+            lin_b = BlockSparseLinear(1024, 256, bias=True, density=0.5, activation="gelu")
+            lin_b.load_state_dict(lin.state_dict())
+            with torch.no_grad():  # (with gradients the layer keeps an fp32 pre-activation and works on fp32 tensors)
+                got_b = lin_b(x.bfloat16())
+            want_b = torch.nn.functional.gelu(x.bfloat16().double() @ lin.weight.to_dense().detach().double().t() + lin.bias.detach().double())
+            assert got_b.dtype == torch.bfloat16
+            assert float((got_b.double() - want_b).norm() / want_b.norm()) <= tol
+    finally:
+        native.set_default_precision("tf32x3")
     assert_device_healthy()
