@@ -512,7 +512,7 @@ def run_c5(dev, world, rank, steps, precisions):
         # every rank's full-width output over NVLink peer mappings (symmetric memory) while it computes
         fused_state = {}
 
-        def step_fused(_):
+        def fused_step(reduce_too):
             if "buf" not in fused_state:
                 from pytorch_block_sparse_b200.distributed import PeerOutputs
 
@@ -520,20 +520,42 @@ def run_c5(dev, world, rank, steps, precisions):
                 full_y, handle = fused_state["outputs"].get(m, world * n_local, y.dtype, dev)
                 fused_state["buf"], fused_state["handle"] = full_y, handle
                 fused_state["peers"] = [int(handle.buffer_ptrs[r]) for r in range(world) if r != rank]
+            if reduce_too and "parts" not in fused_state:
+                parts, hp = fused_state["outputs"].get(m, k, torch.float32, dev, tag="dx_parts")
+                total, ht = fused_state["outputs"].get(m, k, torch.float32, dev, tag="dx_sum")
+                fused_state["parts"], fused_state["hp"], fused_state["ht"] = parts.view(world, m // world, k), hp, ht
+                fused_state["part_ptrs"] = [int(hp.buffer_ptrs[r]) for r in range(world)]
+                fused_state["sum_ptrs"] = [int(ht.buffer_ptrs[r]) for r in range(world)]
             handle = fused_state["handle"]
             packed = native.pack_weights(data, prec)
-            handle.barrier()
+            handle.barrier()  # every rank is done with the previous step's outputs, parts and sums
             native.dsd_matmul(x, plan_f, packed, n_local, True, bias=bias, out=fused_state["buf"],
                               out_col0=rank * n_local, peer_outs=fused_state["peers"])
             native.sddmm(dy, True, x, True, w.blocks, dw, precision=prec, plan=plan_w)
-            native.dsd_matmul(dy, plan_d, packed, k, False, out=dx)
-            dist.all_reduce(dx)
-            handle.barrier()
+            if reduce_too:
+                # dgrad fused with the reduce-scatter half of the all-reduce: completed tiles go to this rank's slot on
+                # the rank owning their tokens; each rank then adds its slots and stores the sums to every rank
+                native.dsd_scatter(dy, plan_d, packed, k, False, fused_state["part_ptrs"], rank, scratch=dx)
+                handle.barrier()  # every rank's columns and parts have arrived
+                native.sum_row_slots(fused_state["parts"], fused_state["sum_ptrs"], rank * (m // world))
+                handle.barrier()  # every rank's rows of the summed gradient have arrived
+            else:
+                native.dsd_matmul(dy, plan_d, packed, k, False, out=dx)
+                dist.all_reduce(dx)
+                handle.barrier()
+
+        def step_fused(_):
+            fused_step(False)
+
+        def step_fused_both(_):
+            fused_step(True)
 
         res = {}
         legs_c5 = [("compute_ms", step, False), ("with_collectives_ms", step, True)]
         if world > 1:
             legs_c5.append(("with_fused_gather_ms", step_fused, True))
+            if prec_name != "bf16" and m % (128 * world) == 0:
+                legs_c5.append(("with_fused_gather_and_reduce_scatter_ms", step_fused_both, True))
         for name, fn, coll in legs_c5:
             if coll and world == 1:
                 res[name] = res["compute_ms"]
@@ -543,7 +565,7 @@ def run_c5(dev, world, rank, steps, precisions):
             try:
                 ms = time_op(lambda: fn(coll), max(2, min(steps, 5)), warm=2)
             except Exception as exc:  # symmetric memory may be unavailable on a box without peer access
-                if fn is step_fused:
+                if fn is step_fused or fn is step_fused_both:
                     res[name] = None
                     res["fused_gather_unavailable"] = str(exc)[:200]
                     continue
@@ -560,6 +582,8 @@ def run_c5(dev, world, rank, steps, precisions):
         res["effective_tflops"] = f_total / (res["with_collectives_ms"] / 1e3) / 1e12
         if res.get("with_fused_gather_ms"):
             res["effective_tflops_fused_gather"] = f_total / (res["with_fused_gather_ms"] / 1e3) / 1e12
+        if res.get("with_fused_gather_and_reduce_scatter_ms"):
+            res["effective_tflops_fused_both"] = f_total / (res["with_fused_gather_and_reduce_scatter_ms"] / 1e3) / 1e12
         res["effective_tflops_compute_only"] = f_total / (res["compute_ms"] / 1e3) / 1e12
         out[prec_name] = res
     return out

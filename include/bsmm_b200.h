@@ -156,12 +156,39 @@ int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
  *   peer_outs      HOST array of n_peer_outs (<= 8) device-visible pointers to tensors laid out like `out`
  *   bias, residual, pre_activation stay [n] / [m, n] tensors of this rank's slice
  * A tile leaves for the peers only when its row is complete (rows of more than 48 blocks gather their parts in
- * the local output first).  Tensor-core precisions, forward, row-major output only.
+ * the local output first).  Tensor-core precisions, row-major output only.
  */
 int bsmm_dsd_multi(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
                    const float* data, const void* packed, const void* plan, int64_t n, void* out, int64_t out_ld,
                    int64_t out_col0, const float* bias, const float* residual, float* pre_activation,
                    void* const* peer_outs, int n_peer_outs, uint32_t flags, bsmm_stream_t stream);
+
+/*
+ * A product fused with a reduce-scatter over rows -- the input gradient of the same sharded layer, where every
+ * rank computes a partial sum of the whole [m, n] result and rank i is to own rows i * m / n_parts ... of the sum.
+ *   parts     HOST array of n_parts (<= 8) device-visible pointers, one per rank in rank order, this rank's own
+ *             included: rank i's tensor of parts, fp32 [n_parts][m / n_parts][n] (slot s = what rank s computed for
+ *             the rows rank i owns), the other ranks' reached through NVLink peer mappings
+ *   slot      this rank's index: every completed tile is stored (plain TMA store) into slot `slot` of the parts
+ *             tensor of the rank that owns the tile's rows
+ *   scratch   fp32 [m, n], local: rows of more than 48 blocks gather their partial sums here before the total
+ *             leaves; contents unspecified afterwards
+ * After a barrier across the ranks, bsmm_sum_row_slots adds a rank's slots.  m must be a multiple of
+ * 128 * n_parts; tensor-core precisions, fp32 tensors; flags as for bsmm_dsd (BSMM_DSD_DGRAD or forward, no
+ * bias).  Nothing is added concurrently anywhere: the result does not depend on arrival order.
+ */
+int bsmm_dsd_scatter(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+                     const float* data, const void* packed, const void* plan, int64_t n, float* scratch,
+                     void* const* parts, int n_parts, int slot, uint32_t flags, bsmm_stream_t stream);
+
+/*
+ * outs[j][(out_row0 + r) * cols + c] = sum over s < slots (in slot order) of parts[(s * rows + r) * cols + c]
+ * for every j < n_outs: the second half of the all-reduce that bsmm_dsd_scatter starts -- the slots of the rows
+ * this rank owns are added and the sums stored into every rank's full tensor (outs: HOST array of <= 8
+ * device-visible pointers to fp32 [*, cols] tensors, peers' through NVLink mappings).  cols a multiple of 4.
+ */
+int bsmm_sum_row_slots(const float* parts, int slots, int64_t rows, int64_t cols, float* const* outs, int n_outs,
+                       int64_t out_row0, bsmm_stream_t stream);
 
 /*
  * Dense^T x dense -> block-sparse (SDDMM).  Replaces blocksparse_matmul_back_cutlass

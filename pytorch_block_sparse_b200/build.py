@@ -15,7 +15,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libbsmm_b200.so")
-SOURCES = ["bsmm_api.cu", "bsmm_simt.cu", "bsmm_pack.cu", "bsmm_plan.cu", "bsmm_pattern.cu", "bsmm_umma.cu", "bsmm_sddmm_umma.cu"]
+SOURCES = ["bsmm_api.cu", "bsmm_simt.cu", "bsmm_pack.cu", "bsmm_plan.cu", "bsmm_pattern.cu", "bsmm_collective.cu", "bsmm_umma.cu", "bsmm_sddmm_umma.cu"]
 HEADERS = ["bsmm_common.cuh", "bsmm_umma.cuh", "bsmm_ptx.cuh"]
 
 

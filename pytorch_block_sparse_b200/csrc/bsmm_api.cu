@@ -108,11 +108,50 @@ int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
                           nullptr, 0, flags, stream);
 }
 
+// bsmm_dsd_multi (scatter_slot < 0) and bsmm_dsd_scatter (peer_outs = the ranks' tensors of parts)
+static int dsd_general(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+                       const float* data, const void* packed, const void* plan, int64_t n, void* out, int64_t out_ld,
+                       int64_t out_col0, const float* bias, const float* residual, float* pre_activation,
+                       void* const* peer_outs, int n_peer_outs, int scatter_slot, uint32_t flags, bsmm_stream_t stream);
+
 int bsmm_dsd_multi(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
                    const float* data, const void* packed, const void* plan, int64_t n, void* out, int64_t out_ld,
                    int64_t out_col0, const float* bias, const float* residual, float* pre_activation,
                    void* const* peer_outs, int n_peer_outs, uint32_t flags, bsmm_stream_t stream) {
+    return dsd_general(a, m, k, ptr, idx, nnz, data, packed, plan, n, out, out_ld, out_col0, bias, residual,
+                       pre_activation, peer_outs, n_peer_outs, -1, flags, stream);
+}
+
+int bsmm_dsd_scatter(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+                     const float* data, const void* packed, const void* plan, int64_t n, float* scratch,
+                     void* const* parts, int n_parts, int slot, uint32_t flags, bsmm_stream_t stream) {
+    if (n_parts < 1 || n_parts > 8 || slot < 0 || slot >= n_parts || parts == nullptr) return BSMM_ERR_INVALID_ARGUMENT;
+    if (m <= 0 || (m % (128 * (int64_t)n_parts)) != 0 || nnz == 0 || k == 0) return BSMM_ERR_UNSUPPORTED;
+    const uint32_t precision = flags & BSMM_PREC_MASK;
+    if ((flags & (BSMM_DSD_OUT_COLMAJOR | BSMM_DSD_GELU | BSMM_DSD_IO_BF16)) != 0 || precision == BSMM_PREC_FP32_SIMT)
+        return BSMM_ERR_UNSUPPORTED;
+    return dsd_general(a, m, k, ptr, idx, nnz, data, packed, plan, n, scratch, 0, 0, nullptr, nullptr, nullptr, parts,
+                       n_parts, slot, flags, stream);
+}
+
+int bsmm_sum_row_slots(const float* parts, int slots, int64_t rows, int64_t cols, float* const* outs, int n_outs,
+                       int64_t out_row0, bsmm_stream_t stream) {
     forget_earlier_errors();
+    if (parts == nullptr || outs == nullptr || slots < 1 || n_outs < 1 || n_outs > 8 || rows < 0 || cols < 0 ||
+        (cols % 4) != 0 || out_row0 < 0 || !aligned(parts, 16))
+        return BSMM_ERR_INVALID_ARGUMENT;
+    for (int j = 0; j < n_outs; ++j)
+        if (outs[j] == nullptr || !aligned(outs[j], 16)) return BSMM_ERR_INVALID_ARGUMENT;
+    return cuda_status(bsmm::launch_sum_row_slots(parts, slots, rows, cols, outs, n_outs, out_row0,
+                                                  static_cast<cudaStream_t>(stream)));
+}
+
+static int dsd_general(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
+                       const float* data, const void* packed, const void* plan, int64_t n, void* out, int64_t out_ld,
+                       int64_t out_col0, const float* bias, const float* residual, float* pre_activation,
+                       void* const* peer_outs, int n_peer_outs, int scatter_slot, uint32_t flags, bsmm_stream_t stream) {
+    forget_earlier_errors();
+    const bool scatter = scatter_slot >= 0;
     if (n_peer_outs < 0 || n_peer_outs > 8 || (n_peer_outs > 0 && peer_outs == nullptr)) return BSMM_ERR_INVALID_ARGUMENT;
     if (out_ld < 0 || out_col0 < 0) return BSMM_ERR_INVALID_ARGUMENT;
     const bool placed = n_peer_outs > 0 || (out_ld != 0 && out_ld != n) || out_col0 != 0;
@@ -129,7 +168,7 @@ int bsmm_dsd_multi(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
     if (!aligned(a, 16) || !aligned(out, 16) || !aligned(data, 16) || !aligned(idx, 8) || !aligned(residual, 16) ||
         !aligned(pre_activation, 16))
         return BSMM_ERR_INVALID_ARGUMENT;
-    if (dgrad && (bias != nullptr || fused)) return BSMM_ERR_UNSUPPORTED;
+    if (dgrad && (bias != nullptr || gelu || residual != nullptr || pre_activation != nullptr)) return BSMM_ERR_UNSUPPORTED;
     if (fused && colmajor) return BSMM_ERR_UNSUPPORTED;
     if (pre_activation != nullptr && !gelu) return BSMM_ERR_UNSUPPORTED;
     if (io16 && (precision != BSMM_PREC_BF16 || colmajor || residual != nullptr || pre_activation != nullptr || nnz == 0 || k == 0))
@@ -161,6 +200,8 @@ int bsmm_dsd_multi(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
         epilogue.out_ld = out_ld;
         epilogue.out_col0 = out_col0;
         epilogue.n_peer_outs = n_peer_outs;
+        epilogue.scatter_rows = scatter ? m / n_peer_outs : 0;
+        epilogue.scatter_slot = scatter ? scatter_slot : 0;
         for (int i = 0; i < n_peer_outs; ++i) {
             if (!aligned(peer_outs[i], 16)) return BSMM_ERR_INVALID_ARGUMENT;
             epilogue.peer_outs[i] = peer_outs[i];

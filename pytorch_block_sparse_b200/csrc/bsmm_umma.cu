@@ -87,8 +87,9 @@ struct Cfg {
     static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
 };
 
-// Tensor maps of further output tensors: the same tiles are stored to each of them (peer GPUs' buffers reached
-// through NVLink; plain TMA stores).
+// Further output tensors (peer GPUs' buffers reached through NVLink; plain TMA stores).  Broadcast mode: the same
+// tiles are stored to each of them.  Scatter mode: map[i] is rank i's tensor of parts, and a completed tile is
+// stored into this rank's slot of the tensor of the rank that owns the tile's rows.
 constexpr int kMaxPeerOutputs = 8;
 struct PeerMaps {
     CUtensorMap map[kMaxPeerOutputs];
@@ -106,6 +107,8 @@ struct DsdParams {
     int32_t n_peers;            // further output tensors (other GPUs' copies of the output) that receive every completed tile
     int64_t out_ld;             // row pitch of the output tensor(s) in elements (n, or the full width when this call
     int64_t out_col0;           //   writes a column slice starting at out_col0)
+    int64_t scatter_rows;       // > 0: scatter mode, rows per owner
+    int32_t scatter_slot;       //      this rank's slot in the owners' tensors of parts
     float* out;                 // (bf16 in the bf16-tensor variant, which writes only through tmap_out)
     unsigned int* status;       // device status word
     int64_t m, n;
@@ -541,10 +544,17 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             fence_proxy_async_smem();  // generic-proxy writes, read by the TMA through the async proxy
             asm volatile("bar.sync 2, 128;" ::: "memory");
             if (issuer) {
-                if (overwrite) tma_store_2d(tmap, buf, (int32_t)col0, tok0);
-                else tma_reduce_add_2d(tmap, buf, (int32_t)col0, tok0);
-                if (to_peers)  // the completed tile also goes to every other GPU's copy of the output
-                    for (int i = 0; i < p.n_peers; ++i) tma_store_2d(&peers.map[i], buf, (int32_t)col0, tok0);
+                if (to_peers && p.scatter_rows > 0) {
+                    // reduce-scatter by rows: the completed tile goes to this rank's slot on the rank that owns its rows
+                    const int32_t owner = (int32_t)(tok0 / p.scatter_rows);
+                    const int32_t y = (int32_t)(p.scatter_slot * p.scatter_rows + (tok0 - owner * p.scatter_rows));
+                    tma_store_2d(&peers.map[owner], buf, (int32_t)col0, y);
+                } else {
+                    if (overwrite) tma_store_2d(tmap, buf, (int32_t)col0, tok0);
+                    else tma_reduce_add_2d(tmap, buf, (int32_t)col0, tok0);
+                    if (to_peers)  // the completed tile also goes to every other GPU's copy of the output
+                        for (int i = 0; i < p.n_peers; ++i) tma_store_2d(&peers.map[i], buf, (int32_t)col0, tok0);
+                }
                 bulk_commit_group();
             }
             ++n_out;
@@ -800,6 +810,11 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     if (io16 && (precision != BSMM_PREC_BF16 || out_colmajor || epilogue.residual != nullptr || epilogue.pre_act != nullptr))
         return cudaErrorNotSupported;
     if (epilogue.n_peer_outs < 0 || epilogue.n_peer_outs > kMaxPeerOutputs) return cudaErrorInvalidValue;
+    if (epilogue.scatter_rows != 0 &&
+        (io16 || out_colmajor || epilogue.n_peer_outs == 0 || epilogue.scatter_rows < 0 ||
+         (epilogue.scatter_rows % kTileTokens) != 0 || epilogue.scatter_rows * epilogue.n_peer_outs != m ||
+         epilogue.scatter_slot < 0 || epilogue.scatter_slot >= epilogue.n_peer_outs))
+        return cudaErrorInvalidValue;  // every token tile lies inside one owner's rows; the parts tensors are [m, out_ld] too
     const int64_t out_ld = epilogue.out_ld > 0 ? epilogue.out_ld : n;
     if (out_colmajor && (epilogue.n_peer_outs > 0 || out_ld != n || epilogue.out_col0 != 0)) return cudaErrorNotSupported;
     if (out_ld < n + epilogue.out_col0 || epilogue.out_col0 < 0 || (out_ld % 32) != 0 || (epilogue.out_col0 % 32) != 0)
@@ -858,6 +873,8 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     p.n_peers = epilogue.n_peer_outs;
     p.out_ld = out_ld;
     p.out_col0 = epilogue.out_col0;
+    p.scatter_rows = epilogue.scatter_rows;
+    p.scatter_slot = epilogue.scatter_slot;
     p.packed = static_cast<const uint8_t*>(packed) + (dgrad ? nnz * packed_slot_bytes(precision) : 0);
     p.group_off = static_cast<const int32_t*>(plan);
     p.group_slabs = p.group_off + groups + 1;

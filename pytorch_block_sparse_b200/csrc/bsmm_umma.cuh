@@ -57,7 +57,15 @@ struct DsdEpilogue {
     int64_t out_col0 = 0;             // first column of `out` this call writes (multiple of 32)
     void* peer_outs[8] = {nullptr};   // further tensors laid out like `out` (other GPUs' copies) that receive every tile
     int n_peer_outs = 0;
+    // Scatter mode (scatter_rows > 0): peer_outs[i] is rank i's [n_peer_outs * scatter_rows, out_ld] tensor of
+    // parts, own rank included; rank i owns the rows [i * scatter_rows, (i + 1) * scatter_rows) of the result, and
+    // a completed tile is stored into slot `scatter_slot` of its owner's tensor instead of going to every peer.
+    int64_t scatter_rows = 0;
+    int scatter_slot = 0;
 };
+// out[j][(out_row0 + r) * cols + c] = sum over s < slots of parts[(s * rows + r) * cols + c]  for every j < n_outs
+cudaError_t launch_sum_row_slots(const float* parts, int slots, int64_t rows, int64_t cols, float* const* outs, int n_outs,
+                                 int64_t out_row0, cudaStream_t stream);
 cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
                             bool out_colmajor, const DsdEpilogue& epilogue, cudaStream_t stream);

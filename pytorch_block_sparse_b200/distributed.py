@@ -2,7 +2,8 @@
 
 The reference has no multi-process code (its only multi-GPU artefact is a single-process
 ``nn.DataParallel`` smoke test, ``pytorch_block_sparse/tests/test_data_parallel.py:11-17``).
-Two schemes are provided, both plain NCCL collectives around the single-GPU kernels:
+Two schemes are provided, as plain NCCL collectives around the single-GPU kernels and, for the sharded layer,
+with the collectives fused into the kernels (peer stores / peer reductions over NVLink from the epilogue):
 
 * token data parallelism -- every rank holds the same pattern and weights and its own tokens;
   after backward only the nnz-block gradient buffers ``weight.data.grad`` are summed
@@ -10,7 +11,8 @@ Two schemes are provided, both plain NCCL collectives around the single-GPU kern
   :func:`broadcast_sparse_state`.
 * column parallelism for one large layer -- the weight's block-rows are partitioned
   (:func:`shard_block_rows`); forward all-gathers the output columns, dgrad sums the partial
-  input gradients, wgrad is local (:class:`ColumnParallelBlockSparseLinear`).
+  input gradients, wgrad is local (:class:`ColumnParallelBlockSparseLinear`; ``fused_gather`` /
+  ``fused_reduce`` move the all-gather and the reduce-scatter half of the all-reduce into the kernels).
 """
 import torch
 import torch.distributed as dist
@@ -124,10 +126,10 @@ class PeerOutputs:
         self.group = group if group is not None else dist.group.WORLD
         self._buffers = {}
 
-    def get(self, rows, width, dtype, device):
+    def get(self, rows, width, dtype, device, tag="y"):
         import torch.distributed._symmetric_memory as symm_mem
 
-        key = (rows, width, dtype, str(device))
+        key = (rows, width, dtype, str(device), tag)
         if key not in self._buffers:
             buf = symm_mem.empty((rows, width), dtype=dtype, device=device)
             handle = symm_mem.rendezvous(buf, self.group)
@@ -137,10 +139,14 @@ class PeerOutputs:
 
 class _FusedColumnParallelFunction(torch.autograd.Function):
     """Forward of this rank's block-row shard with the all-gather fused into the kernel's epilogue (peer stores),
-    backward as for the plain shard on this rank's column slice of the incoming gradient."""
+    backward as for the plain shard on this rank's column slice of the incoming gradient.  With ``fused_reduce``
+    the input-gradient kernel stores every completed tile of its partial sum into its slot on the rank owning
+    those tokens (peer stores from the epilogue: a reduce-scatter without atomics), and a second kernel adds each
+    rank's slots in rank order and stores the sums into every rank's gradient tensor -- together an all-reduce of
+    the partial gradients with its first half hidden under the product."""
 
     @staticmethod
-    def forward(ctx, input, weight_data, weight, bias, outputs, group):
+    def forward(ctx, input, weight_data, weight, bias, outputs, group, fused_reduce=False):
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         n_local = weight.shape[0]
         flat = input.reshape(-1, input.shape[-1])
@@ -157,6 +163,7 @@ class _FusedColumnParallelFunction(torch.autograd.Function):
         ctx.save_for_backward(input, weight_data)
         ctx.weight, ctx.packed, ctx.has_bias = weight, packed, bias is not None
         ctx.cols = (rank * n_local, (rank + 1) * n_local)
+        ctx.outputs, ctx.group, ctx.fused_reduce = outputs, group, fused_reduce
         return full.view(*input.shape[:-1], world * n_local)
 
     @staticmethod
@@ -168,10 +175,29 @@ class _FusedColumnParallelFunction(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             grad_weight = weight.matmul_with_output_sparse_support(g, input)
         if ctx.needs_input_grad[0]:
-            grad_input = weight.reverse_matmul(g, transpose=False, packed=ctx.packed)
+            world = dist.get_world_size(ctx.group)
+            gf = g.reshape(-1, g.shape[-1])
+            m, k = gf.shape[0], weight.shape[1]
+            if ctx.fused_reduce and gf.dtype == torch.float32 and m % (128 * world) == 0 and weight.data.shape[0] > 0:
+                rank = dist.get_rank(ctx.group)
+                parts, hp = ctx.outputs.get(m, k, torch.float32, gf.device, tag="dx_parts")  # [world, m / world, k]
+                total, ht = ctx.outputs.get(m, k, torch.float32, gf.device, tag="dx_sum")
+                hp.barrier()  # every rank has summed its slots of the previous call and read its previous total
+                native.dsd_scatter(gf, weight._plan(False), ctx.packed, k, False,
+                                   [int(hp.buffer_ptrs[r]) for r in range(world)], rank)
+                hp.barrier()  # every rank's parts have arrived
+                native.sum_row_slots(parts.view(world, m // world, k), [int(ht.buffer_ptrs[r]) for r in range(world)],
+                                     rank * (m // world))
+                ht.barrier()  # every rank's rows of the sum have arrived
+                grad_input = total.clone().view(input.shape)  # the symmetric buffer is reused by the next call
+            else:
+                grad_input = weight.reverse_matmul(g, transpose=False, packed=ctx.packed)
+                if ctx.fused_reduce:
+                    grad_input = grad_input.contiguous()
+                    dist.all_reduce(grad_input, group=ctx.group)
         if ctx.has_bias and ctx.needs_input_grad[3]:
             grad_bias = g.reshape(-1, g.shape[-1]).sum(0, dtype=torch.float32)
-        return grad_input, grad_weight, None, grad_bias, None, None
+        return grad_input, grad_weight, None, grad_bias, None, None, None
 
 
 class ColumnParallelBlockSparseLinear(nn.Module):
@@ -181,12 +207,16 @@ class ColumnParallelBlockSparseLinear(nn.Module):
     ``forward(x)`` takes the replicated input and returns the full output on every rank.
     ``fused_gather=True``: the forward kernel stores its columns straight into every rank's full-width output
     (symmetric memory, NVLink peer stores from the epilogue) instead of a separate NCCL all-gather; the returned
-    tensor is then a buffer that the next forward of the same shape overwrites."""
+    tensor is then a buffer that the next forward of the same shape overwrites.
+    ``fused_reduce=True`` (with ``fused_gather``): the input-gradient kernel reduce-scatters its partial sums by
+    tokens over NVLink while it computes, and a sum-and-broadcast kernel replaces the all-reduce (token counts
+    that are not a multiple of 128 x world size use the all-reduce)."""
 
-    def __init__(self, weight, bias=None, group=None, fused_gather=False):
+    def __init__(self, weight, bias=None, group=None, fused_gather=False, fused_reduce=False):
         super().__init__()
         self.group = group
         self.fused_gather = fused_gather
+        self.fused_reduce = fused_reduce and fused_gather
         self._peer_outputs = None
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         self.weight = shard_block_rows(weight, rank, world)
@@ -198,13 +228,16 @@ class ColumnParallelBlockSparseLinear(nn.Module):
         self.fn = BlockSparseLinearFunction.apply
 
     def forward(self, x):
-        x = _SumInputGrad.apply(x, self.group)
         if self.fused_gather and isinstance(self.weight, BlockSparseMatrix):
             if self._peer_outputs is None:
                 self._peer_outputs = PeerOutputs(self.group)
+            if not self.fused_reduce:
+                x = _SumInputGrad.apply(x, self.group)
             return _FusedColumnParallelFunction.apply(
-                x, self.weight.get_differentiable_data(), self.weight, self.bias, self._peer_outputs, self.group
+                x, self.weight.get_differentiable_data(), self.weight, self.bias, self._peer_outputs, self.group,
+                self.fused_reduce,
             )
+        x = _SumInputGrad.apply(x, self.group)
         if isinstance(self.weight, BlockSparseMatrix):
             y = self.fn(x, self.weight.get_differentiable_data(), self.weight, self.bias)
         else:

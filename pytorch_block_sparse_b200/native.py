@@ -34,6 +34,8 @@ EXPORTS = (
     "bsmm_dsd",
     "bsmm_dsd_fused",
     "bsmm_dsd_multi",
+    "bsmm_dsd_scatter",
+    "bsmm_sum_row_slots",
     "bsmm_sddmm_plan_bytes",
     "bsmm_build_sddmm_plan",
     "bsmm_sddmm_workspace_bytes",
@@ -92,6 +94,10 @@ def load():
     lib.bsmm_dsd_fused.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, vp, vp, vp, u32, vp]
     lib.bsmm_dsd_multi.restype = i32
     lib.bsmm_dsd_multi.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, i64, i64, vp, vp, vp, vp, i32, u32, vp]
+    lib.bsmm_dsd_scatter.restype = i32
+    lib.bsmm_dsd_scatter.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, u32, vp]
+    lib.bsmm_sum_row_slots.restype = i32
+    lib.bsmm_sum_row_slots.argtypes = [vp, i32, i64, i64, vp, i32, i64, vp]
     lib.bsmm_sddmm_workspace_bytes.restype = i64
     lib.bsmm_sddmm_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
     lib.bsmm_sddmm.restype = i32
@@ -361,6 +367,50 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
             "bsmm_dsd",
         )
     return out
+
+
+def dsd_scatter(a, plan, packed, n_out, transpose, parts, slot, scratch=None):
+    """``a @ W.T`` or ``a @ W`` fused with a reduce-scatter over rows (``bsmm_dsd_scatter``): ``parts`` are the
+    device pointers (integers) of every rank's ``[world, m / world, n_out]`` fp32 tensor of parts in rank order, own
+    included; every completed tile is stored into slot ``slot`` (this rank's index) of the tensor of the rank
+    owning the tile's rows.  ``scratch``: an ``[m, n_out]`` fp32 tensor (allocated when missing)."""
+    _need_cuda(a, "dense_a")
+    lib = load()
+    m, k = a.shape
+    prec = packed.precision
+    if prec == PREC_FP32_SIMT:
+        raise NativeError("the fused reduce-scatter needs a tensor-core precision")
+    if a.dtype != torch.float32:
+        a = a.float()
+    if scratch is None:
+        scratch = torch.empty((m, n_out), dtype=torch.float32, device=a.device)
+    group = plan.group_for(m, prec)
+    flags = prec | (0 if transpose else DSD_DGRAD) | (group << 8)
+    part_array = (ctypes.c_void_p * len(parts))(*[ctypes.c_void_p(int(ptr)) for ptr in parts])
+    with torch.cuda.device(a.device):
+        check(
+            lib.bsmm_dsd_scatter(
+                _ptr(a), m, k, _ptr(plan.ptr), _ptr(plan.idx), plan.nnz, _ptr(packed.data), _ptr(packed.images),
+                _ptr(plan.buffer(group)), n_out, _ptr(scratch), part_array, len(parts), slot, flags, _stream(a.device),
+            ),
+            "bsmm_dsd_scatter",
+        )
+    return scratch
+
+
+def sum_row_slots(parts, outs, out_row0):
+    """``outs[j][out_row0 : out_row0 + rows] = parts.sum(0)`` for every pointer in ``outs`` (``bsmm_sum_row_slots``):
+    ``parts`` is this rank's ``[slots, rows, cols]`` fp32 tensor, ``outs`` device pointers (integers) of ``[*, cols]``
+    fp32 tensors -- every rank's full tensor, the peers' through NVLink mappings."""
+    _need_cuda(parts, "parts")
+    lib = load()
+    slots, rows, cols = parts.shape
+    out_array = (ctypes.c_void_p * len(outs))(*[ctypes.c_void_p(int(ptr)) for ptr in outs])
+    with torch.cuda.device(parts.device):
+        check(
+            lib.bsmm_sum_row_slots(_ptr(parts), slots, rows, cols, out_array, len(outs), out_row0, _stream(parts.device)),
+            "bsmm_sum_row_slots",
+        )
 
 
 class SddmmPlan:

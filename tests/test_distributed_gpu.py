@@ -1,6 +1,7 @@
 """Two-GPU NCCL test of the multi-GPU layers with the real kernels: the column-parallel layer (block-rows
 split over the ranks) must reproduce the unsharded layer's output, input gradient and its shard of the
-weight gradient; token data parallelism must all-reduce the nnz-block gradients to the sum over ranks.
+weight gradient, also with the all-gather and the reduce-scatter fused into the kernels (NVLink peer stores and
+reductions); token data parallelism must all-reduce the nnz-block gradients to the sum over ranks.
 One process per GPU, rendezvous on 127.0.0.1.  Skipped with fewer than two GPUs."""
 import os
 import socket
@@ -87,6 +88,38 @@ def _worker(rank, world, port, results):
             want = long_rows.reverse_matmul(x2, transpose=True)
             ok_fused = ok_fused and rel(fused2(x2), want) < 4e-6
 
+        # the input gradient fused with a reduce-scatter over tokens (peer reductions from the dgrad epilogue) and
+        # completed by an all-gather, instead of an all-reduce of the partial gradients; 512 tokens = 2 x 256
+        ok_reduce = True
+        x3 = torch.randn(512, 384, generator=torch.Generator().manual_seed(31)).to(dev)
+        g3 = torch.randn(512, 512, generator=torch.Generator().manual_seed(32)).to(dev)
+        both = bsd.ColumnParallelBlockSparseLinear(full, bias, fused_gather=True, fused_reduce=True)
+        for _ in range(2):  # twice through the same symmetric shard buffer
+            xb = x3.clone().requires_grad_(True)
+            yb = both(xb)
+            ok_reduce = ok_reduce and rel(yb, full.reverse_matmul(x3, transpose=True, bias=bias)) < 2e-6
+            yb.backward(g3)
+            torch.cuda.synchronize()
+            ok_reduce = ok_reduce and rel(xb.grad, full.reverse_matmul(g3, transpose=False)) < 2e-6
+        # columns with 64 blocks per shard: the partial sum of a row leaves tensor memory in two parts, and the
+        # completed total is what travels
+        np.random.seed(14)
+        torch.manual_seed(14)
+        tall = BlockSparseMatrix.zeros((4096, 64), n_blocks=128 * 2, device=dev)
+        with torch.no_grad():
+            tall.data.copy_((torch.randn(tall.data.shape) * 0.02).to(dev))
+        both2 = bsd.ColumnParallelBlockSparseLinear(tall, None, fused_gather=True, fused_reduce=True)
+        x4 = torch.randn(256, 64, generator=torch.Generator().manual_seed(33)).to(dev).requires_grad_(True)
+        g4 = torch.randn(256, 4096, generator=torch.Generator().manual_seed(34)).to(dev)
+        both2(x4).backward(g4)
+        torch.cuda.synchronize()
+        ok_reduce = ok_reduce and rel(x4.grad, tall.reverse_matmul(g4, transpose=False)) < 4e-6
+        # a token count the shards cannot split evenly falls back to the all-reduce
+        x5 = torch.randn(300, 384, generator=torch.Generator().manual_seed(35)).to(dev).requires_grad_(True)
+        both(x5).backward(g)
+        torch.cuda.synchronize()
+        ok_reduce = ok_reduce and rel(x5.grad, dx_ref) < 2e-6
+
         # token data parallelism: same layer everywhere, own tokens, gradients summed over the ranks
         np.random.seed(12)
         torch.manual_seed(12)
@@ -100,7 +133,7 @@ def _worker(rank, world, port, results):
         gathered = [torch.empty_like(local) for _ in range(world)]
         dist.all_gather(gathered, local)
         ok_ar = rel(lin.weight.data.grad, sum(gathered)) < 1e-6
-        results[rank] = (ok_fwd, ok_dx, ok_dw, ok_ar, ok_fused, native.device_status() == 0)
+        results[rank] = (ok_fwd, ok_dx, ok_dw, ok_ar, ok_fused, ok_reduce, native.device_status() == 0)
     finally:
         dist.destroy_process_group()
 
@@ -113,4 +146,4 @@ def test_two_gpus_column_parallel_and_token_dp():
         results = mgr.dict()
         mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
         for rank in range(world):
-            assert results[rank] == (True, True, True, True, True, True), (rank, results[rank])
+            assert results[rank] == (True, True, True, True, True, True, True), (rank, results[rank])
