@@ -19,6 +19,7 @@ import torch
 import torch.autograd
 import torch.nn as nn
 
+from . import native
 from .block_sparse import BlockSparseMatrix, BlockSparseMatrixBase, BlockSparseMatrixEmulator
 
 
@@ -58,6 +59,9 @@ class BlockSparseLinearFunction(torch.autograd.Function):
                 pre = pre + residual
             out = torch.nn.functional.gelu(pre) if activation == "gelu" else pre
         else:
+            # needs_input_grad reports the inputs' requires_grad flags even when no graph is being recorded (and
+            # the grad mode cannot be asked here: it is always off inside forward); the layer's forward therefore
+            # takes the inference path itself when gradients are disabled
             need_pre = activation is not None and any(ctx.needs_input_grad)
             out, pre = weight.reverse_matmul_fused(
                 input, bias=bias, residual=residual, activation=activation, packed=ctx.packed, keep_pre=need_pre
@@ -163,6 +167,10 @@ class BlockSparseLinear(nn.Module):
         if self._optimized:
             if residual is None and self.activation is None:
                 return self.fn(x, self.weight.get_differentiable_data(), self.weight, self.bias)
+            if (not torch.is_grad_enabled() and isinstance(self.weight, BlockSparseMatrix)
+                    and native.resolve_precision(None) != native.PREC_FP32_SIMT):
+                # inference: no pre-activation tensor is kept (and bf16 tensors stay bf16)
+                return self.weight.reverse_matmul_fused(x, bias=self.bias, residual=residual, activation=self.activation)[0]
             return self.fn(x, self.weight.get_differentiable_data(), self.weight, self.bias, residual, self.activation)
         x = self.fn(x, self.weight.get_differentiable_data(), self.weight)
         if self.bias is not None:

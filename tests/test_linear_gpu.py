@@ -409,3 +409,39 @@ def test_fused_epilogue_in_the_other_tensor_core_precisions(precision, tol):
     finally:
         native.set_default_precision("tf32x3")
     assert_device_healthy()
+
+
+def test_layer_step_replays_as_a_cuda_graph():
+    # the library allocates nothing and synchronises nowhere, and its launches go to the caller's stream: one
+    # forward + backward of the layer is capturable, and a replay on new inputs reproduces the eager result
+    np.random.seed(5)
+    torch.manual_seed(5)
+    lin = BlockSparseLinear(256, 128, bias=True, density=0.4)
+    x = torch.randn(96, 256, device="cuda", requires_grad=True)
+    g = torch.randn(96, 128, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # warm-up outside the capture: plans, symbol addresses, kernel attributes
+        for _ in range(3):
+            lin(x).backward(g)
+    torch.cuda.current_stream().wait_stream(side)
+    lin.zero_grad(set_to_none=True)
+    x.grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y = lin(x)
+        y.backward(g)
+    for seed in (1, 2):
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        with torch.no_grad():
+            x.copy_(torch.randn(96, 256, device="cuda", generator=gen))
+            g.copy_(torch.randn(96, 128, device="cuda", generator=gen))
+        graph.replay()
+        torch.cuda.synchronize()
+        got = (y.detach().clone(), x.grad.clone(), lin.weight.data.grad.clone(), lin.bias.grad.clone())
+        x2 = x.detach().clone().requires_grad_(True)
+        lin2_grads = torch.autograd.grad(lin(x2), (x2, lin.weight.data, lin.bias), g)
+        assert torch.equal(got[0], lin(x2).detach())
+        for a, b in zip(got[1:], lin2_grads):
+            assert torch.equal(a, b)
+    assert_device_healthy()
