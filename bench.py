@@ -712,8 +712,22 @@ def run_gpu_arm(args, cfg):
     case = LayerCase(cfg, dev, rank, host_buffers=True)
     lin, w = case.lin, case.w
     x, dy, y, dx, dw = case.x, case.dy, case.y, case.dx, case.dw
-    pack, fwd, dgrad, wgrad = case.ops(prec)
     side = torch.cuda.Stream(device=dev)
+    reducer, allreduce_kind = None, "none"
+    if world > 1:
+        # the nnz-block gradient is summed over the ranks by this library's own peer-memory kernel (the gradient
+        # buffer lives in symmetric memory); NCCL where symmetric memory is not available
+        allreduce_kind = "nccl"
+        if not args.nccl_allreduce:
+            try:
+                from pytorch_block_sparse_b200.distributed import PeerAllReduce
+
+                reducer = PeerAllReduce(case.dw.numel(), dev)
+                case.dw = dw = reducer.buffer[: dw.numel()].view_as(dw)
+                allreduce_kind = "bsmm_allreduce_peers over symmetric memory"
+            except Exception as exc:  # noqa: BLE001
+                allreduce_kind = "nccl (symmetric memory unavailable: %s)" % str(exc)[:120]
+    pack, fwd, dgrad, wgrad = case.ops(prec)
 
     def step():
         # the weight gradient first: its all-reduce (N > 1) then travels while dgrad computes
@@ -723,13 +737,18 @@ def run_gpu_arm(args, cfg):
         if world > 1:
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                dist.all_reduce(dw)
+                if reducer is not None:
+                    reducer()
+                else:
+                    dist.all_reduce(dw)
         dgrad()
         if world > 1:
             torch.cuda.current_stream().wait_stream(side)
 
     # kernels of this library launched per step: pack, fwd, dgrad, wgrad (+ its token-range reduction)
     launches_per_step = 5 if native.load().bsmm_sddmm_workspace_bytes(n, k, m, nnz, prec) > 0 else 4
+    if reducer is not None:
+        launches_per_step += 1  # the peer-memory all-reduce kernel (the two barriers around it are torch's)
 
     def barrier():
         if world > 1:
@@ -934,7 +953,7 @@ def run_gpu_arm(args, cfg):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": prec_name, "data": "synthetic",
-        "config": dict(workload=args.workload, nnz=nnz, parallelism="token-dp%d" % world,
+        "config": dict(workload=args.workload, nnz=nnz, parallelism="token-dp%d" % world, grad_allreduce=allreduce_kind,
                        cache=("x and dy are %d and %d MiB, larger than the 126 MB L2" % (m * k * 4 >> 20, m * n * 4 >> 20))
                        if min(m * k, m * n) * 4 > (126 << 20) else
                        ("x and dy (%d and %d MiB) fit the 126 MB L2 and are not flushed between steps"
@@ -970,6 +989,8 @@ def main():
     ap.add_argument("--precision", default="tf32x3", choices=["tf32x3", "tf32", "bf16", "fp32"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-comparators", action="store_true")
+    ap.add_argument("--nccl-allreduce", action="store_true",
+                    help="N > 1: sum the weight gradients with NCCL instead of the library's peer-memory kernel")
     ap.add_argument("--legs", default="sweep,c5,c4",
                     help="comma list of extra legs timed after the headline: sweep (1 GPU only), c5, c4; 'none' for none")
     args = ap.parse_args()

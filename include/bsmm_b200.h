@@ -191,6 +191,18 @@ int bsmm_sum_row_slots(const float* parts, int slots, int64_t rows, int64_t cols
                        int64_t out_row0, bsmm_stream_t stream);
 
 /*
+ * In-place all-reduce (sum, times `scale`) of one fp32 buffer of `elems` elements per rank through NVLink peer
+ * mappings -- the nnz-block weight gradients of token data parallelism (config 4's scheme; the reference's
+ * only multi-GPU artefact is tests/test_data_parallel.py:11-17).
+ *   bufs   HOST array of n (<= 8) device-visible pointers, the ranks' buffers in rank order, own included
+ * This rank adds slice `rank` of every buffer in rank order and stores the result into slice `rank` of every
+ * buffer (elems is cut into n slices of 16-byte granularity).  The caller synchronises the ranks before the call
+ * (every buffer complete) and after it (every slice stored).  Every rank ends with the same bits.  The grid is
+ * small on purpose: the kernel is meant to run on a side stream beside bsmm_dsd.  elems a multiple of 4.
+ */
+int bsmm_allreduce_peers(float* const* bufs, int n, int rank, int64_t elems, float scale, bsmm_stream_t stream);
+
+/*
  * Dense^T x dense -> block-sparse (SDDMM).  Replaces blocksparse_matmul_back_cutlass
  * (reference native/block_sparse_native.cpp:18-29, native/block_sparse_cutlass_kernel_back.cu:118-160):
  *   sparse_c[s*32 + c][r] = sum_t a[t, R*32+r] * b[t, C*32+c],  (C, R) = blocks[2s], blocks[2s+1]

@@ -108,6 +108,15 @@ int bsmm_dsd_fused(const void* a, int64_t m, int64_t k, const int32_t* ptr, cons
                           nullptr, 0, flags, stream);
 }
 
+int bsmm_allreduce_peers(float* const* bufs, int n, int rank, int64_t elems, float scale, bsmm_stream_t stream) {
+    forget_earlier_errors();
+    if (bufs == nullptr || n < 1 || n > 8 || rank < 0 || rank >= n || elems < 0 || (elems % 4) != 0)
+        return BSMM_ERR_INVALID_ARGUMENT;
+    for (int r = 0; r < n; ++r)
+        if (bufs[r] == nullptr || !aligned(bufs[r], 16)) return BSMM_ERR_INVALID_ARGUMENT;
+    return cuda_status(bsmm::launch_allreduce_slice(bufs, n, rank, elems, scale, static_cast<cudaStream_t>(stream)));
+}
+
 // bsmm_dsd_multi (scatter_slot < 0) and bsmm_dsd_scatter (peer_outs = the ranks' tensors of parts)
 static int dsd_general(const void* a, int64_t m, int64_t k, const int32_t* ptr, const int32_t* idx, int64_t nnz,
                        const float* data, const void* packed, const void* plan, int64_t n, void* out, int64_t out_ld,

@@ -64,6 +64,9 @@ struct DsdEpilogue {
     int scatter_slot = 0;
 };
 // out[j][(out_row0 + r) * cols + c] = sum over s < slots of parts[(s * rows + r) * cols + c]  for every j < n_outs
+// in-place sum over n ranks' buffers of `elems` floats: this rank adds slice `rank` of every buffer (rank order),
+// scales it and stores it into slice `rank` of every buffer
+cudaError_t launch_allreduce_slice(float* const* bufs, int n, int rank, int64_t elems, float scale, cudaStream_t stream);
 cudaError_t launch_sum_row_slots(const float* parts, int slots, int64_t rows, int64_t cols, float* const* outs, int n_outs,
                                  int64_t out_row0, cudaStream_t stream);
 cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,

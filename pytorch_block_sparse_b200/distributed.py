@@ -7,8 +7,8 @@ with the collectives fused into the kernels (peer stores / peer reductions over 
 
 * token data parallelism -- every rank holds the same pattern and weights and its own tokens;
   after backward only the nnz-block gradient buffers ``weight.data.grad`` are summed
-  (:func:`allreduce_sparse_grads`), and patterns are kept identical with
-  :func:`broadcast_sparse_state`.
+  (:func:`allreduce_sparse_grads` over NCCL, :class:`PeerAllReduce` with this library's own kernel), and
+  patterns are kept identical with :func:`broadcast_sparse_state`.
 * column parallelism for one large layer -- the weight's block-rows are partitioned
   (:func:`shard_block_rows`); forward all-gathers the output columns, dgrad sums the partial
   input gradients, wgrad is local (:class:`ColumnParallelBlockSparseLinear`; ``fused_gather`` /
@@ -57,6 +57,47 @@ def allreduce_sparse_grads(model, group=None, average=True):
         g.copy_(flat[off : off + g.numel()].view_as(g))
         off += g.numel()
     return flat.numel() * flat.element_size()
+
+
+class PeerAllReduce:
+    """In-place all-reduce of one flat fp32 buffer per rank with this library's own kernel over NVLink peer mappings
+    (``bsmm_allreduce_peers``) instead of NCCL: a small grid that runs beside the persistent tensor-core kernels, so
+    the weight gradients of token data parallelism can travel on a side stream while the input gradient is
+    computed.  ``buffer`` lives in symmetric memory; write the gradients into it (or views of it), call the object,
+    read the sums from it.  Every rank obtains the same bits (sums in rank order)."""
+
+    def __init__(self, numel, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.numel = (numel + 3) // 4 * 4
+        self.buffer = symm_mem.empty(self.numel, dtype=torch.float32, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self._ptrs = [int(self.handle.buffer_ptrs[r]) for r in range(self.world)]
+        if self.numel != numel:
+            self.buffer[numel:].zero_()
+
+    def __call__(self, average=False):
+        self.handle.barrier()  # every rank's buffer is complete
+        native.allreduce_peers(self._ptrs, self.rank, self.numel, 1.0 / self.world if average else 1.0, self.buffer.device)
+        self.handle.barrier()  # every rank's slice has been stored everywhere
+        return self.buffer
+
+
+def allreduce_sparse_grads_peer(model, reducer, average=True):
+    """:func:`allreduce_sparse_grads` through a :class:`PeerAllReduce` of at least the gradients' total size."""
+    grads = [m.data.grad for m in sparse_matrices(model) if m.data.grad is not None]
+    off = 0
+    for g in grads:
+        reducer.buffer[off : off + g.numel()].copy_(g.reshape(-1))
+        off += g.numel()
+    reducer(average=average)
+    off = 0
+    for g in grads:
+        g.copy_(reducer.buffer[off : off + g.numel()].view_as(g))
+        off += g.numel()
+    return off * 4
 
 
 def shard_block_rows(matrix, rank, world, cls=None):

@@ -36,6 +36,7 @@ EXPORTS = (
     "bsmm_dsd_multi",
     "bsmm_dsd_scatter",
     "bsmm_sum_row_slots",
+    "bsmm_allreduce_peers",
     "bsmm_sddmm_plan_bytes",
     "bsmm_build_sddmm_plan",
     "bsmm_sddmm_workspace_bytes",
@@ -98,6 +99,8 @@ def load():
     lib.bsmm_dsd_scatter.argtypes = [vp, i64, i64, vp, vp, i64, vp, vp, vp, i64, vp, vp, i32, i32, u32, vp]
     lib.bsmm_sum_row_slots.restype = i32
     lib.bsmm_sum_row_slots.argtypes = [vp, i32, i64, i64, vp, i32, i64, vp]
+    lib.bsmm_allreduce_peers.restype = i32
+    lib.bsmm_allreduce_peers.argtypes = [vp, i32, i32, i64, ctypes.c_float, vp]
     lib.bsmm_sddmm_workspace_bytes.restype = i64
     lib.bsmm_sddmm_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
     lib.bsmm_sddmm.restype = i32
@@ -411,6 +414,16 @@ def sum_row_slots(parts, outs, out_row0):
             lib.bsmm_sum_row_slots(_ptr(parts), slots, rows, cols, out_array, len(outs), out_row0, _stream(parts.device)),
             "bsmm_sum_row_slots",
         )
+
+
+def allreduce_peers(bufs, rank, elems, scale, device):
+    """In-place sum (times ``scale``) over the ranks' buffers ``bufs`` (device pointers as integers, rank order, own
+    included) through peer mappings (``bsmm_allreduce_peers``); the caller synchronises the ranks around it."""
+    lib = load()
+    arr = (ctypes.c_void_p * len(bufs))(*[ctypes.c_void_p(int(ptr)) for ptr in bufs])
+    with torch.cuda.device(device):
+        check(lib.bsmm_allreduce_peers(arr, len(bufs), rank, elems, ctypes.c_float(scale), _stream(device)),
+              "bsmm_allreduce_peers")
 
 
 class SddmmPlan:

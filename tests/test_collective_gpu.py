@@ -86,3 +86,18 @@ def test_scatter_rejects_token_counts_it_cannot_split():
     parts = torch.empty(2, 150, 128, device="cuda")
     with pytest.raises(native.NativeError):
         native.dsd_scatter(g, full._plan(False), packed, 128, False, [parts.data_ptr(), parts.data_ptr()], 0)
+
+
+def test_allreduce_kernel_sums_every_rank_slice():
+    # bsmm_allreduce_peers: each "rank" adds its slice of all buffers and stores it into all of them
+    world, elems = 3, 4 * 1000 + 8  # slices of unequal length
+    bufs = [torch.randn(elems, device="cuda") for _ in range(world)]
+    want = sum(b.double() for b in bufs) * 0.5
+    ptrs = [b.data_ptr() for b in bufs]
+    for rank in range(world):
+        native.allreduce_peers(ptrs, rank, elems, 0.5, bufs[0].device)
+    torch.cuda.synchronize()
+    for b in bufs:
+        assert torch.equal(b, bufs[0])
+        assert float((b.double() - want).abs().max()) < 1e-5
+    assert_device_healthy()

@@ -133,6 +133,15 @@ def _worker(rank, world, port, results):
         gathered = [torch.empty_like(local) for _ in range(world)]
         dist.all_gather(gathered, local)
         ok_ar = rel(lin.weight.data.grad, sum(gathered)) < 1e-6
+        # the same sum through this library's peer-memory all-reduce kernel (symmetric memory instead of NCCL)
+        reducer = bsd.PeerAllReduce(local.numel(), dev)
+        lin.weight.data.grad.copy_(local)
+        bsd.allreduce_sparse_grads_peer(lin, reducer, average=False)
+        torch.cuda.synchronize()
+        ok_ar = ok_ar and rel(lin.weight.data.grad, sum(gathered)) < 1e-6
+        bits = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(bits, lin.weight.data.grad)
+        ok_ar = ok_ar and all(torch.equal(b, bits[0]) for b in bits)  # every rank holds the same bits
         results[rank] = (ok_fwd, ok_dx, ok_dw, ok_ar, ok_fused, ok_reduce, native.device_status() == 0)
     finally:
         dist.destroy_process_group()
