@@ -153,6 +153,11 @@ def set_default_precision(name):
     _default_precision = name
 
 
+def default_precision():
+    """Name of the precision used when a call names none."""
+    return _default_precision
+
+
 def resolve_precision(precision):
     name = _default_precision if precision is None else precision
     if name not in PRECISIONS:
