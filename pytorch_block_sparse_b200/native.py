@@ -169,6 +169,16 @@ def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+def _aligned(t, alignment=16):
+    """``t`` itself when its storage pointer is aligned, else a copy with the same strides.  Torch allocations are
+    512-byte aligned, but views are not, nor are the parameters and buffers of ``nn.DataParallel`` replicas
+    (slices of one flat broadcast buffer: an int32 buffer after one with an odd element count sits on a 4-byte
+    boundary), while the kernels read with 8- and 16-byte accesses and TMA wants 16-byte bases."""
+    if t is None or t.data_ptr() % alignment == 0:
+        return t
+    return t.clone(memory_format=torch.preserve_format)
+
+
 def _stream(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -193,7 +203,7 @@ def pack_weights(data, precision):
     _need_cuda(data, "data")
     lib = load()
     nnz = data.shape[0] // 32
-    raw = data.detach()
+    raw = _aligned(data.detach())
     sumsq = torch.empty(nnz, dtype=torch.float32, device=data.device)
     nbytes = lib.bsmm_packed_bytes(nnz, precision)
     images = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=data.device) if nbytes > 0 else None
@@ -214,6 +224,7 @@ def block_sumsq(data):
     raw = data.detach()
     if not raw.is_contiguous():
         raw = raw.contiguous()
+    raw = _aligned(raw)
     sumsq = torch.empty(nnz, dtype=torch.float32, device=data.device)
     with torch.cuda.device(data.device):
         check(lib.bsmm_pack_weights(_ptr(raw), nnz, PREC_FP32_SIMT, None, _ptr(sumsq), _stream(data.device)),
@@ -283,8 +294,8 @@ class DsdPlan:
     def __init__(self, ptr, idx):
         _need_cuda(ptr, "ptr")
         load()
-        self.ptr = ptr
-        self.idx = idx
+        self.ptr = _aligned(ptr)
+        self.idx = _aligned(idx)
         self.n_out_blocks = ptr.shape[0] - 1
         self.nnz = idx.shape[0]
         self._buffers = {}
@@ -337,6 +348,7 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
     want = torch.bfloat16 if io16 else torch.float32
     if a.dtype != want:
         a = a.to(want)
+    a = _aligned(a)
     if out is not None and out.dtype != want:
         raise NativeError("out must be %s for this call, got %s" % (want, out.dtype))
     if out is None:
@@ -359,8 +371,9 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
         flags |= group << 8
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
+    bias = _aligned(bias.detach()) if bias is not None else None
     if residual is not None:
-        residual = residual.detach().reshape(m, n_out).to(torch.float32).contiguous()
+        residual = _aligned(residual.detach().reshape(m, n_out).to(torch.float32).contiguous())
     if pre_activation is not None and (pre_activation.dtype != torch.float32 or not pre_activation.is_contiguous()
                                        or pre_activation.numel() != m * n_out):
         raise NativeError("pre_activation must be a contiguous float32 tensor of the output's size")
@@ -368,7 +381,7 @@ def dsd_matmul(a, plan, packed, n_out, transpose, bias=None, out=None, out_colma
         check(
             lib.bsmm_dsd_multi(
                 _ptr(a), m, k, _ptr(plan.ptr), _ptr(plan.idx), plan.nnz, _ptr(packed.data), _ptr(packed.images),
-                _ptr(plan_buf), n_out, _ptr(out), out_ld, out_col0, _ptr(bias.detach() if bias is not None else None),
+                _ptr(plan_buf), n_out, _ptr(out), out_ld, out_col0, _ptr(bias),
                 _ptr(residual), _ptr(pre_activation), peer_array if peer_outs else None, len(peer_outs), flags,
                 _stream(a.device),
             ),
@@ -437,8 +450,8 @@ class SddmmPlan:
     def __init__(self, ptr, idx):
         _need_cuda(ptr, "ptr")
         lib = load()
-        self.ptr = ptr
-        self.idx = idx
+        self.ptr = ptr = _aligned(ptr)
+        self.idx = _aligned(idx)
         n_rows = ptr.shape[0] - 1
         nnz = idx.shape[0]
         self.buffer = torch.empty(lib.bsmm_sddmm_plan_bytes(n_rows, nnz), dtype=torch.uint8, device=ptr.device)
@@ -503,6 +516,7 @@ def sddmm(a, a_rowmajor, b, b_rowmajor, blocks, out, precision=None, block_sumsq
             and plan is not None and tokens >= 32)
     if not io16 and (a.dtype != torch.float32 or b.dtype != torch.float32):
         a, b = a.float(), b.float()
+    a, b, blocks = _aligned(a), _aligned(b), _aligned(blocks)
     flags = prec | (0 if a_rowmajor else SDDMM_A_COLMAJOR) | (0 if b_rowmajor else SDDMM_B_COLMAJOR)
     flags |= SDDMM_IO_BF16 if io16 else 0
     ws_bytes = lib.bsmm_sddmm_workspace_bytes(rows, cols, tokens, nnz, flags) if plan is not None else 0

@@ -554,3 +554,36 @@ def test_bf16_tensors_in_memory():
     finally:
         native.set_default_precision("tf32x3")
     assert_device_healthy()
+
+
+def _shifted(t, elems=1):
+    """A copy of ``t`` whose storage starts ``elems`` elements into a larger allocation: a misaligned view, as the
+    parameters and buffers of an nn.DataParallel replica are (slices of one flat broadcast buffer)."""
+    flat = torch.empty(t.numel() + elems, dtype=t.dtype, device=t.device)
+    view = flat[elems:].view(t.shape)
+    view.copy_(t)
+    return view
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_misaligned_tensors_are_taken(precision):
+    # index buffers, data, bias and operands on 4-byte boundaries give the results of the aligned call
+    m = make_matrix((256, 192), n_blocks=17, seed=21)
+    a, g = randn((70, 192), 5).cuda(), randn((70, 256), 6).cuda()
+    bias = randn((256,), 7).cuda()
+    want_y = m.reverse_matmul(a, transpose=True, bias=bias, precision=precision)
+    want_dx = m.reverse_matmul(g, transpose=False, precision=precision)
+    want_dw = m.matmul_with_output_sparse_support(g, a, precision=precision)
+
+    prec = native.resolve_precision(precision)
+    packed = native.pack_weights(_shifted(m.data.detach()), prec)
+    plan_f = native.DsdPlan(_shifted(m.row_start_ends_a), _shifted(m.cols_a))
+    plan_d = native.DsdPlan(_shifted(m.col_start_ends_b), _shifted(m.rows_b))
+    y = native.dsd_matmul(_shifted(a), plan_f, packed, 256, True, bias=_shifted(bias))
+    dx = native.dsd_matmul(_shifted(g), plan_d, packed, 192, False)
+    plan_w = native.SddmmPlan(_shifted(m.row_start_ends_a), _shifted(m.cols_a))
+    dw = torch.empty_like(m.data)
+    native.sddmm(_shifted(g), True, _shifted(a), True, _shifted(m.blocks), dw, precision=prec, plan=plan_w)
+    torch.cuda.synchronize()
+    assert torch.equal(y, want_y) and torch.equal(dx, want_dx) and torch.equal(dw, want_dw)
+    assert_device_healthy()
