@@ -8,7 +8,10 @@
 // one CTA per SM walks its tiles, and every ring position runs on across tiles.
 //
 //   warps 0-3   weight producers : warp w feeds MMA warp w's own ring of kWRing stages, one linear bulk
-//                                  copy (8 KiB, bf16: 2 KiB) per block of its packed weight image
+//                                  copy (8 KiB, bf16: 2 KiB) per block of its packed weight image, and beside it
+//                                  a 32-byte command: everything the MMA warp needs to know about the block
+//                                  (accumulator and operand addresses, barriers, flags), so that the plan is
+//                                  decoded off the MMA warps' critical path
 //   warp 4      activation producer : TMA tensor load of the [128 x 32] fp32 slab (128-byte swizzle)
 //   warps 5-8   MMA : tcgen05.mma kind::tf32, M = 128, A from tensor memory, B from smem; output row r
 //                     of the group belongs to warp r mod 4.
@@ -86,7 +89,8 @@ struct Cfg {
     static constexpr uint32_t kOffBar = kOffOut + 2 * kSlabBytes;
     static constexpr int kNumBars = 2 * kXStages + 2 * kWStages + kAStages + 2 * G;
     static constexpr uint32_t kOffMisc = kOffBar + kNumBars * 8;
-    static constexpr uint32_t kSmemBytes = kOffMisc + 64 + 1024;  // + slack to align the base to 1 KiB
+    static constexpr uint32_t kOffCmd = (kOffMisc + 64 + 15) / 16 * 16;   // one 32-byte command per weight stage
+    static constexpr uint32_t kSmemBytes = kOffCmd + kWStages * 32 + 1024;  // + slack to align the base to 1 KiB
     static_assert(kAStages >= 2, "tensor memory over-subscribed");
     static_assert(kSmemBytes <= 232448, "shared memory over-subscribed");
 };
@@ -246,12 +250,29 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // ~1000, while the tensor core needs only ~200 cycles for a block.  Hence: the flag bits and row numbers
     // of a chunk become warp-uniform bit masks (ballots) and the per-entry decisions are bit tests; ring
     // stages follow from entry and slab counts, so a warp visits only the entries it has work for.
+    // Command flags (word 7 of a command; words 0-6: accumulator columns, activation stage, its counter's
+    // address and target, its release barrier, the row's p_ready and p_taken barriers)
+    constexpr uint32_t kCmdAcc = 1u, kCmdWarpLast = 2u, kCmdDrain = 4u, kCmdIdleShift = 3u /* 2 bits */,
+                       kCmdNeedTaken = 32u, kCmdTakenParity = 64u, kCmdEnd = 128u;
+    auto cmd_addr = [&](int ws) { return smem_base + C::kOffCmd + 32u * ws; };
+
     if (warp < kWProducers) {
         // ------------------------------------------------------------------ weight producers
         // Every MMA warp has a ring of kWRing stages of its own, filled by a producer warp of its own in the
         // order of that warp's blocks: one producer and one consumer per ring, each seeing every phase (which a
         // phase-parity barrier needs), and a full ring stalls nobody else's loads.
-        uint32_t seq = 0;  // blocks of this warp's MMA warp loaded so far
+        // The producer also decodes the plan for its MMA warp: which accumulator columns and activation stage the
+        // block uses, whether it starts a partial sum, ends a slab or triggers a promotion, and which barriers
+        // that involves -- all of it a function of the plan's order alone -- and hands the result over as a
+        // 32-byte command in the stage (written before the arrival that opens the stage's phase, so the phase's
+        // observer sees it).  The MMA warp's loop is then: wait for the stage, read the command, wait for the
+        // activation stage, issue.  Measured on c3_d0.25: -4...-6 % in the single-pass and bf16 modes, -1 % in 3xTF32.
+        const uint32_t mw = (uint32_t)warp;
+        uint32_t seq = 0;       // blocks of this warp's MMA warp loaded so far
+        uint32_t started = 0;   // bit r: the row's columns hold a partial sum of the current segment
+        uint32_t pending = 0;   // bit r: a promotion of the row was requested; its next block must see it taken
+        uint32_t taken_ph = 0;  // bit r: parity of the next p_taken[r] phase to wait for
+        int slab_base = -1;     // number (over all tiles of this CTA) of the last slab opened before this chunk
         int4 ahead = first_chunk();
         for (int tile = blockIdx.x; tile < n_tiles && !bad; tile += tile_step) {
             const int g = tile % p.groups;
@@ -259,20 +280,61 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             for (int base = e0; base < e1 && !bad; base += 32) {
                 const int4 mine = ahead;
                 ahead = prefetch(tile, base, e1);
-                uint32_t todo = __ballot_sync(0xffffffffu, base + lane < e1 && ((uint32_t)mine.z & (kMmaWarps - 1)) == (uint32_t)warp);
+                const uint32_t valid = __ballot_sync(0xffffffffu, base + lane < e1);
+                const uint32_t firsts = __ballot_sync(0xffffffffu, (mine.w & kPlanFirst) != 0);
+                const uint32_t lasts = __ballot_sync(0xffffffffu, (mine.w & kPlanLast) != 0);
+                const uint32_t wlasts = __ballot_sync(0xffffffffu, (mine.w & kPlanWarpLast) != 0);
+                const uint32_t drains = __ballot_sync(0xffffffffu, (mine.w & kDrainFlag) != 0);
+                const uint32_t idle_b0 = __ballot_sync(0xffffffffu, (mine.w & (1 << kPlanIdleShift)) != 0);
+                const uint32_t idle_b1 = __ballot_sync(0xffffffffu, (mine.w & (2 << kPlanIdleShift)) != 0);
+                const uint32_t row_b2 = __ballot_sync(0xffffffffu, (mine.z & 4) != 0);
+                uint32_t todo = __ballot_sync(0xffffffffu, ((uint32_t)mine.z & (kMmaWarps - 1)) == mw) & valid;
                 while (todo != 0) {
                     const int i = __ffs(todo) - 1;
                     todo &= todo - 1;
                     const int slot = __shfl_sync(0xffffffffu, mine.y, i);
-                    const int ws = (int)(warp * kWRing + (seq & (kWRing - 1)));
+                    const int slab = slab_base + __popc(firsts & (0xffffffffu >> (31 - i)));
+                    const int as = slab % AS;
+                    const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
+                    const uint32_t row = mw | (((row_b2 >> i) & 1u) << 2);  // this warp's rows: mw and mw + 4
+                    const uint32_t rbit = 1u << row;
+                    const bool drain = ((drains >> i) & 1u) != 0;
+                    // the warp that issues a slab's last block also arrives for the warps that have none in it
+                    const uint32_t idle = ((lasts >> i) & 1u) * (((idle_b0 >> i) & 1u) | (((idle_b1 >> i) & 1u) << 1));
+                    uint32_t flags = ((started & rbit) ? kCmdAcc : 0u) | (((wlasts >> i) & 1u) ? kCmdWarpLast : 0u) |
+                                     (drain ? kCmdDrain : 0u) | (idle << kCmdIdleShift);
+                    if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
+                        flags |= kCmdNeedTaken | (((taken_ph >> row) & 1u) ? kCmdTakenParity : 0u);
+                        taken_ph ^= rbit;
+                        pending &= ~rbit;
+                    }
+                    started |= rbit;
+                    if (drain) { pending |= rbit; started &= ~rbit; }
+                    const uint32_t c_d = tmem + row * C::kRowCols;
+                    const uint32_t c_a = tmem + C::kAccCols + as * C::kAStageCols;
+                    const uint32_t c_cnt = a_count(as), c_target = 4u * (uint32_t)(slab / AS + 1);
+                    const uint32_t c_abar = a_empty(as), c_pbar = p_ready(row), c_taken = p_taken(row);
                     wait(w_empty(ws), ((seq / kWRing) & 1u) ^ 1u, 1);
                     ++seq;
                     const uint8_t* src = p.packed + (int64_t)slot * C::kWBytes;
                     if (elect_one() && !bad) {
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(cmd_addr(ws)), "r"(c_d), "r"(c_a),
+                                     "r"(c_cnt), "r"(c_target) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(cmd_addr(ws) + 16u), "r"(c_abar),
+                                     "r"(c_pbar), "r"(c_taken), "r"(flags) : "memory");
                         mbar_arrive_expect_tx(w_full(ws), C::kWBytes);
                         bulk_load(smem_base + C::kOffW + ws * kWStageBytes, src, C::kWBytes, w_full(ws));
                     }
                 }
+                slab_base += __popc(firsts & valid);
+            }
+        }
+        {   // the end of this warp's blocks: a command without data
+            const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
+            if (!bad) wait(w_empty(ws), ((seq / kWRing) & 1u) ^ 1u, 1);
+            if (elect_one() && !bad) {
+                asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %2};" ::"r"(cmd_addr(ws) + 16u), "r"(0u), "r"(kCmdEnd) : "memory");
+                mbar_arrive(w_full(ws));
             }
         }
         if (tracing && lane == 0 && warp == 0) {
@@ -310,100 +372,63 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         // ------------------------------------------------------------------ MMA issuers
         // The warps share the issue work by output row (row mod kMmaWarps): accumulations into one row stay
         // in one thread's program order, and while one warp is between blocks the others keep the tensor pipe
-        // fed.  Each warp visits only its own blocks; a slab's stage is released by one commit from every
-        // warp that read it plus, from the warp issuing the slab's last block, plain arrivals on behalf of the
-        // warps that had nothing in it.
+        // fed.  Each warp sees only its own blocks, as commands from its weight producer; a slab's stage is
+        // released by one commit from every warp that read it plus, from the warp issuing the slab's last block,
+        // plain arrivals on behalf of the warps that had nothing in it.
         const uint32_t mw = (uint32_t)(warp - kFirstMmaWarp);
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
         constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, false);
-        uint32_t started = 0;   // bit r: the row's columns hold a partial sum of the current segment
-        uint32_t pending = 0;   // bit r: a promotion of the row was requested and not yet seen taken
-        uint32_t taken_ph = 0;  // bit r: parity of the next p_taken[r] phase to wait for
-        int slab_base = -1;     // number (over all tiles of this CTA) of the last slab opened before this chunk
-        uint32_t seq = 0;       // this warp's blocks so far: position in its weight ring
-        int4 ahead = first_chunk();
-        for (int tile = blockIdx.x; tile < n_tiles && !bad; tile += tile_step) {
-            const int g = tile % p.groups;
-            const int e0 = __ldg(p.group_off + g), e1 = __ldg(p.group_off + g + 1);
-            for (int base = e0; base < e1 && !bad; base += 32) {
-                const int4 mine4 = ahead;
-                ahead = prefetch(tile, base, e1);
-                const uint32_t valid = __ballot_sync(0xffffffffu, base + lane < e1);
-                const uint32_t firsts = __ballot_sync(0xffffffffu, (mine4.w & kPlanFirst) != 0);
-                const uint32_t lasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanLast) != 0);
-                const uint32_t wlasts = __ballot_sync(0xffffffffu, (mine4.w & kPlanWarpLast) != 0);
-                const uint32_t drains = __ballot_sync(0xffffffffu, (mine4.w & kDrainFlag) != 0);
-                const uint32_t idle_b0 = __ballot_sync(0xffffffffu, (mine4.w & (1 << kPlanIdleShift)) != 0);
-                const uint32_t idle_b1 = __ballot_sync(0xffffffffu, (mine4.w & (2 << kPlanIdleShift)) != 0);
-                const uint32_t row_b2 = __ballot_sync(0xffffffffu, (mine4.z & 4) != 0);
-                uint32_t todo = __ballot_sync(0xffffffffu, (uint32_t)(mine4.z & (kMmaWarps - 1)) == mw) & valid;
-                while (todo != 0) {
-                    const int i = __ffs(todo) - 1;
-                    todo &= todo - 1;
-                    // everything that does not depend on the operands' arrival first: the time from a slab's
-                    // publication to this warp's commit is part of the stage's recycle time
-                    const int slab = slab_base + __popc(firsts & (0xffffffffu >> (31 - i)));
-                    const int as = slab % AS;
-                    const int ws = (int)(mw * kWRing + (seq & (kWRing - 1)));
-                    const uint32_t w_parity = (seq / kWRing) & 1u;
-                    ++seq;
-                    const uint32_t row = mw | (((row_b2 >> i) & 1u) << 2);  // this warp's rows: mw and mw + 4
-                    const uint32_t rbit = 1u << row;
-                    const bool wlast = ((wlasts >> i) & 1u) != 0, drain = ((drains >> i) & 1u) != 0;
-                    // the warp that issues a slab's last block also arrives for the warps that have none in it
-                    const uint32_t idle = ((lasts >> i) & 1u) * (((idle_b0 >> i) & 1u) | (((idle_b1 >> i) & 1u) << 1));
-                    const uint64_t b_desc =
-                        kBf16 ? smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage16Lbo, kImage16Sbo)
-                                     : smem_desc_noswizzle(smem_base + C::kOffW + ws * kWStageBytes, kImage32Lbo, kImage32Sbo);
-                    const uint32_t a_hi = tmem + C::kAccCols + as * C::kAStageCols;
-                    const uint32_t d = tmem + row * C::kRowCols;
-                    const uint32_t acc0 = (started & rbit) ? 1u : 0u;
-                    const uint32_t w_bar = w_empty(ws), a_bar = a_empty(as), p_bar = p_ready(row);
-                    if (pending & rbit) {  // the drain warps must have read the row before it is overwritten
-                        wait(p_taken(row), (taken_ph >> row) & 1u, 2);
-                        taken_ph ^= rbit;
-                        pending &= ~rbit;
-                    }
-                    // the stage counter's load travels while the weight barrier is polled
-                    const uint32_t a_cnt = a_count(as), a_target = 4u * (uint32_t)(slab / AS + 1);
-                    const uint32_t seen = smem_load_acquire(a_cnt);
-                    wait(w_full(ws), w_parity, 1);
-                    if ((int32_t)(seen - a_target) < 0) wait_count(a_cnt, a_target);
-                    // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the row) precede the MMAs
-                    tc_fence_after();
-                    const long long ti = tracing ? clock64() : 0;
-                    if (elect_one() & (bad == 0)) {
-                        if (kBf16) {
+        static_assert((kWRing & (kWRing - 1)) == 0, "ring positions are taken with a mask");
+        const uint32_t w0 = smem_base + C::kOffW + (mw * kWRing) * kWStageBytes;
+        // descriptor of the ring's first stage; a stage further is kWStageBytes / 16 more in its address field
+        const uint64_t b_desc0 = kBf16 ? smem_desc_noswizzle(w0, kImage16Lbo, kImage16Sbo)
+                                       : smem_desc_noswizzle(w0, kImage32Lbo, kImage32Sbo);
+        for (uint32_t seq = 0;; ++seq) {
+            const uint32_t pos = seq & (uint32_t)(kWRing - 1);
+            const int ws = (int)(mw * kWRing + pos);
+            wait(w_full(ws), (seq / kWRing) & 1u, 1);
+            uint32_t c_d, c_a, c_cnt, c_target, c_abar, c_pbar, c_taken, flags;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c_d), "=r"(c_a), "=r"(c_cnt), "=r"(c_target)
+                         : "r"(cmd_addr(ws)) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c_abar), "=r"(c_pbar), "=r"(c_taken), "=r"(flags)
+                         : "r"(cmd_addr(ws) + 16u) : "memory");
+            if ((flags & kCmdEnd) | bad) break;
+            const uint32_t seen = smem_load_acquire(c_cnt);
+            if (flags & kCmdNeedTaken) wait(c_taken, (flags & kCmdTakenParity) ? 1u : 0u, 2);
+            if ((int32_t)(seen - c_target) < 0) wait_count(c_cnt, c_target);
+            // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the row) precede the MMAs
+            tc_fence_after();
+            const long long ti = tracing ? clock64() : 0;
+            const uint64_t b_desc = b_desc0 + (uint64_t)(pos * (kWStageBytes >> 4));
+            const uint32_t acc0 = flags & kCmdAcc;
+            if (elect_one() & (bad == 0)) {
+                if (kBf16) {
 #pragma unroll
-                            for (int s = 0; s < 2; ++s)  // k-step of 16: 8 columns (bf16 pairs) further, two k-chunks further
-                                mma_ts_f16(d, a_hi + s * 8, b_desc + (uint64_t)(s * (kImage16StepBytes >> 4)), idesc_bf16,
-                                           s == 0 ? acc0 : 1u);
+                    for (int s = 0; s < 2; ++s)  // k-step of 16: 8 columns (bf16 pairs) further, two k-chunks further
+                        mma_ts_f16(c_d, c_a + s * 8, b_desc + (uint64_t)(s * (kImage16StepBytes >> 4)), idesc_bf16,
+                                   s == 0 ? acc0 : 1u);
+                } else {
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        // k-step s: 8 columns further in the slab's tensor-memory copy, 2 KiB further in the image
+                        const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
+                        const uint32_t acc = s == 0 ? acc0 : 1u;
+                        if (kPasses == 3) {
+                            mma_ts_tf32(c_d, c_a + s * 8, b, idesc_wide, acc);               // x_hi x [w_hi ; w_lo]
+                            mma_ts_tf32(c_d + 32, c_a + 32 + s * 8, b, idesc_narrow, 1u);    // x_lo x w_hi
                         } else {
-#pragma unroll
-                            for (int s = 0; s < 4; ++s) {
-                                // k-step s: 8 columns further in the slab's tensor-memory copy, 2 KiB further in the image
-                                const uint64_t b = b_desc + (uint64_t)(s * (kImage32StepBytes >> 4));
-                                const uint32_t acc = s == 0 ? acc0 : 1u;
-                                if (kPasses == 3) {
-                                    mma_ts_tf32(d, a_hi + s * 8, b, idesc_wide, acc);               // x_hi x [w_hi ; w_lo]
-                                    mma_ts_tf32(d + 32, a_hi + 32 + s * 8, b, idesc_narrow, 1u);    // x_lo x w_hi
-                                } else {
-                                    mma_ts_tf32(d, a_hi + s * 8, b, idesc_narrow, acc);
-                                }
-                            }
+                            mma_ts_tf32(c_d, c_a + s * 8, b, idesc_narrow, acc);
                         }
-                        mma_commit(w_bar);
-                        if (wlast) mma_commit(a_bar);
-                        if (idle != 0) mbar_arrive_n(a_bar, idle);
-                        if (drain) mma_commit(p_bar);
                     }
-                    if (tracing) tr[3] += clock64() - ti;
-                    started |= rbit;
-                    if (drain) { pending |= rbit; started &= ~rbit; }
                 }
-                slab_base += __popc(firsts & valid);
+                mma_commit(w_empty(ws));
+                if (flags & kCmdWarpLast) mma_commit(c_abar);
+                const uint32_t idle = (flags >> kCmdIdleShift) & 3u;
+                if (idle != 0) mbar_arrive_n(c_abar, idle);
+                if (flags & kCmdDrain) mma_commit(c_pbar);
             }
+            if (tracing) tr[3] += clock64() - ti;
         }
         if (tracing && lane == 0 && mw == 0) {
             p.trace[kTrMmaAFull] = tr[0];
