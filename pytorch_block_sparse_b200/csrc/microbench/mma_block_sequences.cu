@@ -9,6 +9,9 @@ using namespace bsmm::ptx;
 // MODE 2: x3 with A no-swizzle smem desc
 // MODE 3: x3 TS (A from tensor memory)
 // MODE 4: 1-pass TS
+// MODE 5: x3 TS, the four N=64 instructions first, then the four N=32 ones
+// MODE 6: x3 TS with the third product in bf16 (kind::f16, K = 16): 4 x N=64 tf32 + 2 x N=32 bf16
+// MODE 7: bf16 TS: 2 x N=32 (K = 16)
 template <int MODE>
 __global__ void __launch_bounds__(128, 1) bench(int blocks, long long* out) {
     extern __shared__ uint8_t smem_raw[];
@@ -45,6 +48,17 @@ __global__ void __launch_bounds__(128, 1) bench(int blocks, long long* out) {
                     if (MODE == 1) mma_ss_tf32(d, a, b, in, 1u);
                     if (MODE == 3) { mma_ts_tf32(d, at + s * 8, b, iw, 1u); mma_ts_tf32(d + 32, at + 32 + s * 8, b, in, 1u); }
                     if (MODE == 4) mma_ts_tf32(d, at + s * 8, b, in, 1u);
+                    if (MODE == 5 || MODE == 6) mma_ts_tf32(d, at + s * 8, b, iw, 1u);
+                }
+                if (MODE == 5) {
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) mma_ts_tf32(d + 32, at + 32 + s * 8, bd + (uint64_t)(s * 128), in, 1u);
+                }
+                if (MODE == 6 || MODE == 7) {
+                    constexpr uint32_t ih = make_idesc(1u, 128u, 32u, false, false);
+                    const uint64_t bh = smem_desc_noswizzle(w, 512, 128);
+#pragma unroll
+                    for (int s = 0; s < 2; ++s) mma_ts_f16(d + 32, at + 32 + s * 8, bh + (uint64_t)(s * 64), ih, 1u);
                 }
                 mma_commit(bar);
             }
@@ -74,5 +88,6 @@ int main() {
     long long* d; cudaMalloc(&d, 32);
     run<0>(d, "x3 SS, A sw128"); run<1>(d, "1-pass SS, A sw128"); run<2>(d, "x3 SS, A no swizzle");
     run<3>(d, "x3 TS"); run<4>(d, "1-pass TS");
+    run<5>(d, "x3 TS, wide then narrow"); run<6>(d, "x3 TS, third product bf16"); run<7>(d, "bf16 TS");
     return 0;
 }
