@@ -412,6 +412,33 @@ def run_sweep(dev, steps):
             entry["frac_of_measured_hbm"] = entry["algorithmic_gbs"] / measured_peaks()["hbm_gbs"]
         out["%s/%s" % (workload, prec_name)] = entry
         del pack, fwd, dgrad, wgrad
+    # the headline shape with 64x64 blocks at the same density (the reference sends such shapes to its dense-masked
+    # emulator; here they run on the same kernels through their 32x32 expansion)
+    cases.clear()
+    torch.cuda.empty_cache()
+    import numpy as np
+
+    from pytorch_block_sparse_b200 import BlockSparseMatrix
+
+    c = WORKLOADS["c3_d0.25"]
+    np.random.seed(64)
+    torch.manual_seed(64)
+    w64 = BlockSparseMatrix.zeros((c["n"], c["k"]), n_blocks=nnz_of(c) // 4, block_shape=(64, 64), device=dev)
+    with torch.no_grad():
+        w64.data.normal_(0, 0.02)
+    x64 = torch.randn(c["m"], c["k"], device=dev)
+    dy64 = torch.randn(c["m"], c["n"], device=dev)
+
+    def step64():
+        packed = w64.packed_weights()
+        w64.reverse_matmul(x64, transpose=True, packed=packed)
+        w64.matmul_with_output_sparse_support(dy64, x64)
+        w64.reverse_matmul(dy64, transpose=False, packed=packed)
+
+    ms = time_op(step64, max(3, min(steps, 10)), warm=3)
+    out["c3_d0.25_blocks64/tf32x3"] = {"ms_per_step": ms, "effective_tflops": 3 * flops_per_op(c) / (ms / 1e3) / 1e12}
+    del w64, x64, dy64
+    torch.cuda.empty_cache()
     # host-side cost of one call: the smallest configuration is launch-bound, so the wall time of a long run of
     # back-to-back asynchronous calls is what the Python layer, ctypes, the tensor-map encoding and the launch cost
     import time as _time
