@@ -12,6 +12,7 @@ using namespace bsmm::ptx;
 // MODE 5: x3 TS, the four N=64 instructions first, then the four N=32 ones
 // MODE 6: x3 TS with the third product in bf16 (kind::f16, K = 16): 4 x N=64 tf32 + 2 x N=32 bf16
 // MODE 7: bf16 TS: 2 x N=32 (K = 16)
+// MODE 8: 3xTF32 TS for a PAIR of blocks of adjacent rows: 4 x (N=128 + N=64), accumulators of 128 columns
 template <int MODE>
 __global__ void __launch_bounds__(128, 1) bench(int blocks, long long* out) {
     extern __shared__ uint8_t smem_raw[];
@@ -49,6 +50,16 @@ __global__ void __launch_bounds__(128, 1) bench(int blocks, long long* out) {
                     if (MODE == 3) { mma_ts_tf32(d, at + s * 8, b, iw, 1u); mma_ts_tf32(d + 32, at + 32 + s * 8, b, in, 1u); }
                     if (MODE == 4) mma_ts_tf32(d, at + s * 8, b, in, 1u);
                     if (MODE == 5 || MODE == 6) mma_ts_tf32(d, at + s * 8, b, iw, 1u);
+                }
+                if (MODE == 8) {
+                    constexpr uint32_t i128 = make_idesc(2u, 128u, 128u, false, false);
+                    const uint32_t dp = tmem + (uint32_t)(g & 1) * 128;
+                    const uint64_t bp = smem_desc_noswizzle(base + 131072 + (uint32_t)(ws & 3) * 16384, 2048, 128);
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        mma_ts_tf32(dp, at + s * 8, bp + (uint64_t)(s * 256), i128, 1u);
+                        mma_ts_tf32(dp + 64, at + 32 + s * 8, bp + (uint64_t)(s * 256), iw, 1u);
+                    }
                 }
                 if (MODE == 5) {
 #pragma unroll
@@ -89,5 +100,6 @@ int main() {
     run<0>(d, "x3 SS, A sw128"); run<1>(d, "1-pass SS, A sw128"); run<2>(d, "x3 SS, A no swizzle");
     run<3>(d, "x3 TS"); run<4>(d, "1-pass TS");
     run<5>(d, "x3 TS, wide then narrow"); run<6>(d, "x3 TS, third product bf16"); run<7>(d, "bf16 TS");
+    run<8>(d, "x3 TS, pair of blocks");
     return 0;
 }
