@@ -20,6 +20,11 @@
  * attribute and binds the device's primary context to the calling thread (cudaFuncSetAttribute,
  * cudaSetDevice on the current device): make the first call per device before a capture begins.
  *
+ * Alignment.  Activation, output, `data`, bias and workspace pointers: 16 bytes (TMA bases and 16-byte accesses);
+ * `idx` and `blocks`: 8 bytes (read as int2 pairs); `ptr`: 4 bytes.  A misaligned pointer is refused with
+ * BSMM_ERR_INVALID_ARGUMENT, never dereferenced.  (Allocations of torch and cudaMalloc are 256-byte aligned;
+ * views and the flat buffers nn.DataParallel replicates into are not: the Python layer copies those.)
+ *
  * The weight format is the reference's (pytorch_block_sparse/block_sparse.py:10-76,
  * :125-153): `data` fp32 [nnz*32, 32], slot s holding its 32x32 block transposed
  * (data[s*32+c][r] = W[R*32+r][C*32+c]); CSR `ptr`/`idx` = row_start_ends_a/cols_a,

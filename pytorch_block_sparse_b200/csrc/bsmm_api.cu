@@ -175,7 +175,7 @@ static int dsd_general(const void* a, int64_t m, int64_t k, const int32_t* ptr, 
     if (ptr == nullptr || out == nullptr || (nnz > 0 && (idx == nullptr || data == nullptr || a == nullptr)))
         return BSMM_ERR_INVALID_ARGUMENT;
     if (!aligned(a, 16) || !aligned(out, 16) || !aligned(data, 16) || !aligned(idx, 8) || !aligned(residual, 16) ||
-        !aligned(pre_activation, 16))
+        !aligned(pre_activation, 16) || !aligned(bias, 16) || !aligned(ptr, 4))
         return BSMM_ERR_INVALID_ARGUMENT;
     if (dgrad && (bias != nullptr || gelu || residual != nullptr || pre_activation != nullptr)) return BSMM_ERR_UNSUPPORTED;
     if (fused && colmajor) return BSMM_ERR_UNSUPPORTED;
