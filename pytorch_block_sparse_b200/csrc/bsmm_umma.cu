@@ -239,6 +239,14 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int ng = nt % p.groups;
         return fetch(__ldg(p.group_off + ng) + lane, __ldg(p.group_off + ng + 1));
     };
+    // A tile without entries (G consecutive empty block-rows) has no chunk to walk, so nothing inside its chunk
+    // loop moves `ahead` on: the role does it by hand, or the next tile would be decoded from this tile's empty chunk.
+    auto skip_empty_tile = [&](int tile) {
+        const int nt = tile + tile_step;
+        if (nt >= n_tiles) return make_int4(0, 0, 0, 0);
+        const int ng = nt % p.groups;
+        return fetch(__ldg(p.group_off + ng) + lane, __ldg(p.group_off + ng + 1));
+    };
     auto first_chunk = [&]() {
         if ((int)blockIdx.x >= n_tiles) return make_int4(0, 0, 0, 0);
         const int g0 = (int)blockIdx.x % p.groups;
@@ -277,6 +285,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int tile = blockIdx.x; tile < n_tiles && !bad; tile += tile_step) {
             const int g = tile % p.groups;
             const int e0 = __ldg(p.group_off + g), e1 = __ldg(p.group_off + g + 1);
+            if (e0 == e1) ahead = skip_empty_tile(tile);
             for (int base = e0; base < e1 && !bad; base += 32) {
                 const int4 mine = ahead;
                 ahead = prefetch(tile, base, e1);
@@ -350,6 +359,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             const int g = tile % p.groups;
             const int32_t tok0 = (tile / p.groups) * kTileTokens;
             const int e0 = __ldg(p.group_off + g), e1 = __ldg(p.group_off + g + 1);
+            if (e0 == e1) ahead = skip_empty_tile(tile);
             for (int base = e0; base < e1 && !bad; base += 32) {
                 const int4 mine = ahead;
                 ahead = prefetch(tile, base, e1);
@@ -677,6 +687,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             };
 
             uint32_t seen = 0;      // bit r: the row has been written once in this tile
+            if (e0 == e1) ahead = skip_empty_tile(tile);
             for (int base = e0; base < e1 && ok; base += 32) {
                 const int4 mine = ahead;
                 ahead = prefetch(tile, base, e1);

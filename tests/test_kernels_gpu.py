@@ -587,3 +587,28 @@ def test_misaligned_tensors_are_taken(precision):
     torch.cuda.synchronize()
     assert torch.equal(y, want_y) and torch.equal(dx, want_dx) and torch.equal(dw, want_dw)
     assert_device_healthy()
+
+
+@pytest.mark.parametrize("group", ["4", "5", "6", "8"])
+def test_dsd_groups_of_empty_rows_between_tiles(group, monkeypatch):
+    # Whole groups of output block-rows without a block, in a launch where every CTA walks several tiles: a tile
+    # without entries has no chunk of the plan to read, and the tile after it must still be decoded from its own.
+    monkeypatch.setenv("BSMM_PLAN_GROUP", group)
+    rows = [2, 11, 12, 12, 13, 15, 15, 17, 17, 19, 21, 21, 22, 25, 27, 30]
+    cols = [2, 5, 1, 4, 5, 0, 8, 1, 7, 1, 3, 7, 1, 3, 2, 5]
+    m = make_matrix((37 * 32, 9 * 32), blocks=list(zip(rows, cols)), seed=51)
+    x = randn((9000, 9 * 32), seed=52)
+    bias = randn((37 * 32,), seed=53)
+    for precision in ("tf32x3", "tf32"):
+        if (precision == "tf32x3" and group == "8") or (precision == "tf32" and group == "5"):
+            continue  # 8-row tiles leave 3xTF32 no tensor memory, 5-row tiles exist for 3xTF32 only
+        got = run_dsd(m, x, True, precision, bias)
+        check(got, oracle_dsd(m, x, True, bias), precision, "fwd")
+        empty = got[:, 4 * 32:8 * 32]  # block-rows 4..7 hold no block: bias exactly
+        assert torch.equal(empty, bias[4 * 32:8 * 32].cuda().expand_as(empty))
+    # the same pattern seen from the other side: dgrad of the transposed layout has the empty groups on its output
+    mt = make_matrix((9 * 32, 37 * 32), blocks=list(zip(cols, rows)), seed=54)
+    dy = randn((9000, 9 * 32), seed=55)
+    check(run_dsd(mt, dy, False, "tf32x3" if group != "8" else "tf32"), oracle_dsd(mt, dy, False),
+          "tf32x3" if group != "8" else "tf32", "dgrad")
+    assert_device_healthy()
