@@ -62,3 +62,71 @@ def test_random_cases(seed):
             assert _rel(out, torch.nn.functional.gelu(want_y + res.double())) <= 2e-5, (what, "fused epilogue")
         assert native.device_status(clear=True) == 0, what
     assert_device_healthy()
+
+
+def test_random_layers_forward_and_backward():
+    """The layer through autograd on random configurations -- block size, density, bias, fused activation and
+    residual, leading dimensions, non-contiguous inputs -- against a float64 dense computation, and the weight
+    gradient for all four storage orders of its operands."""
+    from pytorch_block_sparse_b200 import BlockSparseLinear
+
+    rng = random.Random(77)
+    for case in range(30):
+        np.random.seed(500 + case)
+        torch.manual_seed(500 + case)
+        bs = rng.choice([32, 32, 64])
+        fin, fout = bs * rng.randint(1, 1024 // bs), bs * rng.randint(1, 1024 // bs)
+        density = rng.choice([0.05, 0.1, 0.3, 0.6, 1.0])
+        if int(density * fin * fout / (bs * bs)) < 1:
+            density = 1.0
+        act = rng.choice([None, "gelu"])
+        use_res, use_bias = rng.random() < 0.5, rng.random() < 0.7
+        lead = rng.choice([(7,), (3, 50), (2, 3, 41), (129,), (1000,), (4, 600)])
+        lin = BlockSparseLinear(fin, fout, bias=use_bias, density=density, block_shape=(bs, bs), activation=act)
+        with torch.no_grad():
+            lin.weight.data.mul_(0.05)
+            if use_bias:
+                lin.bias.normal_(0, 0.3)
+        x = torch.randn(*lead, fin, device="cuda")
+        if rng.random() < 0.3:
+            x = torch.randn(*lead[:-1], fin, lead[-1], device="cuda").transpose(-1, -2)
+        x = x.detach().requires_grad_(True)
+        res = torch.randn(*lead, fout, device="cuda", requires_grad=True) if use_res else None
+        g = torch.randn(*lead, fout, device="cuda")
+        y = lin(x, residual=res)
+        y.backward(g)
+
+        dense = lin.weight.to_dense().detach().double()
+        mask = lin.weight.to_dense(data_replace=torch.ones_like(lin.weight.data)).detach().double()
+        xd = x.detach().double().requires_grad_(True)
+        wd = dense.clone().requires_grad_(True)
+        pre = xd @ wd.t()
+        bd = rd = None
+        if use_bias:
+            bd = lin.bias.detach().double().requires_grad_(True)
+            pre = pre + bd
+        if use_res:
+            rd = res.detach().double().requires_grad_(True)
+            pre = pre + rd
+        want = torch.nn.functional.gelu(pre) if act == "gelu" else pre
+        want.backward(g.double())
+        what = (case, lead, fin, fout, density, bs, act, use_res, use_bias)
+        pairs = [(y, want.detach()), (x.grad, xd.grad),
+                 (lin.weight.to_dense(data_replace=lin.weight.data.grad), wd.grad * mask)]
+        if use_bias:
+            pairs.append((lin.bias.grad, bd.grad))
+        if use_res:
+            pairs.append((res.grad, rd.grad))
+        for got, ref in pairs:
+            assert _rel(got, ref) <= 2e-5, what
+
+        tokens = int(np.prod(lead))
+        a, b = g.reshape(tokens, fout), x.detach().reshape(tokens, fin)
+        ref_dw = lin.weight.matmul_with_output_sparse_support(a.contiguous(), b.contiguous())
+        for a_fm in (False, True):
+            for b_fm in (False, True):
+                aa = a.t().contiguous().t() if a_fm else a.contiguous()
+                bb = b.t().contiguous().t() if b_fm else b.contiguous()
+                assert _rel(lin.weight.matmul_with_output_sparse_support(aa, bb), ref_dw.double()) <= 1e-5, (what, a_fm, b_fm)
+        assert native.device_status(clear=True) == 0, what
+    assert_device_healthy()
