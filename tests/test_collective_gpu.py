@@ -27,16 +27,18 @@ def _matrix(shape, n_blocks, seed):
     return w
 
 
+@pytest.mark.parametrize("rows,n_blocks,tokens", [(512, 70, 300), (2368, 12, 9000)])
 @pytest.mark.parametrize("precision", ["tf32x3", "tf32", "bf16"])
-def test_forward_writes_its_column_slice_to_every_output(precision):
+def test_forward_writes_its_column_slice_to_every_output(precision, rows, n_blocks, tokens):
     # bsmm_dsd_multi: each "rank" writes the columns of its block-row shard into both full-width outputs
-    world, tokens = 2, 300
-    full = _matrix((512, 384), 70, 3)
-    bias = torch.randn(512, device="cuda") * 0.02
+    # (second case: a dozen blocks in 74 block-rows -- whole tiles without a block still deliver their bias tiles)
+    world = 2
+    full = _matrix((rows, 384), n_blocks, 3)
+    bias = torch.randn(rows, device="cuda") * 0.02
     x = torch.randn(tokens, 384, device="cuda")
     prec = native.resolve_precision(precision)
     want = full.reverse_matmul(x, transpose=True, bias=bias, precision=precision)
-    outs = [torch.full((tokens, 512), float("nan"), device="cuda") for _ in range(world)]
+    outs = [torch.full((tokens, rows), float("nan"), device="cuda") for _ in range(world)]
     for rank in range(world):
         shard = shard_block_rows(full, rank, world)
         n_local = shard.shape[0]
@@ -50,7 +52,7 @@ def test_forward_writes_its_column_slice_to_every_output(precision):
     assert_device_healthy()
 
 
-@pytest.mark.parametrize("shape,n_blocks,tokens", [((512, 384), 70, 512), ((4096, 64), 256, 256)])
+@pytest.mark.parametrize("shape,n_blocks,tokens", [((512, 384), 70, 512), ((4096, 64), 256, 256), ((320, 2368), 12, 9216)])
 def test_input_gradient_reduce_scatter_and_sum(shape, n_blocks, tokens):
     # bsmm_dsd_scatter + bsmm_sum_row_slots: every rank's partial tiles land in its slot on the owner of the tokens;
     # adding the slots gives the unsharded input gradient.  The second shape has 64 blocks per shard and column:
