@@ -49,9 +49,10 @@ WORKLOADS = {
 }
 C5 = dict(m=65536, n=32768, k=8192, density=0.1)
 # what the sweep leg times beside the headline (workload, precision)
-# ("bf16io" = 'bf16' precision on bf16 activation / output tensors: half the activation bytes in HBM)
-SWEEP = [("c3_d0.25", "tf32"), ("c3_d0.25", "bf16"), ("c3_d0.25", "bf16io"), ("c3_d0.10", "tf32x3"), ("c3_d0.10", "bf16io"),
-         ("c3_d0.50", "tf32x3"), ("c3_d0.75", "tf32x3"), ("c2_up", "tf32x3"), ("c2_down", "tf32x3"),
+# ("bf16io" = 'bf16' precision on bf16 activation / output tensors: half the activation bytes in HBM;
+#  "bf16x3" = the other fp32-class mode: forward and dgrad split into bf16 pairs, wgrad as in 3xTF32)
+SWEEP = [("c3_d0.25", "bf16x3"), ("c3_d0.25", "tf32"), ("c3_d0.25", "bf16"), ("c3_d0.25", "bf16io"), ("c3_d0.10", "tf32x3"), ("c3_d0.10", "bf16io"),
+         ("c3_d0.50", "tf32x3"), ("c3_d0.50", "bf16x3"), ("c3_d0.75", "tf32x3"), ("c2_up", "tf32x3"), ("c2_down", "tf32x3"),
          ("c5_shard", "tf32x3"), ("c5_shard", "bf16io")]
 
 
@@ -1022,7 +1023,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3_d0.25", choices=sorted(WORKLOADS))
-    ap.add_argument("--precision", default="tf32x3", choices=["tf32x3", "tf32", "bf16", "fp32"])
+    ap.add_argument("--precision", default="tf32x3", choices=["tf32x3", "bf16x3", "tf32", "bf16", "fp32"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-comparators", action="store_true")
     ap.add_argument("--nccl-allreduce", action="store_true",

@@ -55,6 +55,9 @@ extern "C" {
 #define BSMM_PREC_TF32X3 1u    /* tcgen05 kind::tf32, 3-pass hi/lo split, fp32-class accuracy  */
 #define BSMM_PREC_BF16 2u      /* tcgen05 kind::f16: operands rounded to bf16 in the kernel, fp32 accumulate; tensors stay fp32 */
 #define BSMM_PREC_TF32 3u      /* tcgen05 kind::tf32, single pass (cuBLAS allow_tf32 accuracy class) */
+#define BSMM_PREC_BF16X3 4u    /* fp32-class accuracy (about 2e-6): bsmm_dsd splits both operands into bf16 hi + lo parts and
+                                  adds three kind::f16 products with fp32 accumulation (half the tensor-core instructions of
+                                  BSMM_PREC_TF32X3); bsmm_sddmm computes as BSMM_PREC_TF32X3; tensors stay fp32 */
 #define BSMM_PREC_MASK 0xFu
 
 /* bsmm_dsd flags */

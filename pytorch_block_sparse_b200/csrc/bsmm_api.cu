@@ -19,6 +19,12 @@ bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) &
 // them, so every entry point that launches starts from a clean error state.
 void forget_earlier_errors() { (void)cudaGetLastError(); }
 
+// The weight gradient reads no weight images: under BSMM_PREC_BF16X3 it computes as 3xTF32.
+uint32_t sddmm_precision(uint32_t flags) {
+    const uint32_t precision = flags & BSMM_PREC_MASK;
+    return precision == BSMM_PREC_BF16X3 ? BSMM_PREC_TF32X3 : precision;
+}
+
 }  // namespace
 
 extern "C" {
@@ -63,14 +69,14 @@ int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* 
         if (block_sumsq == nullptr) return BSMM_OK;
         return cuda_status(bsmm::launch_block_sumsq(data, nnz, block_sumsq, s));
     }
-    if (!bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return BSMM_ERR_UNSUPPORTED;
+    if (!bsmm::is_umma_precision(precision)) return BSMM_ERR_UNSUPPORTED;
     if (nnz > 0 && (packed == nullptr || !aligned(packed, 256))) return BSMM_ERR_INVALID_ARGUMENT;
     return cuda_status(bsmm::launch_pack(data, nnz, precision, packed, block_sumsq, s));
 }
 
 int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz, uint32_t precision) {
     (void)nnz;
-    const bool wide_ok = (precision & BSMM_PREC_MASK) != BSMM_PREC_TF32X3;  // 3xTF32 rows take 64 columns
+    const bool wide_ok = !bsmm::is_split_precision(precision & BSMM_PREC_MASK);  // rows with correction terms take 64 columns
     if (m <= 0 || n_out_blocks <= 0) return wide_ok ? 8 : 6;
     // The widest tile re-uses each activation slab most; narrower tiles are only worth it when the
     // wide one would leave most of the 148 SMs without a CTA.  3xTF32 at 6 rows has room for only two
@@ -190,7 +196,7 @@ static int dsd_general(const void* a, int64_t m, int64_t k, const int32_t* ptr, 
         return cuda_status(bsmm::launch_dsd_simt(static_cast<const float*>(a), m, k, ptr, idx, data, n,
                                                  static_cast<float*>(out), bias, dgrad, colmajor, s));
     }
-    if (bsmm::is_tf32_precision(precision) || precision == BSMM_PREC_BF16) {
+    if (bsmm::is_umma_precision(precision)) {
         if (k == 0 || nnz == 0) {  // nothing to contract: the CUDA-core kernel writes the zeros (+bias)
             if (fused) return BSMM_ERR_UNSUPPORTED;
             return cuda_status(bsmm::launch_dsd_simt(static_cast<const float*>(a), m, k, ptr, idx, data, n,
@@ -198,7 +204,7 @@ static int dsd_general(const void* a, int64_t m, int64_t k, const int32_t* ptr, 
         }
         const int group = (int)((flags >> 8) & 0xFFu);
         if (packed == nullptr || plan == nullptr || !aligned(packed, 256) || !aligned(plan, 16) ||
-            !bsmm::plan_group_valid(group) || (group == 8 && precision == BSMM_PREC_TF32X3) ||
+            !bsmm::plan_group_valid(group) || (group == 8 && bsmm::is_split_precision(precision)) ||
             (group == 5 && precision != BSMM_PREC_TF32X3))
             return BSMM_ERR_INVALID_ARGUMENT;
         bsmm::DsdEpilogue epilogue;
@@ -242,7 +248,7 @@ int bsmm_build_sddmm_plan(const int32_t* ptr, int64_t n_block_rows, int64_t nnz,
 
 int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t flags) {
     if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0) return -1;
-    const uint32_t precision = flags & BSMM_PREC_MASK;
+    const uint32_t precision = sddmm_precision(flags);
     if (!bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return 0;
     if ((flags & (BSMM_SDDMM_A_COLMAJOR | BSMM_SDDMM_B_COLMAJOR)) != 0 && (tokens % 4) != 0) return 0;
     return bsmm::sddmm_umma_workspace_bytes(rows, cols, tokens, nnz, precision);
@@ -252,7 +258,7 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
                const int32_t* blocks, int64_t nnz, const int32_t* csr_idx, const void* plan, float* block_sumsq,
                void* workspace, uint32_t flags, bsmm_stream_t stream) {
     forget_earlier_errors();
-    const uint32_t precision = flags & BSMM_PREC_MASK;
+    const uint32_t precision = sddmm_precision(flags);
     const bool a_col = (flags & BSMM_SDDMM_A_COLMAJOR) != 0;
     const bool b_col = (flags & BSMM_SDDMM_B_COLMAJOR) != 0;
     if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0 || (rows % 32) != 0 || (cols % 32) != 0)

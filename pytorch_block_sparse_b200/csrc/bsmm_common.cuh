@@ -33,16 +33,37 @@ constexpr uint32_t kImage16Lbo = 512;
 constexpr uint32_t kImage16Sbo = 128;
 constexpr uint32_t kImage16StepBytes = 1024;   // one MMA k-step = 16 values of k = two k-chunks
 
+// bf16 hi | lo operand image of one 32 x 32 block (the bf16 pair splitting of BSMM_PREC_BF16X3): per k-chunk of 8
+// values [hi: 4 mn-groups][lo: 4 mn-groups], 1 KiB; an N = 64 instruction sees [hi rows ; lo rows], an N = 32
+// instruction the hi part.
+__host__ __device__ constexpr uint32_t image16x3_offset(uint32_t mn, uint32_t k, uint32_t lo_part) {
+    return (k >> 3) * 1024u + lo_part * 512u + (mn >> 3) * 128u + (mn & 7u) * 16u + (k & 7u) * 2u;
+}
+constexpr uint32_t kImage16x3Bytes = 4096;
+constexpr uint32_t kImage16x3Lbo = 1024;
+constexpr uint32_t kImage16x3Sbo = 128;
+constexpr uint32_t kImage16x3StepBytes = 2048;   // one MMA k-step = 16 values of k = two k-chunks
+
 // tensor-core arithmetic that reads the tf32 images
 __host__ __device__ constexpr bool is_tf32_precision(uint32_t precision) {
     return precision == BSMM_PREC_TF32X3 || precision == BSMM_PREC_TF32;
 }
 
+// any of the tensor-core precisions
+__host__ __device__ constexpr bool is_umma_precision(uint32_t precision) {
+    return is_tf32_precision(precision) || precision == BSMM_PREC_BF16 || precision == BSMM_PREC_BF16X3;
+}
+// an output row keeps main and correction terms apart: 64 tensor-memory columns instead of 32
+__host__ __device__ constexpr bool is_split_precision(uint32_t precision) {
+    return precision == BSMM_PREC_TF32X3 || precision == BSMM_PREC_BF16X3;
+}
+
 // Packed-weight buffer layout: [fwd images: nnz][dgrad images: nnz]
 __host__ __device__ constexpr int64_t packed_slot_bytes(uint32_t precision) {
-    return is_tf32_precision(precision)  ? (int64_t)kImage32Bytes
-         : precision == BSMM_PREC_BF16   ? (int64_t)kImage16Bytes
-                                         : 0;
+    return is_tf32_precision(precision)   ? (int64_t)kImage32Bytes
+         : precision == BSMM_PREC_BF16    ? (int64_t)kImage16Bytes
+         : precision == BSMM_PREC_BF16X3  ? (int64_t)kImage16x3Bytes
+                                          : 0;
 }
 
 // launchers (one per translation unit); all return a cudaError_t

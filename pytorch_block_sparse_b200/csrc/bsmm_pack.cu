@@ -8,7 +8,8 @@
 //   dgrad (out = dy * W ): mn = c (input feature),  k = r  -> value T[mn][k]
 // The tf32 image interleaves hi = rna_tf32(w) and lo = rna_tf32(w - hi) per k-chunk, so that one
 // N = 64 MMA reads [hi ; lo] and an N = 32 MMA reads hi alone.  Both parts are exact tf32 values:
-// nothing depends on how the MMA unit would truncate fp32 bit patterns.
+// nothing depends on how the MMA unit would truncate fp32 bit patterns.  The bf16 hi | lo image
+// (image16x3_offset) does the same with hi = bf16(w), lo = bf16(w - hi).
 #include <cuda_bf16.h>
 
 #include "bsmm_common.cuh"
@@ -22,7 +23,14 @@ __device__ __forceinline__ float tf32_rna(float x) {
     return __uint_as_float(r);
 }
 
-template <bool kTf32>
+// hi or lo part of the bf16 pair splitting: hi = bf16(w), lo = bf16(w - hi)
+__device__ __forceinline__ float bf16_part(float w, uint32_t lo_part) {
+    const float h = __bfloat162float(__float2bfloat16_rn(w));
+    return lo_part ? w - h : h;   // (the caller rounds: hi is exact already)
+}
+
+// kMode: 0 = tf32 hi | lo images, 1 = bf16 images, 2 = bf16 hi | lo images
+template <int kMode>
 __global__ void __launch_bounds__(256)
 pack_kernel(const float* __restrict__ data, int64_t nnz, uint8_t* __restrict__ packed,
             float* __restrict__ block_sumsq) {
@@ -51,7 +59,7 @@ pack_kernel(const float* __restrict__ data, int64_t nnz, uint8_t* __restrict__ p
         block_sumsq[slot] = t;
     }
 
-    if (kTf32) {
+    if (kMode == 0) {
         float* fwd = reinterpret_cast<float*>(packed + slot * (int64_t)kImage32Bytes);
         float* dgr = reinterpret_cast<float*>(packed + (nnz + slot) * (int64_t)kImage32Bytes);
 #pragma unroll
@@ -67,6 +75,19 @@ pack_kernel(const float* __restrict__ data, int64_t nnz, uint8_t* __restrict__ p
             const float wd = T[mn][k];
             const float hd = tf32_rna(wd);
             dgr[w] = lo_part ? tf32_rna(wd - hd) : hd;
+        }
+    } else if (kMode == 2) {
+        __nv_bfloat162* fwd = reinterpret_cast<__nv_bfloat162*>(packed + slot * (int64_t)kImage16x3Bytes);
+        __nv_bfloat162* dgr = reinterpret_cast<__nv_bfloat162*>(packed + (nnz + slot) * (int64_t)kImage16x3Bytes);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w = tid + 256 * i;  // 32-bit word = two consecutive k of one mn, hi or lo part
+            const uint32_t byte = w * 4;
+            const uint32_t k = (byte / 1024u) * 8u + (byte % 16u) / 2u;
+            const uint32_t lo_part = (byte % 1024u) / 512u;
+            const uint32_t mn = ((byte % 512u) / 128u) * 8u + (byte % 128u) / 16u;
+            fwd[w] = __floats2bfloat162_rn(bf16_part(T[k][mn], lo_part), bf16_part(T[k + 1][mn], lo_part));
+            dgr[w] = __floats2bfloat162_rn(bf16_part(T[mn][k], lo_part), bf16_part(T[mn][k + 1], lo_part));
         }
     } else {
         __nv_bfloat162* fwd = reinterpret_cast<__nv_bfloat162*>(packed + slot * (int64_t)kImage16Bytes);
@@ -90,9 +111,11 @@ cudaError_t launch_pack(const float* data, int64_t nnz, uint32_t precision, void
     if (nnz == 0) return cudaSuccess;
     uint8_t* p = static_cast<uint8_t*>(packed);
     if (is_tf32_precision(precision))
-        pack_kernel<true><<<(unsigned)nnz, 256, 0, stream>>>(data, nnz, p, block_sumsq);
+        pack_kernel<0><<<(unsigned)nnz, 256, 0, stream>>>(data, nnz, p, block_sumsq);
     else if (precision == BSMM_PREC_BF16)
-        pack_kernel<false><<<(unsigned)nnz, 256, 0, stream>>>(data, nnz, p, block_sumsq);
+        pack_kernel<1><<<(unsigned)nnz, 256, 0, stream>>>(data, nnz, p, block_sumsq);
+    else if (precision == BSMM_PREC_BF16X3)
+        pack_kernel<2><<<(unsigned)nnz, 256, 0, stream>>>(data, nnz, p, block_sumsq);
     else
         return cudaErrorInvalidValue;
     return cudaGetLastError();

@@ -19,6 +19,8 @@
 //                       x_hi x [w_hi ; w_lo]  (N = 64) -> main | correction columns of the row
 //                       x_lo x  w_hi          (N = 32) -> correction columns
 //                     single-pass TF32: one N = 32 instruction per k-step.
+//                     bf16 hi | lo (BSMM_PREC_BF16X3): the same two instructions per k-step as 3xTF32, kind::f16
+//                     on bf16 parts hi = bf16(v), lo = bf16(v - hi), with k-steps of 16: half as many instructions
 //   warps 9-16  split : two groups of four, alternate slabs: slab smem -> registers -> tensor memory
 //                       (lane = token, column = k) with tcgen05.st, which makes it the MMA's A operand;
 //                       for 3xTF32 also lo = x - trunc_tf32(x) (the tensor core reads only the tf32
@@ -61,12 +63,15 @@ constexpr int kFirstSplitWarp = kFirstMmaWarp + kMmaWarps;
 template <int G, int kPasses>
 struct Cfg {
     // kPasses: 3 = 3xTF32, 1 = single-pass TF32, 0 = bf16 operands (kind::f16) rounded in the kernel from fp32
-    // tensors, 4 = bf16 operands with bf16 activations and outputs in memory; fp32 accumulation throughout
-    static constexpr bool kBf16 = kPasses == 0 || kPasses == 4;
+    // tensors, 4 = bf16 operands with bf16 activations and outputs in memory, 5 = three products of bf16 hi and lo
+    // parts of fp32 tensors (the 3xTF32 scheme with kind::f16 instructions: two k-steps of 16 instead of four of 8);
+    // fp32 accumulation throughout
+    static constexpr bool kBf16 = kPasses == 0 || kPasses == 4 || kPasses == 5;
     static constexpr bool kIo16 = kPasses == 4;
-    static constexpr uint32_t kRowCols = kPasses == 3 ? 64 : 32;     // main | correction
-    static constexpr uint32_t kAStageCols = kPasses == 3 ? 64 : kPasses == 1 ? 32 : 16;  // x_hi | x_lo; bf16 pairs
-    static constexpr uint32_t kWBytes = kBf16 ? kImage16Bytes : kImage32Bytes;    // one block's image
+    static constexpr bool kSplit = kPasses == 3 || kPasses == 5;       // hi and lo parts, correction columns
+    static constexpr uint32_t kRowCols = kSplit ? 64 : 32;     // main | correction
+    static constexpr uint32_t kAStageCols = kPasses == 3 ? 64 : (kPasses == 1 || kPasses == 5) ? 32 : 16;  // x_hi | x_lo; bf16 pairs
+    static constexpr uint32_t kWBytes = kPasses == 5 ? kImage16x3Bytes : kBf16 ? kImage16Bytes : kImage32Bytes;    // one block's image
     static constexpr uint32_t kAccCols = G * kRowCols;
     static constexpr int kAStagesMax = (int)((kTmemCols - kAccCols) / kAStageCols);
     static constexpr int kAStages = kAStagesMax >= 8 ? 8 : kAStagesMax >= 4 ? 4 : kAStagesMax;  // 8, 4, 3 or 2
@@ -78,10 +83,10 @@ struct Cfg {
     static constexpr int kThreads = 32 * (kFirstDrainWarp + 4);
     static_assert(kAStages % kSplitGroups == 0, "a ring stage must stay with one split-warp group");
     // Weight stages per MMA warp (a ring of its own, a power of two).  Single-pass TF32 spends the least tensor
-    // time per 8 KiB image and gains 11 % from four stages where shared memory has room for them; 3xTF32 (-1 %)
-    // and bf16 (0 %) keep two.
+    // time per 8 KiB image and gains 11 % from four stages where shared memory has room for them, the bf16 hi | lo
+    // mode 2 %; 3xTF32 (-1 %) and bf16 (0 %) keep two.
     static constexpr int kWRing =
-        (kPasses == 1 && (kXStages + 2) * kSlabBytes + 4 * kMmaWarps * kWStageBytes + 2048 <= 232448) ? 4 : 2;
+        ((kPasses == 1 || kPasses == 5) && (kXStages + 2) * kSlabBytes + 4 * kMmaWarps * kWStageBytes + 2048 <= 232448) ? 4 : 2;
     static constexpr int kWStages = kMmaWarps * kWRing;
     static constexpr uint32_t kOffX = 0;
     static constexpr uint32_t kOffW = kOffX + kXStages * kSlabBytes;
@@ -147,7 +152,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                      const __grid_constant__ CUtensorMap tmap_pre, const __grid_constant__ PeerMaps peers,
                      const DsdParams p) {
     using C = Cfg<G, kPasses>;
-    constexpr bool kBf16 = C::kBf16, kIo16 = C::kIo16;
+    constexpr bool kBf16 = C::kBf16, kIo16 = C::kIo16, kSplit = C::kSplit;
     // bf16 tensors need no promotion against accumulation drift: a row is drained once, at its end
     constexpr int32_t kDrainFlag = kIo16 ? kPlanRowEnd : kPlanDrain;
     constexpr int XS = C::kXStages;
@@ -389,11 +394,13 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, false);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, false);
         constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, false);
+        constexpr uint32_t idesc_bf16_wide = make_idesc(1u, 128u, 64u, false, false);
         static_assert((kWRing & (kWRing - 1)) == 0, "ring positions are taken with a mask");
         const uint32_t w0 = smem_base + C::kOffW + (mw * kWRing) * kWStageBytes;
         // descriptor of the ring's first stage; a stage further is kWStageBytes / 16 more in its address field
-        const uint64_t b_desc0 = kBf16 ? smem_desc_noswizzle(w0, kImage16Lbo, kImage16Sbo)
-                                       : smem_desc_noswizzle(w0, kImage32Lbo, kImage32Sbo);
+        const uint64_t b_desc0 = kPasses == 5 ? smem_desc_noswizzle(w0, kImage16x3Lbo, kImage16x3Sbo)
+                                 : kBf16      ? smem_desc_noswizzle(w0, kImage16Lbo, kImage16Sbo)
+                                              : smem_desc_noswizzle(w0, kImage32Lbo, kImage32Sbo);
         for (uint32_t seq = 0;; ++seq) {
             const uint32_t pos = seq & (uint32_t)(kWRing - 1);
             const int ws = (int)(mw * kWRing + pos);
@@ -413,7 +420,14 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             const uint64_t b_desc = b_desc0 + (uint64_t)(pos * (kWStageBytes >> 4));
             const uint32_t acc0 = flags & kCmdAcc;
             if (elect_one() & (bad == 0)) {
-                if (kBf16) {
+                if (kPasses == 5) {
+#pragma unroll
+                    for (int s = 0; s < 2; ++s) {  // k-step of 16: x_hi pairs in columns 0-15 of the stage, x_lo pairs in 16-31
+                        const uint64_t b = b_desc + (uint64_t)(s * (kImage16x3StepBytes >> 4));
+                        mma_ts_f16(c_d, c_a + s * 8, b, idesc_bf16_wide, s == 0 ? acc0 : 1u);   // x_hi x [w_hi ; w_lo]
+                        mma_ts_f16(c_d + 32, c_a + 16 + s * 8, b, idesc_bf16, 1u);              // x_lo x w_hi
+                    }
+                } else if (kBf16) {
 #pragma unroll
                     for (int s = 0; s < 2; ++s)  // k-step of 16: 8 columns (bf16 pairs) further, two k-chunks further
                         mma_ts_f16(c_d, c_a + s * 8, b_desc + (uint64_t)(s * (kImage16StepBytes >> 4)), idesc_bf16,
@@ -502,7 +516,19 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     mbar_arrive(x_empty(xs));
                     if (!a_free) wait(a_empty(as), a_parity, 1);
                     tc_fence_after();
-                    if (kBf16) {
+                    if (kPasses == 5) {
+                        // columns 0-15: pairs of hi = bf16(x); columns 16-31: pairs of lo = bf16(x - hi)
+                        uint32_t packed[32];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float x0 = __uint_as_float(hi[2 * j]), x1 = __uint_as_float(hi[2 * j + 1]);
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                            const __nv_bfloat162 l = __floats2bfloat162_rn(x0 - __low2float(h), x1 - __high2float(h));
+                            packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                            packed[16 + j] = *reinterpret_cast<const uint32_t*>(&l);
+                        }
+                        tmem_st32(a_hi, packed);
+                    } else if (kBf16) {
                         uint32_t packed[16];  // column j: k = 2j in the low half, k = 2j + 1 in the high half
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
@@ -703,7 +729,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                     uint32_t main_[32];
                     float v[32];
                     tmem_ld32(tmem_lane + r * C::kRowCols, main_);
-                    if (kPasses == 3) {
+                    if (kSplit) {
                         uint32_t corr[32];
                         tmem_ld32(tmem_lane + r * C::kRowCols + 32, corr);
                         tmem_wait_ld();
@@ -846,7 +872,7 @@ cudaError_t device_status_address(unsigned int** addr) {
 cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, const void* packed, const void* plan,
                             int group, int64_t n, void* out, const float* bias, uint32_t precision, bool dgrad,
                             bool out_colmajor, const DsdEpilogue& epilogue, cudaStream_t stream) {
-    if (!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return cudaErrorNotSupported;
+    if (!is_umma_precision(precision)) return cudaErrorNotSupported;
     const bool io16 = epilogue.io_bf16;
     if (io16 && (precision != BSMM_PREC_BF16 || out_colmajor || epilogue.residual != nullptr || epilogue.pre_act != nullptr))
         return cudaErrorNotSupported;
@@ -935,7 +961,14 @@ cudaError_t launch_dsd_umma(const void* a, int64_t m, int64_t k, int64_t nnz, co
     p.trace = g_trace_buffer;
     p.trace_block = g_trace_block;
     const bool split = precision == BSMM_PREC_TF32X3;
-    if (split && group == 8) return cudaErrorInvalidValue;  // 8 rows x 64 columns leave no tensor memory for A
+    if (is_split_precision(precision) && group == 8) return cudaErrorInvalidValue;  // 8 rows x 64 columns leave no tensor memory for A
+    if (precision == BSMM_PREC_BF16X3) {
+        switch (group) {
+            case 4: return launch_dsd_g<4, 5>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
+            case 6: return launch_dsd_g<6, 5>(tmap_a, tmap_out, tmap_pre, peers, p, tiles, stream);
+            default: return cudaErrorInvalidValue;
+        }
+    }
     if (precision == BSMM_PREC_BF16) {
         if (group == 5) return cudaErrorInvalidValue;  // the 5-row tile exists for 3xTF32 only
         if (io16) {

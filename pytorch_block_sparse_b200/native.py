@@ -15,11 +15,12 @@ LIB_PATH = os.path.join(_PKG_DIR, "libbsmm_b200.so")
 # mirrors include/bsmm_b200.h
 ABI_VERSION = 2
 OK = 0
-PREC_FP32_SIMT, PREC_TF32X3, PREC_BF16, PREC_TF32 = 0, 1, 2, 3
+PREC_FP32_SIMT, PREC_TF32X3, PREC_BF16, PREC_TF32, PREC_BF16X3 = 0, 1, 2, 3, 4
 DSD_DGRAD, DSD_OUT_COLMAJOR, DSD_GELU, DSD_IO_BF16 = 0x10, 0x20, 0x40, 0x80
 SDDMM_A_COLMAJOR, SDDMM_B_COLMAJOR, SDDMM_IO_BF16 = 0x10, 0x20, 0x40
 
-PRECISIONS = {"fp32": PREC_FP32_SIMT, "simt": PREC_FP32_SIMT, "tf32x3": PREC_TF32X3, "tf32": PREC_TF32, "bf16": PREC_BF16}
+PRECISIONS = {"fp32": PREC_FP32_SIMT, "simt": PREC_FP32_SIMT, "tf32x3": PREC_TF32X3, "tf32": PREC_TF32, "bf16": PREC_BF16,
+              "bf16x3": PREC_BF16X3}
 EXPORTS = (
     "bsmm_abi_version",
     "bsmm_status_string",
@@ -303,7 +304,7 @@ class DsdPlan:
     def group_for(self, m, precision):
         forced = os.environ.get("BSMM_PLAN_GROUP")
         if forced:
-            return min(int(forced), 6) if precision == PREC_TF32X3 else int(forced)
+            return min(int(forced), 6) if precision in (PREC_TF32X3, PREC_BF16X3) else int(forced)
         return load().bsmm_plan_group(m, self.n_out_blocks, self.nnz, precision)
 
     def buffer(self, group):

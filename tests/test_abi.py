@@ -48,6 +48,10 @@ def test_size_queries():
     assert lib.bsmm_plan_group(4096, 96, 2304, native.PREC_TF32X3) == 6
     assert lib.bsmm_plan_group(128, 24, 288, native.PREC_TF32X3) == 4
     assert lib.bsmm_packed_bytes(10, native.PREC_TF32) == 2 * 10 * 8192
+    assert lib.bsmm_packed_bytes(10, native.PREC_BF16X3) == 2 * 10 * 4096  # bf16 hi | lo images
+    assert lib.bsmm_plan_group(16384, 128, 4096, native.PREC_BF16X3) == 4  # rows with correction columns: as 3xTF32
+    assert lib.bsmm_sddmm_workspace_bytes(4096, 4096, 16384, 4096, native.PREC_BF16X3) == \
+        lib.bsmm_sddmm_workspace_bytes(4096, 4096, 16384, 4096, native.PREC_TF32X3) > 0  # wgrad computes as 3xTF32
     assert lib.bsmm_sddmm_plan_bytes(8, 100) == 16 + 16 * (100 // 8 + 8)  # items of at most 8 blocks
     assert lib.bsmm_sddmm_workspace_bytes(64, 64, 100, 2, native.PREC_FP32_SIMT) == 0
 

@@ -28,7 +28,7 @@ def _matrix(shape, n_blocks, seed):
 
 
 @pytest.mark.parametrize("rows,n_blocks,tokens", [(512, 70, 300), (2368, 12, 9000)])
-@pytest.mark.parametrize("precision", ["tf32x3", "tf32", "bf16"])
+@pytest.mark.parametrize("precision", ["tf32x3", "bf16x3", "tf32", "bf16"])
 def test_forward_writes_its_column_slice_to_every_output(precision, rows, n_blocks, tokens):
     # bsmm_dsd_multi: each "rank" writes the columns of its block-row shard into both full-width outputs
     # (second case: a dozen blocks in 74 block-rows -- whole tiles without a block still deliver their bias tiles)

@@ -1,8 +1,8 @@
 """GPU parity of the three contractions, called through the C-ABI (native.* -> ctypes ->
 libbsmm_b200.so), against the CPU oracle on identical seeded inputs.
 
-Tolerances: relative Frobenius error <= 1e-5 for the fp32-class modes ("fp32" CUDA-core FMA and
-"tf32x3" tensor-core 3-pass), bookkeeping bit-exact.  Shapes follow the reference's own tests
+Tolerances: relative Frobenius error <= 1e-5 for the fp32-class modes ("fp32" CUDA-core FMA, "tf32x3"
+tensor-core 3-pass and "bf16x3", which splits into bf16 pairs in forward and dgrad), bookkeeping bit-exact.  Shapes follow the reference's own tests
 (pytorch_block_sparse/tests/test_matmul.py:141-244, test_matmul_back.py:205-238, test_replace.py:140-161).
 """
 import numpy as np
@@ -18,7 +18,7 @@ from .gpu_util import TOL, assert_device_healthy, check, host, make_matrix, rand
 
 pytestmark = pytest.mark.gpu
 
-PRECISIONS = ["fp32", "tf32x3"]
+PRECISIONS = ["fp32", "tf32x3", "bf16x3"]
 
 # (leading dims of a, sizes[1], sizes[2], blocks) -- reference tests/test_matmul.py:141-227
 REFERENCE_CASES = [
@@ -308,12 +308,13 @@ def test_dsd_long_rows_stay_within_the_error_bound(precision):
     past 1e-5 here; the periodic promotion to an fp32 master tile keeps the error at the CUDA-core level."""
     m = make_matrix((256, 4096), n_blocks=int(0.75 * 8 * 128), seed=31)
     x = randn((256, 4096), seed=32)
+    bound = 6e-6 if precision == "bf16x3" else 4e-6  # (the bf16 pair splitting alone leaves 4.6e-6)
     err = check(run_dsd(m, x, True, precision), oracle_dsd(m, x, True), precision, "fwd")
-    assert err < 4e-6, err
+    assert err < bound, err
     m2 = make_matrix((4096, 256), n_blocks=int(0.75 * 8 * 128), seed=33)
     dy = randn((256, 4096), seed=34)
     err = check(run_dsd(m2, dy, False, precision), oracle_dsd(m2, dy, False), precision, "dgrad")
-    assert err < 4e-6, err
+    assert err < bound, err
     assert_device_healthy()
 
 
@@ -348,7 +349,7 @@ def test_sddmm_long_token_axis_and_statistic(precision):
     assert_device_healthy()
 
 
-@pytest.mark.parametrize("precision", ["tf32x3", "tf32", "bf16"])
+@pytest.mark.parametrize("precision", ["tf32x3", "bf16x3", "tf32", "bf16"])
 @pytest.mark.parametrize("a_rowmajor,b_rowmajor", [(False, True), (True, False), (False, False)])
 def test_sddmm_feature_major_operands_stay_on_the_tensor_cores(precision, a_rowmajor, b_rowmajor):
     """The reference serves all four contiguity combinations of (dY, X) with one kernel
@@ -480,7 +481,7 @@ def _full_size_case(shape, n_blocks, tokens, precision, seed, check_reference_ke
     assert_device_healthy()
 
 
-@pytest.mark.parametrize("precision", ["tf32x3", "tf32", "bf16"])
+@pytest.mark.parametrize("precision", ["tf32x3", "bf16x3", "tf32", "bf16"])
 def test_full_size_config3(precision):
     """Benchmark configuration 3 at density 0.25 in full (4096 x 4096, 4096 blocks, 16384 tokens): every
     persistent CTA walks ~28 tiles."""

@@ -15,7 +15,7 @@ from .gpu_util import assert_device_healthy
 
 pytestmark = pytest.mark.gpu
 
-TOL = {"tf32x3": 1e-5, "tf32": 3e-3, "bf16": 1.5e-2}
+TOL = {"tf32x3": 1e-5, "bf16x3": 1e-5, "tf32": 3e-3, "bf16": 1.5e-2}
 TOKENS = [1, 2, 31, 32, 33, 64, 100, 127, 128, 129, 255, 256, 500, 1000, 1024, 2048, 4100, 9000, 20000]
 DENSITIES = [0.02, 0.05, 0.1, 0.25, 0.5, 0.9, 1.0]
 
@@ -46,7 +46,7 @@ def test_random_cases(seed):
         want_y, want_dx = x.double() @ dense.t() + bias.double(), dy.double() @ dense
         want_dw = (dy.double().t() @ x.double()) * mask
         what = (seed, case, tokens, n, k, nnz, bs)
-        for precision in ("tf32x3", "tf32", "bf16"):
+        for precision in ("tf32x3", "bf16x3", "tf32", "bf16"):
             y = w.reverse_matmul(x, True, bias=bias, precision=precision)
             dx = w.reverse_matmul(dy, False, precision=precision)
             dw = w.to_dense(data_replace=w.matmul_with_output_sparse_support(dy, x, precision=precision))
