@@ -55,9 +55,10 @@ extern "C" {
 #define BSMM_PREC_TF32X3 1u    /* tcgen05 kind::tf32, 3-pass hi/lo split, fp32-class accuracy  */
 #define BSMM_PREC_BF16 2u      /* tcgen05 kind::f16: operands rounded to bf16 in the kernel, fp32 accumulate; tensors stay fp32 */
 #define BSMM_PREC_TF32 3u      /* tcgen05 kind::tf32, single pass (cuBLAS allow_tf32 accuracy class) */
-#define BSMM_PREC_BF16X3 4u    /* fp32-class accuracy (about 2e-6): bsmm_dsd splits both operands into bf16 hi + lo parts and
-                                  adds three kind::f16 products with fp32 accumulation (half the tensor-core instructions of
-                                  BSMM_PREC_TF32X3); bsmm_sddmm computes as BSMM_PREC_TF32X3; tensors stay fp32 */
+#define BSMM_PREC_BF16X3 4u    /* fp32-class accuracy (about 5e-6): both operands are split into bf16 hi + lo parts and three
+                                  kind::f16 products are added with fp32 accumulation: half the tensor-core instructions of
+                                  BSMM_PREC_TF32X3 (bsmm_sddmm with a feature-major operand computes as BSMM_PREC_TF32X3);
+                                  tensors stay fp32 */
 #define BSMM_PREC_MASK 0xFu
 
 /* bsmm_dsd flags */
@@ -108,13 +109,13 @@ int bsmm_pack_weights(const float* data, int64_t nnz, uint32_t precision, void* 
 
 /*
  * Per-pattern launch plan of the tensor-core dsd kernel: for every group of `group`
- * consecutive output block-rows (group = 4, 5, 6 or 8; 5 with BSMM_PREC_TF32X3 only, 8 not with it: the kernel's tile is 128 tokens x group*32
+ * consecutive output block-rows (group = 4, 5, 6 or 8; 5 with BSMM_PREC_TF32X3 only, 8 neither with it nor with BSMM_PREC_BF16X3: the kernel's tile is 128 tokens x group*32
  * columns), the group's index entries re-ordered by (inner block index, row-in-group), with the
  * points at which the kernel promotes its tensor-memory partial sums.  `plan` must hold
  * bsmm_plan_bytes(n_out_blocks, nnz, group) bytes, 16-byte aligned.  Depends only on ptr/idx
  * (each row's entries in ascending inner index, as the reference builds them); rebuild after
  * block_replace / load_state_dict.  bsmm_plan_group suggests a group size for a problem shape and
- * precision (BSMM_PREC_TF32X3 takes 4 or 6: its rows occupy 64 tensor-memory columns each).
+ * precision (BSMM_PREC_TF32X3 and BSMM_PREC_BF16X3 take 4 or 6: their rows occupy 64 tensor-memory columns each).
  */
 int bsmm_plan_group(int64_t m, int64_t n_out_blocks, int64_t nnz, uint32_t precision);
 int64_t bsmm_plan_bytes(int64_t n_out_blocks, int64_t nnz, int group);

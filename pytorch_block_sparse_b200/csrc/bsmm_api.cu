@@ -19,12 +19,6 @@ bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) &
 // them, so every entry point that launches starts from a clean error state.
 void forget_earlier_errors() { (void)cudaGetLastError(); }
 
-// The weight gradient reads no weight images: under BSMM_PREC_BF16X3 it computes as 3xTF32.
-uint32_t sddmm_precision(uint32_t flags) {
-    const uint32_t precision = flags & BSMM_PREC_MASK;
-    return precision == BSMM_PREC_BF16X3 ? BSMM_PREC_TF32X3 : precision;
-}
-
 }  // namespace
 
 extern "C" {
@@ -248,8 +242,8 @@ int bsmm_build_sddmm_plan(const int32_t* ptr, int64_t n_block_rows, int64_t nnz,
 
 int64_t bsmm_sddmm_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t flags) {
     if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0) return -1;
-    const uint32_t precision = sddmm_precision(flags);
-    if (!bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16) return 0;
+    const uint32_t precision = flags & BSMM_PREC_MASK;
+    if (!bsmm::is_umma_precision(precision)) return 0;
     if ((flags & (BSMM_SDDMM_A_COLMAJOR | BSMM_SDDMM_B_COLMAJOR)) != 0 && (tokens % 4) != 0) return 0;
     return bsmm::sddmm_umma_workspace_bytes(rows, cols, tokens, nnz, precision);
 }
@@ -258,7 +252,7 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
                const int32_t* blocks, int64_t nnz, const int32_t* csr_idx, const void* plan, float* block_sumsq,
                void* workspace, uint32_t flags, bsmm_stream_t stream) {
     forget_earlier_errors();
-    const uint32_t precision = sddmm_precision(flags);
+    const uint32_t precision = flags & BSMM_PREC_MASK;
     const bool a_col = (flags & BSMM_SDDMM_A_COLMAJOR) != 0;
     const bool b_col = (flags & BSMM_SDDMM_B_COLMAJOR) != 0;
     if (rows < 0 || cols < 0 || tokens < 0 || nnz < 0 || (rows % 32) != 0 || (cols % 32) != 0)
@@ -270,8 +264,7 @@ int bsmm_sddmm(const void* a, const void* b, int64_t rows, int64_t cols, int64_t
         !aligned(plan, 16) || !aligned(workspace, 16))
         return BSMM_ERR_INVALID_ARGUMENT;
     if (nnz > 0x7fffffff) return BSMM_ERR_TOO_LARGE;
-    if (precision != BSMM_PREC_FP32_SIMT && !bsmm::is_tf32_precision(precision) && precision != BSMM_PREC_BF16)
-        return BSMM_ERR_UNSUPPORTED;
+    if (precision != BSMM_PREC_FP32_SIMT && !bsmm::is_umma_precision(precision)) return BSMM_ERR_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool io16 = (flags & BSMM_SDDMM_IO_BF16) != 0;
     if (io16 && (precision != BSMM_PREC_BF16 || a_col || b_col)) return BSMM_ERR_UNSUPPORTED;

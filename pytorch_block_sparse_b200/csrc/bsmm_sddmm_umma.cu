@@ -103,6 +103,10 @@ __device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint3
 // kPasses = 4: bf16 operands that are bf16 tensors in memory already (token-major): the dY box, loaded with the
 // 64-byte swizzle, IS the MN-major canonical bf16 operand tile (atoms of 8 token rows x 64 bytes), so the dY split
 // warps have nothing to do; the X split warps read 2-byte values and pack token pairs.
+// kPasses = 5: three products of bf16 hi and lo parts of fp32 tensors (token-major), fp32-class accuracy with half the
+// instructions of 3xTF32: the dY split warps write hi = bf16(v) and lo = bf16(v - hi) as two MN-major bf16 tiles
+// (the 64-byte-swizzle layout of the bf16-tensor mode; [hi ; lo] is the N = 64 operand), the X split warps pack
+// token pairs of hi and of lo.
 // kXFm / kDyFm: the operand is given feature-major ([features, tokens] contiguous, the reference's other
 // contiguity case, native/block_sparse_cutlass_kernel_back.cu:145-157) instead of token-major.  The TMA box is then
 // 32 features x 32 tokens with 128-byte token rows: for X that is already the orientation tensor memory wants
@@ -112,8 +116,9 @@ template <int kPasses, bool kXFm, bool kDyFm>
 __global__ void __launch_bounds__(kThreads, 1)
 sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_dy,
                          const SddmmParams p) {
-    constexpr bool kBf16 = kPasses == 0 || kPasses == 4, kIo16 = kPasses == 4;
-    static_assert(!kIo16 || (!kXFm && !kDyFm), "bf16 tensors are taken token-major");
+    constexpr bool kBf16 = kPasses == 0 || kPasses == 4 || kPasses == 5, kIo16 = kPasses == 4;
+    constexpr bool kSplit = kPasses == 3 || kPasses == 5;   // hi and lo parts, correction columns
+    static_assert((!kIo16 && kPasses != 5) || (!kXFm && !kDyFm), "bf16 tensors and the bf16 hi | lo mode take token-major operands");
     constexpr uint32_t kLoadSlabBytes = kIo16 ? kSlabBytes / 2 : kSlabBytes;   // what one TMA box delivers
     const int n_items = p.items[0];
     if ((int)blockIdx.x >= n_items) return;
@@ -240,7 +245,30 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
             wait(dy_full(ds), (uint32_t)(step / kDyStages) & 1u);
             if (__any_sync(0xffffffffu, bad != 0)) break;
             uint8_t* base = smem_gen + kOffDy + ds * kDyStageBytes;
-            if (kPasses == 3) {
+            if (kPasses == 5) {
+                // this warp's 16 tokens x 4 groups of 8 features, two per lane.  The raw slab lies under the plain
+                // 128-byte swizzle (16-byte chunk index XOR token mod 8); the bf16 tiles have 64-byte token rows under
+                // the 64-byte swizzle (chunk index XOR (token / 2) mod 4): hi at +4 KiB, lo at +6 KiB.
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int u = lane + 32 * i;
+                    const int t = 16 * half + (u >> 2), g = u & 3;
+                    const float4 v0 = *reinterpret_cast<const float4*>(base + t * 128 + (((2 * g) ^ (t & 7)) << 4));
+                    const float4 v1 = *reinterpret_cast<const float4*>(base + t * 128 + (((2 * g + 1) ^ (t & 7)) << 4));
+                    const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    uint32_t h[4], l[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const __nv_bfloat162 hp = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+                        const __nv_bfloat162 lp = __floats2bfloat162_rn(f[2 * q] - __low2float(hp), f[2 * q + 1] - __high2float(hp));
+                        h[q] = *reinterpret_cast<const uint32_t*>(&hp);
+                        l[q] = *reinterpret_cast<const uint32_t*>(&lp);
+                    }
+                    const uint32_t off = (uint32_t)(t * 64 + ((g ^ ((t >> 1) & 3)) << 4));
+                    *reinterpret_cast<uint4*>(base + kSlabBytes + off) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(base + kSlabBytes + kSlabBytes / 2 + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                }
+            } else if (kPasses == 3) {
 #pragma unroll
                 for (int i = 4 * half; i < 4 * half + 4; ++i) {
                     const float4 v = *reinterpret_cast<const float4*>(base + (lane + 32 * i) * 16);
@@ -270,14 +298,21 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 }
             } else {
                 // lane = feature r; the slab (plain 128-byte swizzle in this mode) is read along the tokens
+                // and written eight tokens (one 16-byte core-matrix row) at a time: consecutive lanes, consecutive rows
                 const uint8_t* col = base + ((lane & 3) << 2);
 #pragma unroll
-                for (int t = 16 * half; t < 16 * half + 16; t += 2) {
-                    const float v0 = *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (t & 7)) << 4));
-                    const float v1 = *reinterpret_cast<const float*>(col + (t + 1) * 128 + (((lane >> 2) ^ ((t + 1) & 7)) << 4));
-                    const __nv_bfloat162 pr = __floats2bfloat162_rn(v0, v1);  // k = t low half, k = t + 1 high half
-                    *reinterpret_cast<uint32_t*>(base + kSlabBytes + image16_offset((uint32_t)lane, (uint32_t)t)) =
-                        *reinterpret_cast<const uint32_t*>(&pr);
+                for (int t0 = 16 * half; t0 < 16 * half + 16; t0 += 8) {
+                    uint32_t pk[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int t = t0 + 2 * i;   // (t0 is a multiple of 8: t mod 8 = 2 i)
+                        const float v0 = *reinterpret_cast<const float*>(col + t * 128 + (((lane >> 2) ^ (2 * i)) << 4));
+                        const float v1 = *reinterpret_cast<const float*>(col + (t + 1) * 128 + (((lane >> 2) ^ (2 * i + 1)) << 4));
+                        const __nv_bfloat162 pr = __floats2bfloat162_rn(v0, v1);  // k = t low half, k = t + 1 high half
+                        pk[i] = *reinterpret_cast<const uint32_t*>(&pr);
+                    }
+                    *reinterpret_cast<uint4*>(base + kSlabBytes + image16_offset((uint32_t)lane, (uint32_t)t0)) =
+                        make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
             }
             fence_proxy_async_smem();  // generic-proxy writes, read by the MMA through the async proxy
@@ -288,7 +323,8 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const int ch = warp - kFirstMmaWarp;  // accumulations into one chunk stay in one thread's program order
         constexpr uint32_t idesc_wide = make_idesc(2u, 128u, 64u, false, !kDyFm);
         constexpr uint32_t idesc_narrow = make_idesc(2u, 128u, 32u, false, !kDyFm);
-        constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, kIo16);  // bf16 tensors: B is MN-major
+        constexpr uint32_t idesc_bf16 = make_idesc(1u, 128u, 32u, false, kIo16 || kPasses == 5);  // bf16 tensors, hi | lo tiles: B is MN-major
+        constexpr uint32_t idesc_bf16_wide = make_idesc(1u, 128u, 64u, false, true);
         // The loop is cut into promotion segments (kDrainSteps steps) so that the per-step body has no
         // first-step / last-step decisions: a conditional branch costs this lone warp ~40 cycles, and the
         // body's length bounds how fast a chunk's stages turn around.
@@ -321,7 +357,16 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 // the split warps' tcgen05.st (and the drain warps' tcgen05.ld of the columns) precede the MMAs
                 tc_fence_after();
                 if (elect_one() & (bad == 0)) {
-                    if (kBf16) {
+                    if (kPasses == 5) {
+                        // [hi tile ; lo tile]: two atoms of 32 features along N, 2 KiB apart; 16 tokens = 1 KiB per instruction
+                        const uint64_t b16 = smem_desc_sw64(smem_base + kOffDy + ds * kDyStageBytes + kSlabBytes, kSlabBytes / 2, 512);
+#pragma unroll
+                        for (int s = 0; s < 2; ++s) {  // x_hi pairs in columns 0-15 of the stage, x_lo pairs in 16-31
+                            const uint64_t b = b16 + (uint64_t)(s * (1024 >> 4));
+                            mma_ts_f16(d, a_tm + s * 8, b, idesc_bf16_wide, s == 0 ? acc0 : 1u);   // x_hi x [dy_hi ; dy_lo]
+                            mma_ts_f16(d + 32, a_tm + 16 + s * 8, b, idesc_bf16, 1u);              // x_lo x dy_hi
+                        }
+                    } else if (kBf16) {
                         // K-major bf16 tile made by the dY split warps, or (bf16 tensors) the box as TMA wrote it:
                         // atoms of 8 token rows x 64 bytes, 512 bytes apart along K, 16 tokens = 1 KiB per instruction
                         const uint64_t b16 =
@@ -406,10 +451,20 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                     }
                 }
             }
-            mbar_arrive(x_empty(xs));
             tc_fence_after();
             const uint32_t a_tm = tmem_lane + kAccCols + xs * kAStageCols;
-            if (kBf16) {
+            if (kPasses == 5) {
+                uint32_t packed[32];  // columns 0-15: token pairs of hi = bf16(x); columns 16-31: of lo = bf16(x - hi)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float x0 = __uint_as_float(hi[2 * j]), x1 = __uint_as_float(hi[2 * j + 1]);
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                    const __nv_bfloat162 l = __floats2bfloat162_rn(x0 - __low2float(h), x1 - __high2float(h));
+                    packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    packed[16 + j] = *reinterpret_cast<const uint32_t*>(&l);
+                }
+                tmem_st32(a_tm, packed);
+            } else if (kBf16) {
                 uint32_t packed[16];  // column j: token 2j in the low half, token 2j + 1 in the high half
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -425,6 +480,11 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 tmem_st32(a_tm, hi);
                 if (kPasses == 3) tmem_st32(a_tm + 32, lo);
             }
+            // The slabs are released only here: the stores above took every loaded value as an operand, so the loads
+            // have returned.  Released right after the loads were issued, a refill (TMA, async proxy) has been seen
+            // to overtake reads still queued in the load/store unit (generic proxy): a few rows of a slab were then
+            // read from the next unit.  (The alternative, a proxy fence before the arrival, costs 3 % more.)
+            mbar_arrive(x_empty(xs));
             tmem_wait_st();
             tc_fence_before();
             if ((lane == 0) & (bad == 0)) smem_add_release(a_count(xs), 1u);  // nothing is published once a wait has given up
@@ -457,9 +517,9 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 tc_fence_after();
                 uint32_t acc[32], corr[32];
                 tmem_ld32(tmem_lane + ch * kChunkCols, acc);
-                if (kPasses == 3) tmem_ld32(tmem_lane + ch * kChunkCols + 32, corr);
+                if (kSplit) tmem_ld32(tmem_lane + ch * kChunkCols + 32, corr);
                 tmem_wait_ld();
-                if (kPasses != 3) {
+                if (!kSplit) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) corr[j] = 0u;
                 }
@@ -639,7 +699,7 @@ cudaError_t launch_build_sddmm_plan(const int32_t* ptr, int64_t n_rows, int64_t 
 }
 
 int64_t sddmm_umma_workspace_bytes(int64_t rows, int64_t cols, int64_t tokens, int64_t nnz, uint32_t precision) {
-    if ((!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) || tokens < kStepTokens || nnz == 0) return 0;
+    if (!is_umma_precision(precision) || tokens < kStepTokens || nnz == 0) return 0;
     int64_t splits, per;
     choose_splits(rows / 32, cols, nnz, tokens, &splits, &per);
     return splits > 1 ? splits * nnz * (int64_t)kBlockElems * 4 : 0;
@@ -685,8 +745,7 @@ cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b
                               int64_t nnz, float* block_sumsq, void* workspace, uint32_t precision, bool io_bf16,
                               cudaStream_t stream) {
     if (io_bf16 && (precision != BSMM_PREC_BF16 || a_feature_major || b_feature_major)) return cudaErrorNotSupported;
-    if ((!is_tf32_precision(precision) && precision != BSMM_PREC_BF16) || plan == nullptr || csr_idx == nullptr)
-        return cudaErrorNotSupported;
+    if (!is_umma_precision(precision) || plan == nullptr || csr_idx == nullptr) return cudaErrorNotSupported;
     if (tokens < kStepTokens) return cudaErrorNotSupported;  // a box may not exceed its tensor
     // a feature-major tensor has rows of `tokens` floats: the tensor map wants that pitch to be a multiple of 16 bytes
     if ((a_feature_major || b_feature_major) && (tokens % 4) != 0) return cudaErrorNotSupported;
@@ -697,7 +756,10 @@ cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b
     if (splits > 1 && workspace == nullptr) return cudaErrorInvalidValue;
     if (splits > 65535) return cudaErrorInvalidValue;
 
-    const bool x3 = precision == BSMM_PREC_TF32X3, bf16 = precision == BSMM_PREC_BF16;
+    // the bf16 hi | lo kernel takes token-major operands; feature-major ones compute as 3xTF32 (same accuracy class)
+    const bool x5 = precision == BSMM_PREC_BF16X3 && !a_feature_major && !b_feature_major;
+    const bool x3 = precision == BSMM_PREC_TF32X3 || (precision == BSMM_PREC_BF16X3 && !x5);
+    const bool bf16 = precision == BSMM_PREC_BF16;
     CUtensorMap tmap_x, tmap_dy;
     cudaError_t err;
     if (io_bf16) {
@@ -722,7 +784,7 @@ cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b
                            CU_TENSOR_MAP_SWIZZLE_128B);
     else
         err = make_tmap_2d(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)rows, (uint64_t)tokens, 32,
-                           kStepTokens, bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+                           kStepTokens, (bf16 || x5) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (err != cudaSuccess) return err;
 
     SddmmParams p;
@@ -737,6 +799,7 @@ cudaError_t launch_sddmm_umma(const void* a, bool a_feature_major, const void* b
     p.split_stride = nnz * (int64_t)kBlockElems;
     dim3 grid((unsigned)max_items(n_rows, nnz), (unsigned)splits);
     if (x3) err = launch_layout<3>(b_feature_major, a_feature_major, grid, tmap_x, tmap_dy, p, stream);
+    else if (x5) err = launch_variant<5, false, false>(grid, tmap_x, tmap_dy, p, stream);
     else if (io_bf16) err = launch_variant<4, false, false>(grid, tmap_x, tmap_dy, p, stream);
     else if (bf16) err = launch_layout<0>(b_feature_major, a_feature_major, grid, tmap_x, tmap_dy, p, stream);
     else err = launch_layout<1>(b_feature_major, a_feature_major, grid, tmap_x, tmap_dy, p, stream);

@@ -492,6 +492,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((j ^ ((row >> 1) & 3)) << 4));
                         packed[4 * j + 0] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
                     }
+                    fence_proxy_async_smem();  // generic-proxy reads before the TMA refill (async proxy) that the arrival allows
                     mbar_arrive(x_empty(xs));
                     if (!a_free) wait(a_empty(as), a_parity, 1);
                     tc_fence_after();
@@ -513,6 +514,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                             }
                         }
                     }
+                    fence_proxy_async_smem();  // generic-proxy reads before the TMA refill (async proxy) that the arrival allows
                     mbar_arrive(x_empty(xs));
                     if (!a_free) wait(a_empty(as), a_parity, 1);
                     tc_fence_after();

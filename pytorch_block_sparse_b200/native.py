@@ -145,7 +145,9 @@ def device_status(clear=True):
 
 
 def set_default_precision(name):
-    """'tf32x3' (default; fp32-class accuracy on tensor cores), 'fp32' (CUDA-core FMA), 'tf32' (single
+    """'tf32x3' (default; fp32-class accuracy on tensor cores), 'bf16x3' (fp32-class too, about 5e-6 instead of
+    2e-6: forward and input gradient add three products of bf16 hi and lo parts, half the tensor-core
+    instructions; the weight gradient computes as 'tf32x3'), 'fp32' (CUDA-core FMA), 'tf32' (single
     tensor-core pass, the accuracy class of cuBLAS with allow_tf32) or 'bf16' (operands rounded to bf16 inside
     the kernels, fp32 tensors and accumulation)."""
     global _default_precision

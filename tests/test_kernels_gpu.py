@@ -344,7 +344,7 @@ def test_sddmm_long_token_axis_and_statistic(precision):
     torch.cuda.synchronize()
     want = orc.wgrad(dy.numpy(), x.numpy(), (128, 1024), m.blocks.cpu().numpy())
     err = check(out, want, precision)
-    assert err < 4e-6, err
+    assert err < (6e-6 if precision == "bf16x3" else 4e-6), err  # (the bf16 pair splitting alone leaves 4.6e-6)
     assert np.allclose(sumsq.cpu().numpy(), orc.block_norm(want) ** 2, rtol=1e-4)
     assert_device_healthy()
 
@@ -478,6 +478,25 @@ def _full_size_case(shape, n_blocks, tokens, precision, seed, check_reference_ke
     del yp, y0
     dwp = m.matmul_with_output_sparse_support(dy[perm].contiguous(), x[perm].contiguous(), precision=precision)
     assert _rel_fro_gpu(dwp, dw) <= tol  # a sum over tokens in another order
+    assert_device_healthy()
+
+
+def test_sddmm_repeated_launches_agree_bit_for_bit():
+    """Regression: the X split warps used to release a slab right after issuing their loads; now and then the TMA
+    refill overtook loads still queued, and a few rows of one block came from the next unit (a few per cent off,
+    in about one launch in 25 with feature-major X, whose 16-byte loads leave the warps earliest).  Every storage
+    order and tensor-core precision, many launches: all results of one configuration are identical."""
+    m = make_matrix((832, 992), n_blocks=26 * 31, seed=517)  # rows of 31 blocks: items of 8, 8, 8 and 7
+    dy = randn((2400, 832), seed=518).cuda()
+    x = randn((2400, 992), seed=519).cuda()
+    dy_fm, x_fm = dy.t().contiguous().t(), x.t().contiguous().t()
+    for precision in ("tf32x3", "bf16x3", "tf32", "bf16"):
+        want = m.matmul_with_output_sparse_support(dy, x, precision=precision).clone()
+        for a, b in ((dy, x_fm), (dy_fm, x_fm), (dy_fm, x), (dy, x)):
+            first = m.matmul_with_output_sparse_support(a, b, precision=precision).clone()
+            assert _rel_fro_gpu(first, want) <= TOL[precision], precision
+            for _ in range(60):
+                assert torch.equal(m.matmul_with_output_sparse_support(a, b, precision=precision), first), precision
     assert_device_healthy()
 
 
