@@ -492,8 +492,6 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((j ^ ((row >> 1) & 3)) << 4));
                         packed[4 * j + 0] = v.x; packed[4 * j + 1] = v.y; packed[4 * j + 2] = v.z; packed[4 * j + 3] = v.w;
                     }
-                    fence_proxy_async_smem();  // generic-proxy reads before the TMA refill (async proxy) that the arrival allows
-                    mbar_arrive(x_empty(xs));
                     if (!a_free) wait(a_empty(as), a_parity, 1);
                     tc_fence_after();
                     tmem_st16(a_hi, packed);
@@ -514,8 +512,6 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                             }
                         }
                     }
-                    fence_proxy_async_smem();  // generic-proxy reads before the TMA refill (async proxy) that the arrival allows
-                    mbar_arrive(x_empty(xs));
                     if (!a_free) wait(a_empty(as), a_parity, 1);
                     tc_fence_after();
                     if (kPasses == 5) {
@@ -543,6 +539,11 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         if (kPasses == 3) tmem_st32(a_hi + 32, lo);
                     }
                 }
+                // The slab is released only here: the stores above took every loaded value as an operand, so the loads
+                // have returned.  Released right after the loads were issued, the refill (TMA, async proxy) could
+                // overtake reads still queued in the load/store unit (generic proxy); a proxy fence before the arrival
+                // would also do, and costs 1-5 % more.
+                mbar_arrive(x_empty(xs));
                 tmem_wait_st();
                 tc_fence_before();
                 if ((lane == 0) & (bad == 0)) smem_add_release(a_count(as), 1u);  // nothing is published once a wait has given up
