@@ -695,14 +695,14 @@ def run_c4(dev, world, rank, steps):
            "patched": "intermediate.dense, output.dense, attention.output.dense at density 0.5"}
     # the patched model twice: with cuBLAS TF32 for the layers that stayed dense (QKV projections, LM head), as
     # beside "dense_tf32", and with strict fp32 there, as beside "dense_fp32"; the sparse layers run in the
-    # library's precision either way -- and once more with single-pass TF32 in the sparse layers too, the
-    # like-for-like partner of "dense_tf32"
+    # library's precision either way -- once more with the other fp32-class mode ("bf16x3") and once with
+    # single-pass TF32 in the sparse layers too, the like-for-like partner of "dense_tf32"
     from pytorch_block_sparse_b200 import native
 
     model = build(True)
     default_precision = native.default_precision()
     for name, tf32, sparse_prec in (("sparse", True, default_precision), ("sparse_fp32_rest", False, default_precision),
-                                    ("sparse_tf32", True, "tf32")):
+                                    ("sparse_bf16x3", True, "bf16x3"), ("sparse_tf32", True, "tf32")):
         native.set_default_precision(sparse_prec)
         try:
             ms, grad_bytes, sparse_bytes, loss = train_ms(model, tf32=tf32)
