@@ -35,9 +35,9 @@ class DenseTwin(torch.nn.Module):
         return torch.nn.functional.linear(x, self.weight * self.mask, self.bias)
 
 
-@pytest.mark.parametrize("precision", ["fp32", "tf32x3"])
+@pytest.mark.parametrize("precision,atol", [("fp32", 1e-5), ("tf32x3", 1e-5), ("bf16x3", 3e-5)])
 @pytest.mark.parametrize("bias", [True, False])
-def test_training_steps_match_dense_masked_twin(precision, bias):
+def test_training_steps_match_dense_masked_twin(precision, atol, bias):
     # reference tests/test_linear_nn.py:58-134: output, dX and dW agree step after step under Adam, 40 steps
     native.set_default_precision(precision)
     try:
@@ -56,16 +56,17 @@ def test_training_steps_match_dense_masked_twin(precision, bias):
             x = torch.randn(8, 50, 256, device="cuda", requires_grad=True)
             x2 = x.detach().clone().requires_grad_(True)
             y, y2 = lin(x), twin(x2)
-            assert torch.allclose(y, y2, atol=1e-5, rtol=1e-4), (step, (y - y2).abs().max())
+            assert torch.allclose(y, y2, atol=atol, rtol=1e-4), (step, (y - y2).abs().max())
             g = torch.randn_like(y)
             opt_a.zero_grad()
             opt_b.zero_grad()
             y.backward(g)
             y2.backward(g)
-            assert torch.allclose(x.grad, x2.grad, atol=1e-5, rtol=1e-4), step
+            assert torch.allclose(x.grad, x2.grad, atol=atol, rtol=1e-4), step
             dw = lin.weight.to_dense(data_replace=lin.weight.data.grad)
             dw2 = twin.weight.grad * twin.mask
-            assert torch.allclose(dw, dw2, atol=2e-4, rtol=1e-4), (step, (dw - dw2).abs().max())
+            # (entries of a gradient block are sums of 400 products of N(0,1) values: 1e-5 of their scale is 2e-4)
+            assert torch.allclose(dw, dw2, atol=20 * atol, rtol=1e-4), (step, (dw - dw2).abs().max())
             if bias:
                 assert torch.allclose(lin.bias.grad, twin.bias.grad, atol=1e-4, rtol=1e-4)
             opt_a.step()
