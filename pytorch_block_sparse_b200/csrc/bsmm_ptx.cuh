@@ -111,6 +111,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Two-part bf16 splitting of a pair of fp32 values: hi = {bf16(x0), bf16(x1)} (round to nearest, x0 in the low
+// half), lo = {bf16(x0 - hi0), bf16(x1 - hi1)}.  The differences are exact in fp32; the mixed-precision fma takes
+// the bf16 halves of hi as they are (hi * -1 + x), so nothing is unpacked: four instructions per pair.
+__device__ __forceinline__ void split_bf16x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    asm("{\n\t.reg .b16 h0, h1, m1;\n\t.reg .f32 d0, d1;\n\t"
+        "cvt.rn.bf16x2.f32 %0, %3, %2;\n\t"
+        "mov.b32 {h0, h1}, %0;\n\t"
+        "mov.b16 m1, 0xBF80;\n\t"
+        "fma.rn.f32.bf16 d0, h0, m1, %2;\n\t"
+        "fma.rn.f32.bf16 d1, h1, m1, %3;\n\t"
+        "cvt.rn.bf16x2.f32 %1, d1, d0;\n\t}"
+        : "=&r"(hi), "=r"(lo)
+        : "f"(x0), "f"(x1));
+}
+
 // ---------------------------------------------------------------- TMA
 // 2-D tiled load: box starting at element (x, y) of the tensor described by `tmap` -> smem,
 // completing `bar` with the box's byte count.  x * element size must be a multiple of 16 B.

@@ -258,12 +258,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                     const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
                     uint32_t h[4], l[4];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const __nv_bfloat162 hp = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
-                        const __nv_bfloat162 lp = __floats2bfloat162_rn(f[2 * q] - __low2float(hp), f[2 * q + 1] - __high2float(hp));
-                        h[q] = *reinterpret_cast<const uint32_t*>(&hp);
-                        l[q] = *reinterpret_cast<const uint32_t*>(&lp);
-                    }
+                    for (int q = 0; q < 4; ++q) split_bf16x2(f[2 * q], f[2 * q + 1], h[q], l[q]);
                     const uint32_t off = (uint32_t)(t * 64 + ((g ^ ((t >> 1) & 3)) << 4));
                     *reinterpret_cast<uint4*>(base + kSlabBytes + off) = make_uint4(h[0], h[1], h[2], h[3]);
                     *reinterpret_cast<uint4*>(base + kSlabBytes + kSlabBytes / 2 + off) = make_uint4(l[0], l[1], l[2], l[3]);
@@ -457,11 +452,7 @@ sddmm_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
                 uint32_t packed[32];  // columns 0-15: token pairs of hi = bf16(x); columns 16-31: of lo = bf16(x - hi)
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float x0 = __uint_as_float(hi[2 * j]), x1 = __uint_as_float(hi[2 * j + 1]);
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                    const __nv_bfloat162 l = __floats2bfloat162_rn(x0 - __low2float(h), x1 - __high2float(h));
-                    packed[j] = *reinterpret_cast<const uint32_t*>(&h);
-                    packed[16 + j] = *reinterpret_cast<const uint32_t*>(&l);
+                    split_bf16x2(__uint_as_float(hi[2 * j]), __uint_as_float(hi[2 * j + 1]), packed[j], packed[16 + j]);
                 }
                 tmem_st32(a_tm, packed);
             } else if (kBf16) {

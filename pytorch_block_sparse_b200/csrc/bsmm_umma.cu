@@ -519,11 +519,7 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         uint32_t packed[32];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const float x0 = __uint_as_float(hi[2 * j]), x1 = __uint_as_float(hi[2 * j + 1]);
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                            const __nv_bfloat162 l = __floats2bfloat162_rn(x0 - __low2float(h), x1 - __high2float(h));
-                            packed[j] = *reinterpret_cast<const uint32_t*>(&h);
-                            packed[16 + j] = *reinterpret_cast<const uint32_t*>(&l);
+                            split_bf16x2(__uint_as_float(hi[2 * j]), __uint_as_float(hi[2 * j + 1]), packed[j], packed[16 + j]);
                         }
                         tmem_st32(a_hi, packed);
                     } else if (kBf16) {
