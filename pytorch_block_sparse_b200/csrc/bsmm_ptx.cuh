@@ -111,6 +111,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// lo parts of the 3xTF32 splitting of two fp32 values (bit patterns): x - trunc_tf32(x), the two subtractions as
+// one packed instruction.
+__device__ __forceinline__ void tf32_lo_x2(uint32_t x0, uint32_t x1, uint32_t& lo0, uint32_t& lo1) {
+    asm("{\n\t.reg .b64 a, t, d;\n\t"
+        "mov.b64 a, {%2, %3};\n\t"
+        "mov.b64 t, {%4, %5};\n\t"
+        "sub.rn.f32x2 d, a, t;\n\t"
+        "mov.b64 {%0, %1}, d;\n\t}"
+        : "=r"(lo0), "=r"(lo1)
+        : "r"(x0), "r"(x1), "r"(x0 & 0xffffe000u), "r"(x1 & 0xffffe000u));
+}
+
 // Two-part bf16 splitting of a pair of fp32 values: hi = {bf16(x0), bf16(x1)} (round to nearest, x0 in the low
 // half), lo = {bf16(x0 - hi0), bf16(x1 - hi1)}.  The differences are exact in fp32; the mixed-precision fma takes
 // the bf16 halves of hi as they are (hi * -1 + x), so nothing is unpacked: four instructions per pair.

@@ -503,12 +503,10 @@ dsd_umma_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                         for (int j = 0; j < 8; ++j) {
                             // 128-byte swizzle: the 16-byte chunk index is XORed with (row mod 8)
                             const uint4 v = *reinterpret_cast<const uint4*>(xrow + ((j ^ (row & 7)) << 4));
-                            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                hi[j * 4 + q] = u[q];
-                                if (kPasses == 3)
-                                    lo[j * 4 + q] = __float_as_uint(__uint_as_float(u[q]) - __uint_as_float(u[q] & 0xffffe000u));
+                            hi[j * 4 + 0] = v.x; hi[j * 4 + 1] = v.y; hi[j * 4 + 2] = v.z; hi[j * 4 + 3] = v.w;
+                            if (kPasses == 3) {
+                                tf32_lo_x2(v.x, v.y, lo[j * 4 + 0], lo[j * 4 + 1]);
+                                tf32_lo_x2(v.z, v.w, lo[j * 4 + 2], lo[j * 4 + 3]);
                             }
                         }
                     }
