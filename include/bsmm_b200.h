@@ -58,7 +58,7 @@ extern "C" {
 #define BSMM_PREC_BF16X3 4u    /* fp32-class accuracy (about 5e-6): both operands are split into bf16 hi + lo parts and three
                                   kind::f16 products are added with fp32 accumulation: half the tensor-core instructions of
                                   BSMM_PREC_TF32X3 (bsmm_sddmm with a feature-major operand computes as BSMM_PREC_TF32X3);
-                                  tensors stay fp32 */
+                                  tensors stay fp32; magnitudes above bf16's largest finite value (3.39e38) round to infinity */
 #define BSMM_PREC_MASK 0xFu
 
 /* bsmm_dsd flags */
