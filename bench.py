@@ -1011,6 +1011,12 @@ def run_gpu_arm(args, cfg):
         "device_status": status,
     }
     line.update(extra)
+    # the other fp32-class precision on the headline workload (timed in the sweep leg) beside dense cuBLAS TF32
+    other = extra.get("sweep", {}).get("%s/bf16x3" % args.workload)
+    if other is not None and prec_name == "tf32x3" and "cublas_dense_tf32_ms" in comparators:
+        line["bf16x3"] = {"ms_per_step": other["ms_per_step"], "effective_tflops": other["effective_tflops"],
+                          "vs_cublas_tf32": comparators["cublas_dense_tf32_ms"] / other["ms_per_step"],
+                          "note": "fp32-class (error 5e-6, bound 1e-5): three products of bf16 hi and lo parts"}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
